@@ -1,0 +1,152 @@
+/*
+ * C ABI of the B200 (sm_100a) quantized-GEMM library: libb200_int4_gemms.so.
+ *
+ * This is the boundary a host language binds (ctypes, cgo, JNI ...).  It replaces the
+ * reference's HIP code-object dispatcher, native/src/dispatch.cpp, whose eight exported
+ * symbols are listed beside their counterparts below.  Differences in kind, not in spirit:
+ *
+ *   - the kernels are linked into the library, so there is no code-object path / symbol
+ *     argument, and grid / block / shared-memory sizes are decided inside the library
+ *     instead of being read from per-kernel JSON by the caller;
+ *   - a kernel is named by a plain-old-data variant record (dtype, layout, scale mode,
+ *     epilogue, output type) instead of by a file name.
+ *
+ * Conventions shared with the reference (dispatch.cpp:18-23, :206-222, :224-283):
+ *   - every entry point returns 0 on success and 1 on failure;
+ *   - on failure a thread-local message is available from b200_int4_gemms_last_error();
+ *     it is cleared on entry to every launch call;
+ *   - all buffers are caller-owned DEVICE pointers; launches are asynchronous on the
+ *     caller's stream (a cudaStream_t passed as an integer); no call synchronises;
+ *   - the device is selected per call (cudaSetDevice(device_index)).
+ *
+ * Operand format (bit-exact with the reference's quant.py:32-51):
+ *   int4 operands are uint8 bytes holding two signed nibbles packed along K: the low
+ *   nibble is the even k index, the high nibble the odd one.  int8 operands are plain
+ *   signed bytes.  Scales are bfloat16.  Accumulation is exact int32.
+ */
+#ifndef B200_INT4_GEMMS_H_
+#define B200_INT4_GEMMS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { B200_DTYPE_INT4 = 0, B200_DTYPE_INT8 = 1 };
+/* Operand layouts: first letter A, second letter B; N = as given, T = transposed.
+ *   NN: A [M, Kb]   B [Kb, N]        NT: A [M, Kb]   B [N, Kb]
+ *   TN: A [Kb, M]   B [Kb, N]        TT: A [Kb, M]   B [N, Kb]
+ * Kb is K bytes: K/2 (rounded up) for int4, K for int8. */
+enum { B200_LAYOUT_NN = 0, B200_LAYOUT_NT = 1, B200_LAYOUT_TN = 2, B200_LAYOUT_TT = 3 };
+enum { B200_SCALE_PER_CHANNEL = 0, B200_SCALE_SUBCHANNEL = 1 };
+enum { B200_EPILOGUE_NONE = 0, B200_EPILOGUE_RELU2 = 1, B200_EPILOGUE_SWIGLU = 2 };
+/* B200_OUT_S32 stores the raw int32 accumulators (per-channel mode only, scales ignored);
+ * it exists so that callers can check the integer path bit for bit. */
+enum { B200_OUT_BF16 = 0, B200_OUT_F32 = 1, B200_OUT_S32 = 2 };
+/* B200_PATH_AUTO picks the tcgen05 tensor-core kernel whenever the shape and pointers
+ * meet its alignment rules and the plain CUDA-core kernel otherwise; the other two
+ * force one of them (B200_PATH_TCGEN05 fails when the rules are not met). */
+enum { B200_PATH_AUTO = 0, B200_PATH_TCGEN05 = 1, B200_PATH_SIMT = 2 };
+
+typedef struct b200_gemm_variant {
+  int32_t dtype;      /* B200_DTYPE_*      */
+  int32_t layout;     /* B200_LAYOUT_*     */
+  int32_t scale_mode; /* B200_SCALE_*      */
+  int32_t subchannel; /* 32/64/128/256 when scale_mode is SUBCHANNEL, else 0 */
+  int32_t epilogue;   /* B200_EPILOGUE_*   */
+  int32_t out_dtype;  /* B200_OUT_*        */
+  int32_t split_k;    /* 1, 2, 4 or 8; >1 requires epilogue NONE and out_dtype F32 */
+  int32_t path;       /* B200_PATH_*       */
+  int32_t group_m;    /* raster swizzle width in row tiles, 0 = library default */
+  int32_t reserved[7];
+} b200_gemm_variant;
+
+/* Replaces amd_strix_halo_kernels_dispatch_version (dispatch.cpp:206). */
+int b200_int4_gemms_dispatch_version(void);
+/* Replaces amd_strix_halo_kernels_has_compiled_code_objects (dispatch.cpp:208): 1 when the
+ * library was built with its sm_100a kernels. */
+int b200_int4_gemms_has_compiled_kernels(void);
+/* Replaces amd_strix_halo_kernels_has_hip_runtime (dispatch.cpp:212): 1 when a CUDA driver
+ * and at least one device are usable from this process. */
+int b200_int4_gemms_has_cuda_runtime(void);
+/* Replaces amd_strix_halo_kernels_has_linked_kernels (dispatch.cpp:216): both of the above
+ * and device 0 is compute capability 10.x. */
+int b200_int4_gemms_has_linked_kernels(void);
+/* Replaces amd_strix_halo_kernels_last_error (dispatch.cpp:220). */
+const char* b200_int4_gemms_last_error(void);
+
+/* Device-side status word of the most recent launches on a device: 0 = no kernel reported
+ * a problem, 1 = a bounded wait inside a kernel ran out (the kernel gave up and returned).
+ * Reading it does not synchronise; call it after synchronising the stream.  detail[0..2]
+ * (may be NULL) receive the block index and wait site.  No reference counterpart. */
+int b200_int4_gemms_device_status(int device_index, int32_t* detail);
+/* Clears the status word. */
+int b200_int4_gemms_reset_device_status(int device_index);
+
+/* Dense GEMM:  C = epilogue((A_q @ B_q) * a_scale * b_scale).
+ * Replaces amd_strix_halo_kernels_launch_hsaco (dispatch.cpp:224-283).
+ *   a, b       operands in variant->layout (see above); for SWIGLU, B has 2*n output columns
+ *              laid out [up | gate] and c has n columns.
+ *   a_scale    bf16 [m] (per-channel) or [m, ceil(k/S)] (subchannel)
+ *   b_scale    bf16 [cols] or [ceil(k/S), cols], cols = n (2*n for SWIGLU)
+ *   c          [m, n] in variant->out_dtype
+ *   workspace  device scratch of at least b200_int4_gemms_dense_workspace_bytes(...) bytes,
+ *              may be NULL when that is 0
+ *   m, n, k    logical sizes (k counts int4 values, not bytes) */
+int b200_int4_gemms_launch_dense(const b200_gemm_variant* variant, int device_index,
+                                 uintptr_t stream_handle, const void* a, const void* b,
+                                 const void* a_scale, const void* b_scale, void* c,
+                                 void* workspace, size_t workspace_bytes, int32_t m, int32_t n,
+                                 int32_t k);
+size_t b200_int4_gemms_dense_workspace_bytes(const b200_gemm_variant* variant, int32_t m,
+                                             int32_t n, int32_t k);
+
+/* Grouped forward (M-ragged):  out[rows of group g] = (lhs_rows @ rhs[g]) * a_scale * b_scale[g].
+ * Replaces amd_strix_halo_kernels_launch_ragged_fwd_hsaco (dispatch.cpp:286-389).
+ *   lhs        int4 [m, k_packed] (NN/NT) or [k_packed, m] (TN/TT)
+ *   rhs        int4 [groups, k_packed, n] (NN/TN) or [groups, n, k_packed] (NT/TT)
+ *   lhs_scale  bf16 [m] or [m, scale_cols];  rhs_scale bf16 [groups, n] or [groups, scale_cols, n]
+ *   task_*     int64 [num_tasks] row-block tasks as built by calculate_group_info
+ *              (reference ragged.py:201-323); block_rows = the tile they were built with (<= 128)
+ *   out        [m, n] bf16 or f32; rows outside every task's [actual_start, actual_end) are untouched */
+int b200_int4_gemms_launch_ragged_fwd(const b200_gemm_variant* variant, int device_index,
+                                      uintptr_t stream_handle, const void* lhs, const void* rhs,
+                                      const void* lhs_scale, const void* rhs_scale,
+                                      const int64_t* task_group_ids,
+                                      const int64_t* task_block_starts,
+                                      const int64_t* task_actual_starts,
+                                      const int64_t* task_actual_ends, void* out, int32_t m,
+                                      int32_t n, int32_t k_packed, int32_t scale_cols,
+                                      int32_t num_tasks, int32_t groups, int32_t block_rows);
+
+/* Grouped backward (K-ragged):  out[g] = (lhs[g][:, :k_g] @ rhs[g][:k_g, :]) * a_scale[g] * b_scale[g],
+ * k_g = group_sizes[g]; entries beyond k_g (padding, and the odd tail nibble) are ignored;
+ * an empty group produces zeros.
+ * Replaces amd_strix_halo_kernels_launch_ragged_bwd_hsaco (dispatch.cpp:391-456).
+ *   lhs        int4 [groups, m, k_packed] (NN/NT) or [groups, k_packed, m] (TN/TT)
+ *   rhs        int4 [groups, k_packed, n] (NN/TN) or [groups, n, k_packed] (NT/TT)
+ *   lhs_scale  bf16 [groups, m] or [groups, m, scale_cols]; rhs_scale [groups, n] or [groups, scale_cols, n]
+ *   group_sizes int64 [groups]
+ *   out        f32 [groups, m, n]
+ * Split-K is not needed for determinism here: every output tile is owned by one CTA, so
+ * results are bit-identical from run to run. */
+int b200_int4_gemms_launch_ragged_bwd(const b200_gemm_variant* variant, int device_index,
+                                      uintptr_t stream_handle, const void* lhs, const void* rhs,
+                                      const void* lhs_scale, const void* rhs_scale,
+                                      const int64_t* group_sizes, void* out, int32_t m, int32_t n,
+                                      int32_t k_packed, int32_t scale_cols, int32_t groups);
+
+/* Expands packed int4 [rows, cols_packed] to int8 [rows, 2*cols_packed] (values -8..7,
+ * even k from the low nibble).  The A/B comparison partner of the fused unpack path:
+ * expand once, then run the int8 GEMM.  No reference counterpart (the reference only
+ * unpacks on the host, quant.py:41-51). */
+int b200_int4_gemms_unpack_int4(int device_index, uintptr_t stream_handle, const void* packed,
+                                void* out_int8, int64_t rows, int64_t cols_packed);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* B200_INT4_GEMMS_H_ */

@@ -1,0 +1,603 @@
+// C ABI of libb200_int4_gemms.so (declared in include/b200_int4_gemms.h): argument checks,
+// TMA tensor-map construction, kernel selection and launch.  Plays the part of the
+// reference's native/src/dispatch.cpp, with the kernels linked in.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "../../include/b200_int4_gemms.h"
+#include "gemm_kernel.cuh"
+#include "simt_kernel.cuh"
+
+namespace {
+
+using namespace b200;
+
+thread_local std::string g_last_error;
+
+int fail(std::string msg) {
+  g_last_error = std::move(msg);
+  return 1;
+}
+
+int fail_cuda(const char* what, cudaError_t err) {
+  // clear the (non-sticky) error so that the next call starts clean
+  (void)cudaGetLastError();
+  return fail(std::string(what) + " failed: " + cudaGetErrorString(err));
+}
+
+// ---------------------------------------------------------------------------------------
+// driver entry point for tensor maps (no link-time dependency on libcuda)
+// ---------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+std::mutex g_init_mutex;
+EncodeTiledFn g_encode_tiled = nullptr;
+bool g_encode_attempted = false;
+
+EncodeTiledFn encode_tiled_fn() {
+  std::lock_guard<std::mutex> lock(g_init_mutex);
+  if (g_encode_attempted) return g_encode_tiled;
+  g_encode_attempted = true;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (err == cudaSuccess && qres == cudaDriverEntryPointSuccess && fn != nullptr) {
+    g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+  } else {
+    (void)cudaGetLastError();
+  }
+  return g_encode_tiled;
+}
+
+// 2-D byte tensor map: inner extent `inner_bytes` (pitch `pitch_bytes`), `rows` rows.
+int make_map_2d(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_t rows,
+                uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows, bool swizzle128,
+                const char* name) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return fail("cuTensorMapEncodeTiled is not available from this CUDA driver");
+  const cuuint64_t dims[2] = {inner_bytes, rows};
+  const cuuint64_t strides[1] = {pitch_bytes};
+  const cuuint32_t box[2] = {box_inner, box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                  elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    return fail(std::string("cuTensorMapEncodeTiled failed for ") + name + " (CUresult " +
+                std::to_string(static_cast<int>(r)) + ")");
+  }
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// per-device state: SM count, host-mapped status word, one-time kernel attribute set-up
+// ---------------------------------------------------------------------------------------
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+  bool ready = false;
+  int sm_count = 0;
+  int cc_major = 0;
+  int* status_host = nullptr;  // pinned + mapped
+  int* status_dev = nullptr;
+};
+DeviceState g_devices[kMaxDevices];
+std::mutex g_device_mutex;
+
+template <typename Kernel>
+cudaError_t set_smem(Kernel kernel, int bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+#define B200_FOR_EACH_TC_KERNEL(X)                                   \
+  /*  int4  A-MN  scale     epilogue    out       maskK */           \
+  X(true, false, SCALE_PC, EPI_NONE, OUT_BF16, false)                \
+  X(true, false, SCALE_PC, EPI_RELU2, OUT_BF16, false)               \
+  X(true, false, SCALE_PC, EPI_SWIGLU, OUT_BF16, false)              \
+  X(true, false, SCALE_PC, EPI_NONE, OUT_F32, false)                 \
+  X(true, false, SCALE_PC, EPI_NONE, OUT_S32, false)                 \
+  X(true, false, SCALE_SC, EPI_NONE, OUT_BF16, false)                \
+  X(true, false, SCALE_SC, EPI_RELU2, OUT_BF16, false)               \
+  X(true, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false)              \
+  X(true, false, SCALE_SC, EPI_NONE, OUT_F32, false)                 \
+  X(true, true, SCALE_PC, EPI_NONE, OUT_BF16, false)                 \
+  X(true, true, SCALE_PC, EPI_NONE, OUT_F32, false)                  \
+  X(true, true, SCALE_SC, EPI_NONE, OUT_BF16, false)                 \
+  X(true, false, SCALE_PC, EPI_NONE, OUT_F32, true)                  \
+  X(true, true, SCALE_PC, EPI_NONE, OUT_F32, true)                   \
+  X(true, false, SCALE_SC, EPI_NONE, OUT_F32, true)                  \
+  X(true, true, SCALE_SC, EPI_NONE, OUT_F32, true)                   \
+  X(false, false, SCALE_PC, EPI_NONE, OUT_BF16, false)               \
+  X(false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false)              \
+  X(false, false, SCALE_PC, EPI_SWIGLU, OUT_BF16, false)             \
+  X(false, false, SCALE_PC, EPI_NONE, OUT_F32, false)                \
+  X(false, false, SCALE_PC, EPI_NONE, OUT_S32, false)                \
+  X(false, false, SCALE_SC, EPI_NONE, OUT_BF16, false)               \
+  X(false, false, SCALE_SC, EPI_RELU2, OUT_BF16, false)              \
+  X(false, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false)
+
+int ensure_device(int device_index, DeviceState** out) {
+  if (device_index < 0 || device_index >= kMaxDevices) return fail("device_index out of range");
+  cudaError_t err = cudaSetDevice(device_index);
+  if (err != cudaSuccess) return fail_cuda("cudaSetDevice", err);
+  std::lock_guard<std::mutex> lock(g_device_mutex);
+  DeviceState& st = g_devices[device_index];
+  if (!st.ready) {
+    cudaDeviceProp prop;
+    err = cudaGetDeviceProperties(&prop, device_index);
+    if (err != cudaSuccess) return fail_cuda("cudaGetDeviceProperties", err);
+    st.sm_count = prop.multiProcessorCount;
+    st.cc_major = prop.major;
+    if (prop.major != 10) {
+      return fail("this library holds sm_100a kernels only; device " + std::to_string(device_index) +
+                  " is compute capability " + std::to_string(prop.major) + "." +
+                  std::to_string(prop.minor));
+    }
+    err = cudaHostAlloc(reinterpret_cast<void**>(&st.status_host), 4 * sizeof(int), cudaHostAllocMapped);
+    if (err != cudaSuccess) return fail_cuda("cudaHostAlloc(status)", err);
+    std::memset(st.status_host, 0, 4 * sizeof(int));
+    err = cudaHostGetDevicePointer(reinterpret_cast<void**>(&st.status_dev), st.status_host, 0);
+    if (err != cudaSuccess) return fail_cuda("cudaHostGetDevicePointer(status)", err);
+#define X(I4, AMN, SC, EP, OT, MK)                                                              \
+  err = set_smem(gemm_i8_tcgen05_kernel<I4, AMN, SC, EP, OT, MK>,                               \
+                 KernelTraits<I4, AMN, SC, EP, OT, MK>::kSmemBytes);                            \
+  if (err != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(max dynamic shared memory)", err);
+    B200_FOR_EACH_TC_KERNEL(X)
+#undef X
+    st.ready = true;
+  }
+  *out = &st;
+  return 0;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+struct TcLaunch {
+  bool int4, a_mn, mask_k;
+  int scale, epi, out;
+};
+
+int launch_tc(const TcLaunch& l, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+              int grid, cudaStream_t stream) {
+#define X(I4, AMN, SC, EP, OT, MK)                                                               \
+  if (l.int4 == I4 && l.a_mn == AMN && l.scale == SC && l.epi == EP && l.out == OT &&           \
+      l.mask_k == MK) {                                                                          \
+    using T = KernelTraits<I4, AMN, SC, EP, OT, MK>;                                             \
+    gemm_i8_tcgen05_kernel<I4, AMN, SC, EP, OT, MK>                                              \
+        <<<grid, T::kThreads, T::kSmemBytes, stream>>>(ta, tb, p);                               \
+    cudaError_t err = cudaGetLastError();                                                        \
+    if (err != cudaSuccess) return fail_cuda("tcgen05 GEMM kernel launch", err);                 \
+    return 0;                                                                                    \
+  }
+  B200_FOR_EACH_TC_KERNEL(X)
+#undef X
+  return -1;  // no such instantiation
+}
+
+bool tc_has(const TcLaunch& l) {
+#define X(I4, AMN, SC, EP, OT, MK)                                                               \
+  if (l.int4 == I4 && l.a_mn == AMN && l.scale == SC && l.epi == EP && l.out == OT &&           \
+      l.mask_k == MK)                                                                            \
+    return true;
+  B200_FOR_EACH_TC_KERNEL(X)
+#undef X
+  return false;
+}
+
+int check_variant(const b200_gemm_variant* v) {
+  if (v == nullptr) return fail("variant must be non-null");
+  if (v->dtype != B200_DTYPE_INT4 && v->dtype != B200_DTYPE_INT8) return fail("variant.dtype is not INT4 or INT8");
+  if (v->layout < B200_LAYOUT_NN || v->layout > B200_LAYOUT_TT) return fail("variant.layout is not NN, NT, TN or TT");
+  if (v->scale_mode == B200_SCALE_SUBCHANNEL) {
+    if (v->subchannel != 32 && v->subchannel != 64 && v->subchannel != 128 && v->subchannel != 256)
+      return fail("variant.subchannel must be 32, 64, 128 or 256");
+  } else if (v->scale_mode != B200_SCALE_PER_CHANNEL) {
+    return fail("variant.scale_mode is not PER_CHANNEL or SUBCHANNEL");
+  }
+  if (v->epilogue < B200_EPILOGUE_NONE || v->epilogue > B200_EPILOGUE_SWIGLU) return fail("variant.epilogue is unknown");
+  if (v->out_dtype < B200_OUT_BF16 || v->out_dtype > B200_OUT_S32) return fail("variant.out_dtype is unknown");
+  if (v->out_dtype == B200_OUT_S32 && (v->scale_mode != B200_SCALE_PER_CHANNEL || v->epilogue != B200_EPILOGUE_NONE))
+    return fail("out_dtype S32 (raw accumulators) needs per-channel mode and no epilogue");
+  if (v->split_k != 1 && v->split_k != 2 && v->split_k != 4 && v->split_k != 8) return fail("variant.split_k must be 1, 2, 4 or 8");
+  if (v->split_k > 1 && (v->epilogue != B200_EPILOGUE_NONE || v->out_dtype != B200_OUT_F32))
+    return fail("split_k > 1 needs epilogue NONE and float32 output");
+  if (v->path < B200_PATH_AUTO || v->path > B200_PATH_SIMT) return fail("variant.path is unknown");
+  return 0;
+}
+
+int launch_simt(const SimtParams& sp, int rows_per_z, int z, cudaStream_t stream) {
+  if (sp.N <= 0 || rows_per_z <= 0 || z <= 0) return 0;
+  dim3 grid((sp.N + 63) / 64, (rows_per_z + 3) / 4, z);
+  if (grid.y > 65535 || grid.z > 65535) return fail("problem too large for the CUDA-core kernel's grid");
+  gemm_simt_kernel<<<grid, 256, 0, stream>>>(sp);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda("CUDA-core GEMM kernel launch", err);
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int b200_int4_gemms_dispatch_version(void) { return 1; }
+
+extern "C" int b200_int4_gemms_has_compiled_kernels(void) { return 1; }
+
+extern "C" int b200_int4_gemms_has_cuda_runtime(void) {
+  int count = 0;
+  cudaError_t err = cudaGetDeviceCount(&count);
+  if (err != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return count > 0 ? 1 : 0;
+}
+
+extern "C" int b200_int4_gemms_has_linked_kernels(void) {
+  if (!b200_int4_gemms_has_cuda_runtime()) return 0;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, 0) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return prop.major == 10 ? 1 : 0;
+}
+
+extern "C" const char* b200_int4_gemms_last_error(void) { return g_last_error.c_str(); }
+
+extern "C" int b200_int4_gemms_device_status(int device_index, int32_t* detail) {
+  if (device_index < 0 || device_index >= kMaxDevices) return 0;
+  DeviceState& st = g_devices[device_index];
+  if (!st.ready || st.status_host == nullptr) return 0;
+  volatile int* s = st.status_host;
+  if (detail != nullptr) {
+    detail[0] = s[1];
+    detail[1] = s[2];
+    detail[2] = s[3];
+  }
+  return s[0];
+}
+
+extern "C" int b200_int4_gemms_reset_device_status(int device_index) {
+  if (device_index < 0 || device_index >= kMaxDevices) return 1;
+  DeviceState& st = g_devices[device_index];
+  if (st.ready && st.status_host != nullptr) std::memset(st.status_host, 0, 4 * sizeof(int));
+  return 0;
+}
+
+extern "C" size_t b200_int4_gemms_dense_workspace_bytes(const b200_gemm_variant* variant, int32_t m,
+                                                        int32_t n, int32_t k) {
+  (void)variant;
+  (void)m;
+  (void)n;
+  (void)k;
+  return 0;  // every output tile is reduced by one CTA; no split-K scratch is needed
+}
+
+extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int device_index,
+                                            uintptr_t stream_handle, const void* a, const void* b,
+                                            const void* a_scale, const void* b_scale, void* c,
+                                            void* workspace, size_t workspace_bytes, int32_t m,
+                                            int32_t n, int32_t k) {
+  g_last_error.clear();
+  (void)workspace;
+  (void)workspace_bytes;
+  if (int rc = check_variant(v); rc != 0) return rc;
+  if (a == nullptr || b == nullptr || c == nullptr) return fail("a, b and c pointers must be non-null");
+  if (v->out_dtype != B200_OUT_S32 && (a_scale == nullptr || b_scale == nullptr))
+    return fail("a_scale and b_scale pointers must be non-null");
+  if (m <= 0 || n <= 0 || k <= 0) return fail("m, n and k must be positive");
+  const bool int4 = v->dtype == B200_DTYPE_INT4;
+  if (int4 && k >= 131072) return fail("int4 path supports k < 131072 (accumulator headroom of the 16x operand encoding)");
+  DeviceState* dev = nullptr;
+  if (int rc = ensure_device(device_index, &dev); rc != 0) return rc;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_handle);
+
+  const bool swiglu = v->epilogue == B200_EPILOGUE_SWIGLU;
+  const int b_cols = swiglu ? 2 * n : n;
+  const int kb = int4 ? (k + 1) / 2 : k;
+  const bool a_t = (v->layout == B200_LAYOUT_TN || v->layout == B200_LAYOUT_TT);
+  const bool b_t = (v->layout == B200_LAYOUT_NT || v->layout == B200_LAYOUT_TT);
+  const int sc_mode = (v->scale_mode == B200_SCALE_SUBCHANNEL) ? SCALE_SC : SCALE_PC;
+  const int scale_cols = sc_mode == SCALE_SC ? (k + v->subchannel - 1) / v->subchannel : 1;
+
+  TcLaunch tl{int4, a_t, false, sc_mode, v->epilogue, v->out_dtype};
+  bool tc_ok = !b_t && tc_has(tl) && aligned16(a) && aligned16(b);
+  // TMA needs 16-byte pitches; vector stores need an aligned output pitch.
+  tc_ok = tc_ok && ((a_t ? m : kb) % 16 == 0) && (b_cols % 16 == 0);
+  if (v->path == B200_PATH_SIMT) tc_ok = false;
+  if (v->path == B200_PATH_TCGEN05 && !tc_ok)
+    return fail("the tcgen05 kernel needs B stored [K, N], 16-byte aligned operands and operand pitches that are multiples of 16 bytes");
+
+  if (!tc_ok) {
+    SimtParams sp{};
+    sp.mode = MODE_DENSE;
+    sp.int4 = int4;
+    sp.a_transposed = a_t;
+    sp.b_transposed = b_t;
+    sp.scale_mode = sc_mode;
+    sp.subchannel = v->subchannel;
+    sp.scale_cols = scale_cols;
+    sp.epilogue = v->epilogue;
+    sp.out_dtype = v->out_dtype;
+    sp.M = m;
+    sp.N = n;
+    sp.K = k;
+    sp.b_cols = b_cols;
+    sp.kb = kb;
+    sp.a = static_cast<const uint8_t*>(a);
+    sp.b = static_cast<const uint8_t*>(b);
+    sp.a_scale = static_cast<const __nv_bfloat16*>(a_scale);
+    sp.b_scale = static_cast<const __nv_bfloat16*>(b_scale);
+    sp.out = c;
+    return launch_simt(sp, m, 1, stream);
+  }
+
+  CUtensorMap ta, tb;
+  if (int4) {
+    if (a_t) {
+      if (int rc = make_map_2d(&ta, a, m, kb, m, NBLK, BK / 2, false, "A"); rc != 0) return rc;
+    } else {
+      if (int rc = make_map_2d(&ta, a, kb, m, kb, BK / 2, BM, false, "A"); rc != 0) return rc;
+    }
+    if (int rc = make_map_2d(&tb, b, b_cols, kb, b_cols, NBLK, BK / 2, false, "B"); rc != 0) return rc;
+  } else {
+    if (a_t) {
+      if (int rc = make_map_2d(&ta, a, m, kb, m, NBLK, BK, true, "A"); rc != 0) return rc;
+    } else {
+      if (int rc = make_map_2d(&ta, a, kb, m, kb, BK, BM, true, "A"); rc != 0) return rc;
+    }
+    if (int rc = make_map_2d(&tb, b, b_cols, kb, b_cols, NBLK, BK, true, "B"); rc != 0) return rc;
+  }
+
+  GemmParams p{};
+  p.mode = MODE_DENSE;
+  p.M = m;
+  p.N = n;
+  p.K = k;
+  p.tile_cols = swiglu ? NBLK : BN;
+  p.tiles_m = (m + BM - 1) / BM;
+  p.tiles_n = (n + p.tile_cols - 1) / p.tile_cols;
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.group_m = v->group_m > 0 ? v->group_m : 8;
+  p.gate_col_offset = swiglu ? n : NBLK;
+  p.ldc = n;
+  p.subchannel = sc_mode == SCALE_SC ? v->subchannel : 0;
+  p.scale_cols = scale_cols;
+  p.lds_b = b_cols;
+  p.a_scale = static_cast<const __nv_bfloat16*>(a_scale);
+  p.b_scale = static_cast<const __nv_bfloat16*>(b_scale);
+  p.out = c;
+  p.status = dev->status_dev;
+  const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
+  int rc = launch_tc(tl, ta, tb, p, grid, stream);
+  if (rc < 0) return fail("internal: no tcgen05 instantiation for this variant");
+  return rc;
+}
+
+extern "C" int b200_int4_gemms_launch_ragged_fwd(
+    const b200_gemm_variant* v, int device_index, uintptr_t stream_handle, const void* lhs,
+    const void* rhs, const void* lhs_scale, const void* rhs_scale, const int64_t* task_group_ids,
+    const int64_t* task_block_starts, const int64_t* task_actual_starts,
+    const int64_t* task_actual_ends, void* out, int32_t m, int32_t n, int32_t k_packed,
+    int32_t scale_cols, int32_t num_tasks, int32_t groups, int32_t block_rows) {
+  g_last_error.clear();
+  if (int rc = check_variant(v); rc != 0) return rc;
+  if (v->dtype != B200_DTYPE_INT4) return fail("ragged kernels take packed int4 operands");
+  if (v->epilogue != B200_EPILOGUE_NONE) return fail("ragged kernels have no fused activation");
+  if (v->out_dtype == B200_OUT_S32) return fail("ragged kernels store bf16 or float32");
+  if (lhs == nullptr || rhs == nullptr || lhs_scale == nullptr || rhs_scale == nullptr ||
+      task_group_ids == nullptr || task_block_starts == nullptr || task_actual_starts == nullptr ||
+      task_actual_ends == nullptr || out == nullptr)
+    return fail("ragged forward kernel pointers must be non-null");
+  if (m <= 0 || n <= 0 || k_packed <= 0 || groups <= 0) return fail("m, n, k_packed and groups must be positive");
+  if (num_tasks < 0) return fail("num_tasks must be non-negative");
+  if (block_rows <= 0 || block_rows > BM) return fail("block_rows must be in [1, 128]");
+  if (k_packed >= 65536) return fail("int4 path supports k < 131072");
+  if (num_tasks == 0) return 0;
+  DeviceState* dev = nullptr;
+  if (int rc = ensure_device(device_index, &dev); rc != 0) return rc;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_handle);
+
+  const bool a_t = (v->layout == B200_LAYOUT_TN || v->layout == B200_LAYOUT_TT);
+  const bool b_t = (v->layout == B200_LAYOUT_NT || v->layout == B200_LAYOUT_TT);
+  const int sc_mode = (v->scale_mode == B200_SCALE_SUBCHANNEL) ? SCALE_SC : SCALE_PC;
+  const int k = 2 * k_packed;
+  if (sc_mode == SCALE_SC && scale_cols != (k + v->subchannel - 1) / v->subchannel)
+    return fail("scale_cols does not match ceil(K / subchannel)");
+
+  TcLaunch tl{true, a_t, false, sc_mode, EPI_NONE, v->out_dtype};
+  bool tc_ok = !b_t && !a_t && tc_has(tl) && aligned16(lhs) && aligned16(rhs) && (k_packed % 16 == 0) && (n % 16 == 0);
+  if (v->path == B200_PATH_SIMT) tc_ok = false;
+  if (v->path == B200_PATH_TCGEN05 && !tc_ok)
+    return fail("the tcgen05 ragged forward kernel needs layout NN, 16-byte aligned operands and k_packed, n multiples of 16");
+
+  if (!tc_ok) {
+    SimtParams sp{};
+    sp.mode = MODE_RAGGED_FWD;
+    sp.int4 = 1;
+    sp.a_transposed = a_t;
+    sp.b_transposed = b_t;
+    sp.scale_mode = sc_mode;
+    sp.subchannel = v->subchannel;
+    sp.scale_cols = sc_mode == SCALE_SC ? scale_cols : 1;
+    sp.epilogue = EPI_NONE;
+    sp.out_dtype = v->out_dtype;
+    sp.M = m;
+    sp.N = n;
+    sp.K = k;
+    sp.b_cols = n;
+    sp.kb = k_packed;
+    sp.num_groups = groups;
+    sp.num_tasks = num_tasks;
+    sp.a = static_cast<const uint8_t*>(lhs);
+    sp.b = static_cast<const uint8_t*>(rhs);
+    sp.a_scale = static_cast<const __nv_bfloat16*>(lhs_scale);
+    sp.b_scale = static_cast<const __nv_bfloat16*>(rhs_scale);
+    sp.task_group_ids = reinterpret_cast<const long long*>(task_group_ids);
+    sp.task_actual_starts = reinterpret_cast<const long long*>(task_actual_starts);
+    sp.task_actual_ends = reinterpret_cast<const long long*>(task_actual_ends);
+    sp.out = out;
+    return launch_simt(sp, block_rows, num_tasks, stream);
+  }
+
+  CUtensorMap ta, tb;
+  if (int rc = make_map_2d(&ta, lhs, k_packed, m, k_packed, BK / 2, BM, false, "lhs"); rc != 0) return rc;
+  if (int rc = make_map_2d(&tb, rhs, n, static_cast<uint64_t>(groups) * k_packed, n, NBLK, BK / 2, false, "rhs"); rc != 0)
+    return rc;
+  GemmParams p{};
+  p.mode = MODE_RAGGED_FWD;
+  p.M = m;
+  p.N = n;
+  p.K = k;
+  p.tile_cols = BN;
+  p.tiles_m = num_tasks;
+  p.tiles_n = (n + BN - 1) / BN;
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.group_m = 1;
+  p.gate_col_offset = NBLK;
+  p.ldc = n;
+  p.subchannel = sc_mode == SCALE_SC ? v->subchannel : 0;
+  p.scale_cols = sc_mode == SCALE_SC ? scale_cols : 1;
+  p.lds_b = n;
+  p.num_groups = groups;
+  p.rows_per_group_b = k_packed;
+  p.task_group_ids = reinterpret_cast<const long long*>(task_group_ids);
+  p.task_block_starts = reinterpret_cast<const long long*>(task_block_starts);
+  p.task_actual_starts = reinterpret_cast<const long long*>(task_actual_starts);
+  p.task_actual_ends = reinterpret_cast<const long long*>(task_actual_ends);
+  p.a_scale = static_cast<const __nv_bfloat16*>(lhs_scale);
+  p.b_scale = static_cast<const __nv_bfloat16*>(rhs_scale);
+  p.out = out;
+  p.status = dev->status_dev;
+  const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
+  int rc = launch_tc(tl, ta, tb, p, grid, stream);
+  if (rc < 0) return fail("internal: no tcgen05 instantiation for this variant");
+  return rc;
+}
+
+extern "C" int b200_int4_gemms_launch_ragged_bwd(const b200_gemm_variant* v, int device_index,
+                                                 uintptr_t stream_handle, const void* lhs,
+                                                 const void* rhs, const void* lhs_scale,
+                                                 const void* rhs_scale, const int64_t* group_sizes,
+                                                 void* out, int32_t m, int32_t n, int32_t k_packed,
+                                                 int32_t scale_cols, int32_t groups) {
+  g_last_error.clear();
+  if (int rc = check_variant(v); rc != 0) return rc;
+  if (v->dtype != B200_DTYPE_INT4) return fail("ragged kernels take packed int4 operands");
+  if (v->epilogue != B200_EPILOGUE_NONE) return fail("ragged kernels have no fused activation");
+  if (v->out_dtype != B200_OUT_F32) return fail("ragged backward stores float32");
+  if (lhs == nullptr || rhs == nullptr || lhs_scale == nullptr || rhs_scale == nullptr ||
+      group_sizes == nullptr || out == nullptr)
+    return fail("ragged backward kernel pointers must be non-null");
+  if (m <= 0 || n <= 0 || k_packed <= 0 || groups <= 0) return fail("m, n, k_packed and groups must be positive");
+  if (k_packed >= 65536) return fail("int4 path supports k < 131072");
+  DeviceState* dev = nullptr;
+  if (int rc = ensure_device(device_index, &dev); rc != 0) return rc;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_handle);
+
+  const bool a_t = (v->layout == B200_LAYOUT_TN || v->layout == B200_LAYOUT_TT);
+  const bool b_t = (v->layout == B200_LAYOUT_NT || v->layout == B200_LAYOUT_TT);
+  const int sc_mode = (v->scale_mode == B200_SCALE_SUBCHANNEL) ? SCALE_SC : SCALE_PC;
+  const int k = 2 * k_packed;
+  if (sc_mode == SCALE_SC && scale_cols != (k + v->subchannel - 1) / v->subchannel)
+    return fail("scale_cols does not match ceil(K / subchannel)");
+
+  TcLaunch tl{true, a_t, true, sc_mode, EPI_NONE, OUT_F32};
+  bool tc_ok = !b_t && tc_has(tl) && aligned16(lhs) && aligned16(rhs) && ((a_t ? m : k_packed) % 16 == 0) && (n % 16 == 0);
+  if (v->path == B200_PATH_SIMT) tc_ok = false;
+  if (v->path == B200_PATH_TCGEN05 && !tc_ok)
+    return fail("the tcgen05 ragged backward kernel needs rhs stored [G, K, N], 16-byte aligned operands and operand pitches that are multiples of 16 bytes");
+
+  if (!tc_ok) {
+    SimtParams sp{};
+    sp.mode = MODE_RAGGED_BWD;
+    sp.int4 = 1;
+    sp.a_transposed = a_t;
+    sp.b_transposed = b_t;
+    sp.scale_mode = sc_mode;
+    sp.subchannel = v->subchannel;
+    sp.scale_cols = sc_mode == SCALE_SC ? scale_cols : 1;
+    sp.epilogue = EPI_NONE;
+    sp.out_dtype = OUT_F32;
+    sp.M = m;
+    sp.N = n;
+    sp.K = k;
+    sp.b_cols = n;
+    sp.kb = k_packed;
+    sp.num_groups = groups;
+    sp.a = static_cast<const uint8_t*>(lhs);
+    sp.b = static_cast<const uint8_t*>(rhs);
+    sp.a_scale = static_cast<const __nv_bfloat16*>(lhs_scale);
+    sp.b_scale = static_cast<const __nv_bfloat16*>(rhs_scale);
+    sp.group_sizes = reinterpret_cast<const long long*>(group_sizes);
+    sp.out = out;
+    return launch_simt(sp, m, groups, stream);
+  }
+
+  CUtensorMap ta, tb;
+  if (a_t) {
+    if (int rc = make_map_2d(&ta, lhs, m, static_cast<uint64_t>(groups) * k_packed, m, NBLK, BK / 2, false, "lhs"); rc != 0)
+      return rc;
+  } else {
+    if (int rc = make_map_2d(&ta, lhs, k_packed, static_cast<uint64_t>(groups) * m, k_packed, BK / 2, BM, false, "lhs"); rc != 0)
+      return rc;
+  }
+  if (int rc = make_map_2d(&tb, rhs, n, static_cast<uint64_t>(groups) * k_packed, n, NBLK, BK / 2, false, "rhs"); rc != 0)
+    return rc;
+  GemmParams p{};
+  p.mode = MODE_RAGGED_BWD;
+  p.M = m;
+  p.N = n;
+  p.K = k;
+  p.tile_cols = BN;
+  p.tiles_m = (m + BM - 1) / BM;
+  p.tiles_n = (n + BN - 1) / BN;
+  p.num_tiles = groups * p.tiles_m * p.tiles_n;
+  p.group_m = 1;
+  p.gate_col_offset = NBLK;
+  p.ldc = n;
+  p.subchannel = sc_mode == SCALE_SC ? v->subchannel : 0;
+  p.scale_cols = sc_mode == SCALE_SC ? scale_cols : 1;
+  p.lds_b = n;
+  p.num_groups = groups;
+  p.rows_per_group_a = a_t ? k_packed : m;
+  p.rows_per_group_b = k_packed;
+  p.group_sizes = reinterpret_cast<const long long*>(group_sizes);
+  p.a_scale = static_cast<const __nv_bfloat16*>(lhs_scale);
+  p.b_scale = static_cast<const __nv_bfloat16*>(rhs_scale);
+  p.out = out;
+  p.status = dev->status_dev;
+  const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
+  int rc = launch_tc(tl, ta, tb, p, grid, stream);
+  if (rc < 0) return fail("internal: no tcgen05 instantiation for this variant");
+  return rc;
+}
+
+extern "C" int b200_int4_gemms_unpack_int4(int device_index, uintptr_t stream_handle,
+                                           const void* packed, void* out_int8, int64_t rows,
+                                           int64_t cols_packed) {
+  g_last_error.clear();
+  if (packed == nullptr || out_int8 == nullptr) return fail("packed and out_int8 pointers must be non-null");
+  if (rows < 0 || cols_packed < 0) return fail("rows and cols_packed must be non-negative");
+  if (!aligned16(packed) || !aligned16(out_int8)) return fail("packed and out_int8 must be 16-byte aligned");
+  DeviceState* dev = nullptr;
+  if (int rc = ensure_device(device_index, &dev); rc != 0) return rc;
+  const long long total = rows * cols_packed;
+  if (total == 0) return 0;
+  long long blocks = (total / 16 + 255) / 256;
+  const long long cap = static_cast<long long>(dev->sm_count) * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  unpack_int4_kernel<<<static_cast<unsigned>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream_handle)>>>(
+      static_cast<const uint8_t*>(packed), static_cast<int8_t*>(out_int8), total);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda("unpack kernel launch", err);
+  return 0;
+}

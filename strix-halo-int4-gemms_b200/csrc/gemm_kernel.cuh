@@ -1,0 +1,669 @@
+// Persistent, warp-specialised integer GEMM for sm_100a.
+//
+//   C[M,N] = epilogue( sum over K-groups( s32( A_q @ B_q ) * sA * sB ) )
+//
+// One CTA per SM walks a list of 128 x 256 output tiles.  Roles (warps):
+//   warp 0        TMA producer: brings packed-int4 (or int8) operand tiles into shared memory
+//   warp 1        MMA issuer: one thread issues tcgen05.mma kind::i8 (s8 x s8 -> s32 in TMEM)
+//   warps 2..     epilogue: tcgen05.ld the accumulator, scale in fp32, activation, store
+//   last 4 warps  (int4 only) unpack: expand nibbles to int8 into the swizzled UMMA tiles
+//
+// int4 operands.  Blackwell tensor cores have no int4 MMA, so each nibble v becomes the
+// int8 value 16*v (the nibble moved to the top of its byte, no sign-extension arithmetic).
+// The s32 accumulator then holds 256 * sum(a*b), exactly, and the epilogue shifts it right
+// by 8 (arithmetic, exact) before converting to fp32.  |sum| <= 64*K, so this is safe for
+// K < 131072, which the host side checks.
+//
+// K order inside a 128-wide K block.  A dot product does not care about the order of its
+// terms as long as A and B use the same order.  Packed byte p of a block (p = 0..63) holds
+// k = 2p (low nibble) and k = 2p+1 (high nibble).  Its low nibble goes to K slot
+// 32*(p/16) + p%16 and its high nibble to that slot + 16, for both operands.  A 16-byte
+// load of packed data therefore produces two whole 16-byte chunks of int8, and each K=32
+// MMA step still covers one contiguous range of 32 original k indices (so K-groups of
+// 32/64/128/256 keep their boundaries).
+//
+// Shared-memory tiles use the 128-byte-swizzle UMMA canonical layouts:
+//   A, K-major  : [128 rows][128 B of K], 16-byte chunk c of row r stored at chunk c ^ (r & 7)
+//   A/B MN-major: per 128-wide M/N block [128 K rows][128 B of M/N], chunk c of K row s at c ^ (s & 7)
+// int8 operands are written there directly by TMA (SWIZZLE_128B), int4 by the unpack warps.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cstdint>
+
+#include "ptx.cuh"
+
+namespace b200 {
+
+enum : int { MODE_DENSE = 0, MODE_RAGGED_FWD = 1, MODE_RAGGED_BWD = 2 };
+enum : int { SCALE_PC = 0, SCALE_SC = 1 };
+enum : int { EPI_NONE = 0, EPI_RELU2 = 1, EPI_SWIGLU = 2 };
+enum : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_S32 = 2 };
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 128;   // logical K per pipeline stage
+constexpr int NBLK = 128; // width of one M/N block of an MN-major operand (bytes == elements)
+constexpr int TMEM_COLS = 512;
+
+struct GemmParams {
+  int mode;
+  int M, N, K;           // logical problem: rows, output columns (SwiGLU: D), reduction length
+  int tiles_m, tiles_n;  // dense / ragged-bwd tile grid (per group for bwd)
+  int num_tiles;
+  int group_m;           // raster swizzle width (dense)
+  int tile_cols;         // output columns per tile: 256, or 128 for SwiGLU (up + gate blocks)
+  int gate_col_offset;   // column distance from the first to the second 128-wide B block:
+                         // 128 normally, D (the gate half) for SwiGLU
+  int ldc;               // output row pitch in elements
+  int subchannel;        // K-group length for subchannel scales (0 = per-channel)
+  int scale_cols;        // number of K-groups (subchannel) per row
+  int lds_b;             // pitch (elements) of one b_scale K-group row
+  // ragged
+  int num_groups;
+  int rows_per_group_a;  // rows of the stacked A map per group (bwd)
+  int rows_per_group_b;  // rows of the stacked B map per group (packed K rows for int4)
+  const long long* task_group_ids;
+  const long long* task_block_starts;
+  const long long* task_actual_starts;
+  const long long* task_actual_ends;
+  const long long* group_sizes;  // bwd: valid K per group
+  const __nv_bfloat16* a_scale;
+  const __nv_bfloat16* b_scale;
+  void* out;
+  int* status;  // host-mapped int[4] or nullptr
+};
+
+struct TileWork {
+  int a_x, a_y;      // TMA coordinates of the first A box of the tile (K block 0)
+  int b_y;           // TMA row coordinate of the first B box
+  int n0, n1;        // column origins of the two 128-wide B blocks
+  int num_kb;        // K blocks to run
+  int k_len;         // reduction length of this tile (bwd: group_sizes[g])
+  int k_valid;       // number of valid k (masking, bwd); INT_MAX otherwise
+  int out_row0;      // output row of tile row 0
+  int row_lo, row_hi;// valid output rows [lo, hi)
+  long long out_off; // element offset added to out (bwd: g*M*N)
+  long long sa_off;  // element offset of this tile's a_scale base
+  long long sb_off;  // element offset of this tile's b_scale base
+};
+
+template <bool kAMn>
+__device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t) {
+  TileWork w;
+  w.k_valid = 0x7FFFFFFF;
+  w.out_off = 0;
+  w.sa_off = 0;
+  w.sb_off = 0;
+  if (p.mode == MODE_DENSE) {
+    // grouped raster: walk group_m row-tiles down before moving to the next column tile
+    const int per_group = p.group_m * p.tiles_n;
+    const int grp = t / per_group;
+    const int first_m = grp * p.group_m;
+    const int rows_here = min(p.tiles_m - first_m, p.group_m);
+    const int local = t - grp * per_group;
+    const int mt = first_m + local % rows_here;
+    const int nt = local / rows_here;
+    w.a_x = kAMn ? mt * BM : 0;
+    w.a_y = kAMn ? 0 : mt * BM;
+    w.b_y = 0;
+    w.n0 = nt * p.tile_cols;
+    w.n1 = w.n0 + p.gate_col_offset;
+    w.k_len = p.K;
+    w.num_kb = (p.K + BK - 1) / BK;
+    w.out_row0 = mt * BM;
+    w.row_lo = w.out_row0;
+    w.row_hi = min(p.M, w.out_row0 + BM);
+  } else if (p.mode == MODE_RAGGED_FWD) {
+    const int task = t / p.tiles_n;
+    const int nt = t - task * p.tiles_n;
+    const int g = static_cast<int>(p.task_group_ids[task]);
+    const int bs = static_cast<int>(p.task_block_starts[task]);
+    w.a_x = 0;
+    w.a_y = bs;
+    w.b_y = g * p.rows_per_group_b;
+    w.n0 = nt * BN;
+    w.n1 = w.n0 + NBLK;
+    w.k_len = p.K;
+    w.num_kb = (p.K + BK - 1) / BK;
+    w.out_row0 = bs;
+    w.row_lo = static_cast<int>(p.task_actual_starts[task]);
+    w.row_hi = static_cast<int>(p.task_actual_ends[task]);
+    w.sb_off = static_cast<long long>(g) * p.lds_b * (p.subchannel ? p.scale_cols : 1);
+  } else {
+    const int per_g = p.tiles_m * p.tiles_n;
+    const int g = t / per_g;
+    const int local = t - g * per_g;
+    const int mt = local / p.tiles_n;
+    const int nt = local - mt * p.tiles_n;
+    const int kg = static_cast<int>(p.group_sizes[g]);
+    w.a_x = kAMn ? mt * BM : 0;
+    w.a_y = kAMn ? g * p.rows_per_group_a : g * p.rows_per_group_a + mt * BM;
+    w.b_y = g * p.rows_per_group_b;
+    w.n0 = nt * BN;
+    w.n1 = w.n0 + NBLK;
+    w.k_valid = kg;
+    w.k_len = kg;
+    w.num_kb = (kg + BK - 1) / BK;
+    w.out_row0 = mt * BM;
+    w.row_lo = w.out_row0;
+    w.row_hi = min(p.M, w.out_row0 + BM);
+    w.out_off = static_cast<long long>(g) * p.M * p.ldc;
+    w.sa_off = static_cast<long long>(g) * p.M * (p.subchannel ? p.scale_cols : 1);
+    w.sb_off = static_cast<long long>(g) * p.lds_b * (p.subchannel ? p.scale_cols : 1);
+  }
+  return w;
+}
+
+// Expand four packed bytes (8 nibbles) into two words of int8 = 16 * nibble value.
+__device__ __forceinline__ void expand_word(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  lo = (w << 4) & 0xF0F0F0F0u;
+  hi = w & 0xF0F0F0F0u;
+}
+
+template <bool kInt4, bool kAMn, int kScale, int kEpi, int kOut, bool kMaskK>
+struct KernelTraits {
+  static constexpr int kUnpackWarps = kInt4 ? 4 : 0;
+  static constexpr int kEpiWarps = (kScale == SCALE_SC) ? 8 : 4;
+  static constexpr int kThreads = (2 + kEpiWarps + kUnpackWarps) * 32;
+  static constexpr int kStages = kInt4 ? 3 : 4;   // int8 UMMA stages
+  static constexpr int kPkStages = kInt4 ? 3 : 0; // packed staging stages
+  static constexpr int kA8Bytes = BM * BK;        // 16 KB
+  static constexpr int kB8Bytes = BN * BK;        // 32 KB
+  static constexpr int kStageBytes = kA8Bytes + kB8Bytes;
+  static constexpr int kPkABytes = BM * BK / 2;   // 8 KB
+  static constexpr int kPkBBytes = BN * BK / 2;   // 16 KB
+  static constexpr int kPkStageBytes = kPkABytes + kPkBBytes;
+  static constexpr int kBarBytes = 256;
+  static constexpr int kSmemBytes =
+      1024 + kStages * kStageBytes + kPkStages * kPkStageBytes + kBarBytes;
+};
+
+template <bool kInt4, bool kAMn, int kScale, int kEpi, int kOut, bool kMaskK>
+__global__ void __launch_bounds__(KernelTraits<kInt4, kAMn, kScale, kEpi, kOut, kMaskK>::kThreads, 1)
+gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                       const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  using T = KernelTraits<kInt4, kAMn, kScale, kEpi, kOut, kMaskK>;
+  constexpr int S = T::kStages;
+  constexpr int PS = T::kPkStages;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  // layout: [S x (A8 | B8)] [PS x (pkA | pkB)] [barriers]
+  const uint32_t stage_base = smem_base;
+  const uint32_t pk_base = stage_base + S * T::kStageBytes;
+  const uint32_t bar_base = pk_base + PS * T::kPkStageBytes;
+  uint8_t* bar_gen = smem_gen + S * T::kStageBytes + PS * T::kPkStageBytes;
+
+  // barrier slots (8 bytes each)
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (4 + s); };
+  auto pk_full_bar = [&](int s) { return bar_base + 8u * (8 + s); };
+  auto pk_empty_bar = [&](int s) { return bar_base + 8u * (12 + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (16 + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (18 + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * 20);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 8 * 20 + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  AbortCtx ctx{abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full_bar(s), kInt4 ? T::kUnpackWarps : 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < PS; ++s) {
+      mbar_init(pk_full_bar(s), 1);
+      mbar_init(pk_empty_bar(s), T::kUnpackWarps);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full_bar(b), 1);
+      mbar_init(acc_empty_bar(b), T::kEpiWarps);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // K-groups: number of K=32 MMA steps between accumulator hand-overs to the epilogue.
+  // Per-channel: the whole tile is one group.
+  const int mma_per_group = (kScale == SCALE_SC) ? (p.subchannel / 32) : 0x7FFFFFFF;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+        const TileWork w = decode_tile<kAMn>(p, t);
+        for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
+          if constexpr (kInt4) {
+            const int s = it % PS;
+            const uint32_t ph = (it / PS) & 1;
+            if (!mbar_wait(pk_empty_bar(s), ph ^ 1u, ctx, 10)) { ok = false; break; }
+            const uint32_t dst = pk_base + s * T::kPkStageBytes;
+            mbar_arrive_expect_tx(pk_full_bar(s), T::kPkStageBytes);
+            if constexpr (kAMn) {
+              tma_load_2d(dst, &tmap_a, w.a_x, w.a_y + kb * (BK / 2), pk_full_bar(s));
+            } else {
+              tma_load_2d(dst, &tmap_a, w.a_x + kb * (BK / 2), w.a_y, pk_full_bar(s));
+            }
+            tma_load_2d(dst + T::kPkABytes, &tmap_b, w.n0, w.b_y + kb * (BK / 2), pk_full_bar(s));
+            tma_load_2d(dst + T::kPkABytes + T::kPkBBytes / 2, &tmap_b, w.n1,
+                        w.b_y + kb * (BK / 2), pk_full_bar(s));
+          } else {
+            const int s = it % S;
+            const uint32_t ph = (it / S) & 1;
+            if (!mbar_wait(empty_bar(s), ph ^ 1u, ctx, 11)) { ok = false; break; }
+            const uint32_t dst = stage_base + s * T::kStageBytes;
+            mbar_arrive_expect_tx(full_bar(s), T::kStageBytes);
+            if constexpr (kAMn) {
+              tma_load_2d(dst, &tmap_a, w.a_x, w.a_y + kb * BK, full_bar(s));
+            } else {
+              tma_load_2d(dst, &tmap_a, w.a_x + kb * BK, w.a_y, full_bar(s));
+            }
+            tma_load_2d(dst + T::kA8Bytes, &tmap_b, w.n0, w.b_y + kb * BK, full_bar(s));
+            tma_load_2d(dst + T::kA8Bytes + T::kB8Bytes / 2, &tmap_b, w.n1, w.b_y + kb * BK,
+                        full_bar(s));
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_i8(BM, BN, kAMn, true);
+      int it = 0;
+      int grp = 0;  // accumulator hand-over counter (one per K-group)
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+        const TileWork w = decode_tile<kAMn>(p, t);
+        const int total_mma = (w.k_len + 31) / 32;  // K=32 steps that hold real data
+        int j = 0;  // MMA step within the tile
+        for (int kb = 0; kb < w.num_kb && ok; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!mbar_wait(full_bar(s), ph, ctx, 20)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_smem = stage_base + s * T::kStageBytes;
+          const uint32_t b_smem = a_smem + T::kA8Bytes;
+#pragma unroll
+          for (int k = 0; k < BK / 32; ++k, ++j) {
+            if (j >= total_mma) break;
+            const int in_group = (kScale == SCALE_SC) ? (j % mma_per_group) : j;
+            const int b = grp & 1;
+            if (in_group == 0) {
+              const uint32_t aph = (grp >> 1) & 1;
+              if (!mbar_wait(acc_empty_bar(b), aph ^ 1u, ctx, 21)) { ok = false; break; }
+              tc_fence_after_sync();
+            }
+            uint64_t a_desc, b_desc;
+            if constexpr (kAMn) {
+              a_desc = umma_smem_desc_sw128(a_smem + k * 32 * NBLK, BK * NBLK, 1024);
+            } else {
+              a_desc = umma_smem_desc_sw128(a_smem + k * 32, 16, 1024);
+            }
+            b_desc = umma_smem_desc_sw128(b_smem + k * 32 * NBLK, BK * NBLK, 1024);
+            umma_i8(tmem_base + b * BN, a_desc, b_desc, idesc, in_group != 0 ? 1u : 0u);
+            const bool group_end = (kScale == SCALE_SC) ? (in_group == mma_per_group - 1 || j == total_mma - 1)
+                                                        : (j == total_mma - 1);
+            if (group_end) {
+              umma_commit(acc_full_bar(b));
+              ++grp;
+            }
+          }
+          if (ok) umma_commit(empty_bar(s));
+        }
+      }
+    }
+  } else if (warp < 2 + T::kEpiWarps) {
+    // ------------------------------------------------------------------ epilogue
+    const int e = warp - 2;
+    const int q = warp & 3;                  // TMEM lane quarter this warp may read
+    const int half = e >> 2;                 // column half (subchannel mode runs 8 warps)
+    const int row_in_tile = q * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    int grp = 0;
+    bool ok = true;
+    // Columns of the 256-wide accumulator this warp owns:
+    //   per-channel, 4 warps: all 256 (SwiGLU: up 0..127 with gate 128..255)
+    //   subchannel, 8 warps : plain -> [128*half, +128); SwiGLU -> up [64*half,+64) with gate 128+[64*half,+64)
+    constexpr int kOwnCols = (kScale == SCALE_SC) ? 128 : 256;
+    constexpr int kChunks = kOwnCols / 32;
+    for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+      const TileWork w = decode_tile<kAMn>(p, t);
+      const int row = w.out_row0 + row_in_tile;
+      const bool row_ok = (row >= w.row_lo) && (row < w.row_hi);
+      const long long sa_row = w.sa_off + static_cast<long long>(row) * (kScale == SCALE_SC ? p.scale_cols : 1);
+
+      // TMEM column of chunk c, and the output / scale column it maps to.
+      auto tmem_col = [&](int c) -> int {
+        if constexpr (kScale == SCALE_SC) {
+          if constexpr (kEpi == EPI_SWIGLU) return (c < 2) ? (64 * half + 32 * c) : (128 + 64 * half + 32 * (c - 2));
+          else return 128 * half + 32 * c;
+        } else {
+          return 32 * c;
+        }
+      };
+      auto scale_col = [&](int c) -> int {  // column index into b_scale
+        const int tc = tmem_col(c);
+        return (tc < NBLK) ? (w.n0 + tc) : (w.n1 + tc - NBLK);
+      };
+
+      if constexpr (kScale == SCALE_PC) {
+        float sa = 0.f;
+        if (row_ok) sa = __bfloat162float(p.a_scale[sa_row]);
+        if (w.num_kb == 0) {
+          // nothing to reduce (empty group): the result is zero
+          if (row_ok) {
+#pragma unroll 1
+            for (int c = 0; c < 8; ++c) {
+              const int col0 = w.n0 + 32 * c;
+              for (int i = 0; i < 32; ++i) {
+                const int col = col0 + i;
+                if (col < p.N) {
+                  const long long o = w.out_off + static_cast<long long>(row) * p.ldc + col;
+                  if constexpr (kOut == OUT_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(0.f);
+                  else if constexpr (kOut == OUT_F32) reinterpret_cast<float*>(p.out)[o] = 0.f;
+                  else reinterpret_cast<int*>(p.out)[o] = 0;
+                }
+              }
+            }
+          }
+          continue;
+        }
+        const int b = grp & 1;
+        const uint32_t aph = (grp >> 1) & 1;
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait(acc_full_bar(b), aph, ctx, 30))) { ok = false; break; }
+        tc_fence_after_sync();
+        constexpr int kOutChunks = (kEpi == EPI_SWIGLU) ? 4 : 8;
+#pragma unroll 1
+        for (int c = 0; c < kOutChunks; ++c) {
+          uint32_t r[32];
+          float v[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + b * BN + 32 * c, r);
+          tmem_ld_wait();
+          const int col0 = w.n0 + 32 * c;  // output column of this chunk
+          if constexpr (kOut == OUT_S32) {
+            if (row_ok) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const int col = col0 + i;
+                if (col < p.N) {
+                  int a = static_cast<int>(r[i]);
+                  if constexpr (kInt4) a >>= 8;
+                  reinterpret_cast<int*>(p.out)[w.out_off + static_cast<long long>(row) * p.ldc + col] = a;
+                }
+              }
+            }
+            continue;
+          }
+          if constexpr (kOut != OUT_S32) {
+          // scales for the columns (uniform across the warp -> broadcast loads)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = col0 + i;
+            int a = static_cast<int>(r[i]);
+            if constexpr (kInt4) a >>= 8;
+            float sb = (col < p.N) ? __bfloat162float(p.b_scale[w.sb_off + col]) : 0.f;
+            v[i] = __fmul_rn(__fmul_rn(static_cast<float>(a), sa), sb);
+          }
+          if constexpr (kEpi == EPI_SWIGLU) {
+            uint32_t g[32];
+            tmem_ld_32x32b_x32(tmem_base + lane_addr + b * BN + NBLK + 32 * c, g);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int col = col0 + i;
+              int a = static_cast<int>(g[i]);
+              if constexpr (kInt4) a >>= 8;
+              float sb = (col < p.N) ? __bfloat162float(p.b_scale[w.sb_off + p.gate_col_offset + col]) : 0.f;
+              const float gate = __fmul_rn(__fmul_rn(static_cast<float>(a), sa), sb);
+              v[i] = v[i] * (gate / (1.0f + __expf(-gate)));
+            }
+          } else if constexpr (kEpi == EPI_RELU2) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float x = fmaxf(v[i], 0.f);
+              v[i] = x * x;
+            }
+          }
+          if (row_ok) {
+            const long long o = w.out_off + static_cast<long long>(row) * p.ldc + col0;
+            if constexpr (kOut == OUT_BF16) {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + o;
+              if (col0 + 32 <= p.N && (p.ldc % 8 == 0)) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  uint4 pk;
+                  __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i + 0], v[8 * i + 1]);
+                  __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
+                  __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
+                  __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
+                  pk.x = *reinterpret_cast<uint32_t*>(&h0);
+                  pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                  pk.z = *reinterpret_cast<uint32_t*>(&h2);
+                  pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                  reinterpret_cast<uint4*>(dst)[i] = pk;
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (col0 + i < p.N) dst[i] = __float2bfloat16_rn(v[i]);
+              }
+            } else {
+              float* dst = reinterpret_cast<float*>(p.out) + o;
+              if (col0 + 32 <= p.N && (p.ldc % 4 == 0)) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                  reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (col0 + i < p.N) dst[i] = v[i];
+              }
+            }
+          }
+          }  // kOut != OUT_S32
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty_bar(b));
+        ++grp;
+      } else {
+        // ---------------------------------------------------------------- subchannel scales
+        float acc[kOwnCols];
+#pragma unroll
+        for (int i = 0; i < kOwnCols; ++i) acc[i] = 0.f;
+        const int total_mma = (w.k_len + 31) / 32;
+        const int num_groups = (total_mma + mma_per_group - 1) / mma_per_group;
+        for (int gi = 0; gi < num_groups && ok; ++gi, ++grp) {
+          const int b = grp & 1;
+          const uint32_t aph = (grp >> 1) & 1;
+          if (!__all_sync(0xFFFFFFFFu, mbar_wait(acc_full_bar(b), aph, ctx, 31))) { ok = false; break; }
+          tc_fence_after_sync();
+          float sa = 0.f;
+          if (row_ok) sa = __bfloat162float(p.a_scale[sa_row + gi]);
+          const __nv_bfloat16* sb_row = p.b_scale + w.sb_off + static_cast<long long>(gi) * p.lds_b;
+#pragma unroll
+          for (int c = 0; c < kChunks; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(tmem_base + lane_addr + b * BN + tmem_col(c), r);
+            tmem_ld_wait();
+            const int sc0 = scale_col(c);
+            const int lim = (kEpi == EPI_SWIGLU) ? 2 * p.N : p.N;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              int a = static_cast<int>(r[i]);
+              if constexpr (kInt4) a >>= 8;
+              const float sb = (sc0 + i < lim) ? __bfloat162float(sb_row[sc0 + i]) : 0.f;
+              acc[32 * c + i] = __fadd_rn(acc[32 * c + i], __fmul_rn(__fmul_rn(static_cast<float>(a), sa), sb));
+            }
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty_bar(b));
+        }
+        if (!ok) break;
+        // activation + store
+        constexpr int kOutChunksSc = (kEpi == EPI_SWIGLU) ? 2 : 4;
+#pragma unroll
+        for (int c = 0; c < kOutChunksSc; ++c) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float x = acc[32 * c + i];
+            if constexpr (kEpi == EPI_SWIGLU) {
+              const float gate = acc[32 * (c + 2) + i];
+              x = x * (gate / (1.0f + __expf(-gate)));
+            } else if constexpr (kEpi == EPI_RELU2) {
+              x = fmaxf(x, 0.f);
+              x = x * x;
+            }
+            v[i] = x;
+          }
+          const int col0 = w.n0 + tmem_col(c);  // up / plain columns sit in block 0 or 1
+          const int ocol0 = (kEpi == EPI_SWIGLU) ? col0 : ((tmem_col(c) < NBLK) ? col0 : (w.n1 + tmem_col(c) - NBLK));
+          if (row_ok) {
+            const long long o = w.out_off + static_cast<long long>(row) * p.ldc + ocol0;
+            if constexpr (kOut == OUT_BF16) {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + o;
+              if (ocol0 + 32 <= p.N && (p.ldc % 8 == 0)) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  uint4 pk;
+                  __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i + 0], v[8 * i + 1]);
+                  __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
+                  __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
+                  __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
+                  pk.x = *reinterpret_cast<uint32_t*>(&h0);
+                  pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                  pk.z = *reinterpret_cast<uint32_t*>(&h2);
+                  pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                  reinterpret_cast<uint4*>(dst)[i] = pk;
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (ocol0 + i < p.N) dst[i] = __float2bfloat16_rn(v[i]);
+              }
+            } else {
+              float* dst = reinterpret_cast<float*>(p.out) + o;
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (ocol0 + i < p.N) dst[i] = v[i];
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ unpack (int4 only)
+    if constexpr (kInt4) {
+      const int ut = threadIdx.x - (2 + T::kEpiWarps) * 32;  // 0..127
+      // A, K-major: item (r, c): packed row r (0..127), 16-byte chunk c (0..3)
+      const int a_r0 = ut >> 2, a_c = ut & 3;
+      const uint32_t a_src0 = a_r0 * 64 + a_c * 16;
+      const uint32_t a_dst_lo0 = (a_r0 >> 3) * 1024 + (a_r0 & 7) * 128 + (((2 * a_c) ^ (a_r0 & 7)) << 4);
+      const uint32_t a_dst_hi0 = (a_r0 >> 3) * 1024 + (a_r0 & 7) * 128 + (((2 * a_c + 1) ^ (a_r0 & 7)) << 4);
+      // MN-major operand block of 128 columns: item (pr, cn): packed K row pr, chunk cn (0..7)
+      const int m_p0 = ut >> 3, m_cn = ut & 7;      // A (MN-major): 16 rows per pass, 4 passes
+      const int b_p0 = ut >> 4, b_cn = ut & 15;     // B: 8 rows per pass, 8 passes, 16 chunks (2 blocks)
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+        const TileWork w = decode_tile<kAMn>(p, t);
+        for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
+          const int ps = it % PS;
+          const uint32_t pph = (it / PS) & 1;
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!__all_sync(0xFFFFFFFFu, mbar_wait(pk_full_bar(ps), pph, ctx, 40))) { ok = false; break; }
+          if (!__all_sync(0xFFFFFFFFu, mbar_wait(empty_bar(s), ph ^ 1u, ctx, 41))) { ok = false; break; }
+          const uint8_t* pk_a = smem_gen + S * T::kStageBytes + ps * T::kPkStageBytes;
+          const uint8_t* pk_b = pk_a + T::kPkABytes;
+          uint8_t* a8 = smem_gen + s * T::kStageBytes;
+          uint8_t* b8 = a8 + T::kA8Bytes;
+          if constexpr (!kAMn) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint4 x = *reinterpret_cast<const uint4*>(pk_a + a_src0 + j * 2048);
+              uint4 lo, hi;
+              expand_word(x.x, lo.x, hi.x);
+              expand_word(x.y, lo.y, hi.y);
+              expand_word(x.z, lo.z, hi.z);
+              expand_word(x.w, lo.w, hi.w);
+              *reinterpret_cast<uint4*>(a8 + a_dst_lo0 + j * 4096) = lo;
+              *reinterpret_cast<uint4*>(a8 + a_dst_hi0 + j * 4096) = hi;
+            }
+          } else {
+            // packed tile [64 K rows][128 B of M]
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int pr = m_p0 + 16 * j;  // 0..63
+              const uint4 x = *reinterpret_cast<const uint4*>(pk_a + pr * 128 + m_cn * 16);
+              uint4 lo, hi;
+              expand_word(x.x, lo.x, hi.x);
+              expand_word(x.y, lo.y, hi.y);
+              expand_word(x.z, lo.z, hi.z);
+              expand_word(x.w, lo.w, hi.w);
+              const int slot = 32 * (pr >> 4) + (pr & 15);
+              const uint32_t d = slot * 128 + ((m_cn ^ (slot & 7)) << 4);
+              *reinterpret_cast<uint4*>(a8 + d) = lo;
+              *reinterpret_cast<uint4*>(a8 + d + 16 * 128) = hi;
+            }
+          }
+          // B: packed tile = two blocks of [64 K rows][128 B of N]
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int pr = b_p0 + 8 * j;  // 0..63
+            const int blk = b_cn >> 3, cn = b_cn & 7;
+            uint4 x = *reinterpret_cast<const uint4*>(pk_b + blk * (T::kPkBBytes / 2) + pr * 128 + cn * 16);
+            uint4 lo, hi;
+            expand_word(x.x, lo.x, hi.x);
+            expand_word(x.y, lo.y, hi.y);
+            expand_word(x.z, lo.z, hi.z);
+            expand_word(x.w, lo.w, hi.w);
+            if constexpr (kMaskK) {
+              const int k_lo = kb * BK + 2 * pr;
+              if (k_lo >= w.k_valid) lo = make_uint4(0, 0, 0, 0);
+              if (k_lo + 1 >= w.k_valid) hi = make_uint4(0, 0, 0, 0);
+            }
+            const int slot = 32 * (pr >> 4) + (pr & 15);
+            const uint32_t d = blk * (T::kB8Bytes / 2) + slot * 128 + ((cn ^ (slot & 7)) << 4);
+            *reinterpret_cast<uint4*>(b8 + d) = lo;
+            *reinterpret_cast<uint4*>(b8 + d + 16 * 128) = hi;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(full_bar(s));
+            mbar_arrive(pk_empty_bar(ps));
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace b200
