@@ -49,6 +49,8 @@ enum { B200_OUT_BF16 = 0, B200_OUT_F32 = 1, B200_OUT_S32 = 2 };
  * meet its alignment rules and the plain CUDA-core kernel otherwise; the other two
  * force one of them (B200_PATH_TCGEN05 fails when the rules are not met). */
 enum { B200_PATH_AUTO = 0, B200_PATH_TCGEN05 = 1, B200_PATH_SIMT = 2 };
+/* PERSISTENT: one CTA per SM walks the tile list.  STANDARD: one CTA per output tile. */
+enum { B200_SCHEDULE_PERSISTENT = 0, B200_SCHEDULE_STANDARD = 1 };
 
 typedef struct b200_gemm_variant {
   int32_t dtype;      /* B200_DTYPE_*      */
@@ -60,7 +62,8 @@ typedef struct b200_gemm_variant {
   int32_t split_k;    /* 1, 2, 4 or 8; >1 requires epilogue NONE and out_dtype F32 */
   int32_t path;       /* B200_PATH_*       */
   int32_t group_m;    /* raster swizzle width in row tiles, 0 = library default */
-  int32_t reserved[7];
+  int32_t schedule;   /* B200_SCHEDULE_*   */
+  int32_t reserved[6];
 } b200_gemm_variant;
 
 /* Replaces amd_strix_halo_kernels_dispatch_version (dispatch.cpp:206). */

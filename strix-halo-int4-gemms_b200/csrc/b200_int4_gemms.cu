@@ -210,6 +210,8 @@ int check_variant(const b200_gemm_variant* v) {
   if (v->split_k > 1 && (v->epilogue != B200_EPILOGUE_NONE || v->out_dtype != B200_OUT_F32))
     return fail("split_k > 1 needs epilogue NONE and float32 output");
   if (v->path < B200_PATH_AUTO || v->path > B200_PATH_SIMT) return fail("variant.path is unknown");
+  if (v->schedule != B200_SCHEDULE_PERSISTENT && v->schedule != B200_SCHEDULE_STANDARD)
+    return fail("variant.schedule is unknown");
   return 0;
 }
 
@@ -375,7 +377,8 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
   p.b_scale = static_cast<const __nv_bfloat16*>(b_scale);
   p.out = c;
   p.status = dev->status_dev;
-  const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
+  int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
+  if (v->schedule == B200_SCHEDULE_STANDARD) grid = p.num_tiles;
   int rc = launch_tc(tl, ta, tb, p, grid, stream);
   if (rc < 0) return fail("internal: no tcgen05 instantiation for this variant");
   return rc;

@@ -1,0 +1,552 @@
+"""ctypes binding of libb200_int4_gemms.so and the tensor-level launchers built on it.
+
+Stands where the reference's ``native.py`` stood (ctypes prototypes :54-143, status :146-155,
+``launch_generated_kernel`` :690-767, ragged launch wrappers :533-667).  The reference read a
+JSON record per kernel to learn its grid, block and shared-memory size and passed them across
+the C boundary; here the library decides those itself and the binding passes a plain variant
+record, the caller's stream, pointers and sizes.
+
+There is no CPU or JIT fallback: when the shared library is missing, or the tensors are not on
+a CUDA device, the launchers raise.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Any
+
+from .metadata import Epilogue, GemmLayout, KernelMetadata, KernelSchedule, OperandDType, ScaleMode, ScaleSpec
+from .template_config import LaunchShape
+
+NATIVE_LIBRARY_NAME = "libb200_int4_gemms.so"
+THREADS_PER_WARP = 32
+
+DTYPE_CODES = {OperandDType.INT4: 0, OperandDType.INT8: 1}
+LAYOUT_CODES = {GemmLayout.NN: 0, GemmLayout.NT: 1, GemmLayout.TN: 2, GemmLayout.TT: 3}
+EPILOGUE_CODES = {Epilogue.NONE: 0, Epilogue.RELU2: 1, Epilogue.SWIGLU: 2}
+OUT_BF16, OUT_F32, OUT_S32 = 0, 1, 2
+PATH_AUTO, PATH_TCGEN05, PATH_SIMT = 0, 1, 2
+SCHEDULE_PERSISTENT, SCHEDULE_STANDARD = 0, 1
+
+EXPORTED_SYMBOLS = (
+    "b200_int4_gemms_dispatch_version",
+    "b200_int4_gemms_has_compiled_kernels",
+    "b200_int4_gemms_has_cuda_runtime",
+    "b200_int4_gemms_has_linked_kernels",
+    "b200_int4_gemms_last_error",
+    "b200_int4_gemms_device_status",
+    "b200_int4_gemms_reset_device_status",
+    "b200_int4_gemms_launch_dense",
+    "b200_int4_gemms_dense_workspace_bytes",
+    "b200_int4_gemms_launch_ragged_fwd",
+    "b200_int4_gemms_launch_ragged_bwd",
+    "b200_int4_gemms_unpack_int4",
+)
+
+
+class GemmVariant(ctypes.Structure):
+    """``b200_gemm_variant`` of include/b200_int4_gemms.h."""
+
+    _fields_ = [
+        ("dtype", ctypes.c_int32),
+        ("layout", ctypes.c_int32),
+        ("scale_mode", ctypes.c_int32),
+        ("subchannel", ctypes.c_int32),
+        ("epilogue", ctypes.c_int32),
+        ("out_dtype", ctypes.c_int32),
+        ("split_k", ctypes.c_int32),
+        ("path", ctypes.c_int32),
+        ("group_m", ctypes.c_int32),
+        ("schedule", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 6),
+    ]
+
+
+@dataclass(frozen=True, slots=True)
+class NativeRuntimeStatus:
+    library_path: Path
+    dispatch_version: int
+    has_compiled_code_objects: bool
+    has_cuda_runtime: bool
+    has_linked_kernels: bool
+
+    @property
+    def has_hip_runtime(self) -> bool:
+        """Name the reference uses for "the GPU runtime is usable" (native.py:19-25)."""
+        return self.has_cuda_runtime
+
+
+def package_root() -> Path:
+    return Path(__file__).resolve().parent
+
+
+def native_library_path(*, root: str | Path | None = None) -> Path:
+    base = Path(root) if root is not None else package_root() / "lib"
+    return base / NATIVE_LIBRARY_NAME
+
+
+_LIBRARIES: dict[str, ctypes.CDLL] = {}
+_LIBRARIES_LOCK = threading.Lock()
+
+
+def _declare(library: ctypes.CDLL) -> None:
+    void_p, i32, i64, size_t = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_size_t
+    variant_p = ctypes.POINTER(GemmVariant)
+    for name in ("dispatch_version", "has_compiled_kernels", "has_cuda_runtime", "has_linked_kernels"):
+        fn = getattr(library, f"b200_int4_gemms_{name}")
+        fn.restype, fn.argtypes = ctypes.c_int, []
+    library.b200_int4_gemms_last_error.restype = ctypes.c_char_p
+    library.b200_int4_gemms_last_error.argtypes = []
+    library.b200_int4_gemms_device_status.restype = ctypes.c_int
+    library.b200_int4_gemms_device_status.argtypes = [ctypes.c_int, ctypes.POINTER(i32)]
+    library.b200_int4_gemms_reset_device_status.restype = ctypes.c_int
+    library.b200_int4_gemms_reset_device_status.argtypes = [ctypes.c_int]
+    library.b200_int4_gemms_launch_dense.restype = ctypes.c_int
+    library.b200_int4_gemms_launch_dense.argtypes = [
+        variant_p, ctypes.c_int, size_t, void_p, void_p, void_p, void_p, void_p, void_p, size_t, i32, i32, i32,
+    ]
+    library.b200_int4_gemms_dense_workspace_bytes.restype = size_t
+    library.b200_int4_gemms_dense_workspace_bytes.argtypes = [variant_p, i32, i32, i32]
+    library.b200_int4_gemms_launch_ragged_fwd.restype = ctypes.c_int
+    library.b200_int4_gemms_launch_ragged_fwd.argtypes = [variant_p, ctypes.c_int, size_t] + [void_p] * 9 + [i32] * 7
+    library.b200_int4_gemms_launch_ragged_bwd.restype = ctypes.c_int
+    library.b200_int4_gemms_launch_ragged_bwd.argtypes = [variant_p, ctypes.c_int, size_t] + [void_p] * 6 + [i32] * 5
+    library.b200_int4_gemms_unpack_int4.restype = ctypes.c_int
+    library.b200_int4_gemms_unpack_int4.argtypes = [ctypes.c_int, size_t, void_p, void_p, i64, i64]
+
+
+def load_dispatch_library(path: str | Path | None = None) -> ctypes.CDLL:
+    """dlopen the CUDA library (once per path) and declare its prototypes."""
+    library_path = Path(path) if path is not None else native_library_path()
+    key = str(library_path)
+    with _LIBRARIES_LOCK:
+        cached = _LIBRARIES.get(key)
+        if cached is not None:
+            return cached
+        if not library_path.exists():
+            raise RuntimeError(
+                f"native dispatch library is not installed at {library_path}; "
+                "build it with build.py (nvcc, sm_100a) - there is no fallback path"
+            )
+        library = ctypes.CDLL(key)
+        _declare(library)
+        _LIBRARIES[key] = library
+        return library
+
+
+def dispatch_runtime_status(path: str | Path | None = None) -> NativeRuntimeStatus:
+    library_path = Path(path) if path is not None else native_library_path()
+    library = load_dispatch_library(library_path)
+    return NativeRuntimeStatus(
+        library_path=library_path,
+        dispatch_version=int(library.b200_int4_gemms_dispatch_version()),
+        has_compiled_code_objects=bool(library.b200_int4_gemms_has_compiled_kernels()),
+        has_cuda_runtime=bool(library.b200_int4_gemms_has_cuda_runtime()),
+        has_linked_kernels=bool(library.b200_int4_gemms_has_linked_kernels()),
+    )
+
+
+def _library_last_error(library: ctypes.CDLL) -> str:
+    raw = library.b200_int4_gemms_last_error()
+    return raw.decode("utf-8", errors="replace") if raw else "unknown native dispatcher error"
+
+
+def device_status(device_index: int = 0, *, library_path: str | Path | None = None) -> tuple[int, tuple[int, int, int]]:
+    """(status, (block, wait site, spare)) reported by kernels on a device; 0 means clean.
+
+    Does not synchronise: call after the stream has been synchronised.
+    """
+    library = load_dispatch_library(library_path)
+    detail = (ctypes.c_int32 * 3)()
+    status = int(library.b200_int4_gemms_device_status(int(device_index), detail))
+    return status, (int(detail[0]), int(detail[1]), int(detail[2]))
+
+
+def reset_device_status(device_index: int = 0, *, library_path: str | Path | None = None) -> None:
+    load_dispatch_library(library_path).b200_int4_gemms_reset_device_status(int(device_index))
+
+
+def _torch() -> Any:
+    try:
+        import torch
+    except ImportError as exc:  # pragma: no cover
+        raise RuntimeError("torch is required for native kernel dispatch") from exc
+    return torch
+
+
+def _stream_handle(torch: Any, tensor: Any, stream: Any | None) -> int:
+    chosen = stream if stream is not None else torch.cuda.current_stream(tensor.device)
+    return int(chosen.cuda_stream)
+
+
+def _device_index(tensor: Any) -> int:
+    return int(tensor.device.index or 0)
+
+
+def _require_contiguous(name: str, tensor: Any) -> Any:
+    if not tensor.is_contiguous():
+        raise ValueError(f"{name} must be contiguous for native dispatch")
+    return tensor
+
+
+def _require_bfloat16_scale(torch: Any, name: str, tensor: Any) -> Any:
+    if tensor.dtype != torch.bfloat16:
+        raise ValueError(f"{name} must have dtype torch.bfloat16 for native dispatch; got {tensor.dtype}")
+    return tensor
+
+
+def _logical_problem_shape(kernel: KernelMetadata, a: Any, b: Any) -> tuple[int, int, int]:
+    """(M, N, K) from operand shapes; packed int4 doubles the K extent; SwiGLU halves N."""
+    k_scale = 2 if kernel.a_dtype is OperandDType.INT4 else 1
+    layout = kernel.layout
+    if layout not in (GemmLayout.NN, GemmLayout.NT, GemmLayout.TN):
+        raise ValueError(f"native dispatch does not support layout={layout.value}")
+    a_rows, a_cols = int(a.shape[-2]), int(a.shape[-1])
+    b_rows, b_cols = int(b.shape[-2]), int(b.shape[-1])
+    m, k_a = (a_cols, a_rows * k_scale) if layout is GemmLayout.TN else (a_rows, a_cols * k_scale)
+    n, k_b = (b_rows, b_cols * k_scale) if layout is GemmLayout.NT else (b_cols, b_rows * k_scale)
+    if kernel.epilogue is Epilogue.SWIGLU:
+        if n % 2:
+            raise ValueError("fused SwiGLU native dispatch requires the logical B output dimension to be even")
+        n //= 2
+    if k_a != k_b:
+        raise ValueError(f"logical K mismatch for layout={layout.value}: A has {k_a}, B has {k_b}")
+    return m, n, k_a
+
+
+def _output_torch_dtype(torch: Any, kernel: KernelMetadata) -> Any:
+    try:
+        return {"bfloat16": torch.bfloat16, "float32": torch.float32}[kernel.output_dtype]
+    except KeyError:
+        raise ValueError(f"unsupported kernel output dtype: {kernel.output_dtype}") from None
+
+
+def _scale_cols(scale: ScaleSpec, k: int) -> int:
+    if scale.subchannel_size is None:
+        raise ValueError("subchannel scale mode requires subchannel_size")
+    return -(-k // scale.subchannel_size)
+
+
+def _validate_scale_shapes(kernel: KernelMetadata, *, m: int, n: int, k: int, a_scale: Any, b_scale: Any) -> None:
+    b_cols = 2 * n if kernel.epilogue is Epilogue.SWIGLU else n
+    if kernel.scale.mode is ScaleMode.PER_CHANNEL:
+        want_a, want_b = (m,), (b_cols,)
+        if tuple(a_scale.shape) != want_a:
+            raise ValueError(f"a_scale must have shape ({m},) for native dispatch; got {tuple(a_scale.shape)}")
+        if tuple(b_scale.shape) != want_b:
+            raise ValueError(f"b_scale must have shape ({b_cols},) for native dispatch; got {tuple(b_scale.shape)}")
+        return
+    groups = _scale_cols(kernel.scale, k)
+    if tuple(a_scale.shape) != (m, groups):
+        raise ValueError(f"a_scale must have shape ({m}, {groups}) for native dispatch; got {tuple(a_scale.shape)}")
+    if tuple(b_scale.shape) != (groups, b_cols):
+        raise ValueError(
+            "subchannel b_scale must use weight-matched layout "
+            f"{(groups, b_cols)} == (scale_cols, output_cols) for native dispatch; got {tuple(b_scale.shape)}. "
+            f"If you have logical layout {(b_cols, groups)} == (output_cols, scale_cols), "
+            "call pack_rhs_subchannel_scales(...) first."
+        )
+
+
+def launch_grid(kernel: KernelMetadata, m: int, n: int, *, num_sms: int = 148) -> tuple[int, int, int]:
+    """Grid the library uses for a dense launch: one CTA per 128 x 256 tile (x 128 columns for
+    SwiGLU), capped at the SM count for the persistent schedule.  Informational: the library
+    sizes the grid itself (the reference computed it in Python, native.py:306-332)."""
+    tile_cols = 128 if kernel.epilogue is Epilogue.SWIGLU else 256
+    tiles = -(-m // 128) * -(-n // tile_cols)
+    if kernel.schedule is KernelSchedule.PERSISTENT:
+        return (min(num_sms, tiles), 1, 1)
+    return (tiles, 1, 1)
+
+
+def block_size(kernel: KernelMetadata) -> int:
+    return kernel.tile.num_warps * THREADS_PER_WARP
+
+
+def make_variant(
+    *,
+    dtype: OperandDType,
+    layout: GemmLayout,
+    scale: ScaleSpec,
+    epilogue: Epilogue,
+    out_dtype: int,
+    split_k: int = 1,
+    path: int = PATH_AUTO,
+    group_m: int = 0,
+    schedule: KernelSchedule = KernelSchedule.PERSISTENT,
+) -> GemmVariant:
+    variant = GemmVariant()
+    variant.dtype = DTYPE_CODES[dtype]
+    variant.layout = LAYOUT_CODES[layout]
+    variant.scale_mode = 1 if scale.mode is ScaleMode.SUBCHANNEL else 0
+    variant.subchannel = int(scale.subchannel_size or 0)
+    variant.epilogue = EPILOGUE_CODES[epilogue]
+    variant.out_dtype = int(out_dtype)
+    variant.split_k = int(split_k)
+    variant.path = int(path)
+    variant.group_m = int(group_m)
+    variant.schedule = SCHEDULE_STANDARD if schedule is KernelSchedule.STANDARD else SCHEDULE_PERSISTENT
+    return variant
+
+
+def launch_dense(
+    variant: GemmVariant,
+    *,
+    device_index: int,
+    stream_handle: int,
+    a_ptr: int,
+    b_ptr: int,
+    a_scale_ptr: int,
+    b_scale_ptr: int,
+    c_ptr: int,
+    m: int,
+    n: int,
+    k: int,
+    workspace_ptr: int = 0,
+    workspace_bytes: int = 0,
+    library_path: str | Path | None = None,
+) -> None:
+    """Pointer-level dense launch (the reference's ``launch_hsaco``, native.py:335-381)."""
+    library = load_dispatch_library(library_path)
+    rc = library.b200_int4_gemms_launch_dense(
+        ctypes.byref(variant), int(device_index), int(stream_handle),
+        ctypes.c_void_p(int(a_ptr)), ctypes.c_void_p(int(b_ptr)),
+        ctypes.c_void_p(int(a_scale_ptr)), ctypes.c_void_p(int(b_scale_ptr)),
+        ctypes.c_void_p(int(c_ptr)), ctypes.c_void_p(int(workspace_ptr)), int(workspace_bytes),
+        int(m), int(n), int(k),
+    )
+    if rc != 0:
+        raise RuntimeError(_library_last_error(library))
+
+
+def launch_generated_kernel(
+    a: Any,
+    b: Any,
+    *,
+    kernel: KernelMetadata,
+    a_scale: Any,
+    b_scale: Any,
+    c: Any | None = None,
+    gate: Any | None = None,
+    root: str | Path | None = None,
+    library_path: str | Path | None = None,
+    stream: Any | None = None,
+    path: int = PATH_AUTO,
+) -> Any:
+    """Run one registry entry on CUDA tensors and return the output tensor.
+
+    Validation, allocation and error types follow the reference launcher
+    (native.py:690-767): CUDA tensors and both scales required, operands contiguous, scales
+    bf16, output dtype fixed by the entry, shape a multiple of the entry's tile record.
+    """
+    torch = _torch()
+    if not torch.cuda.is_available():
+        raise RuntimeError("native generated kernels require a CUDA torch device")
+    if not getattr(a, "is_cuda", False):
+        raise RuntimeError("native generated kernels require CUDA tensors")
+    if a_scale is None or b_scale is None:
+        raise ValueError("native generated kernels require a_scale and b_scale tensors")
+    if kernel.epilogue is Epilogue.SWIGLU and gate is not None:
+        raise ValueError("SwiGLU native dispatch uses fused up/gate columns; external gate is not supported")
+    if kernel.epilogue is not Epilogue.NONE and kernel.tile.split_k != 1:
+        raise ValueError(f"{kernel.epilogue.value} native dispatch currently supports SPLIT_K=1 only")
+    if library_path is None and root is not None:
+        library_path = native_library_path(root=root)
+
+    a = _require_contiguous("a", a)
+    b = _require_contiguous("b", b)
+    a_scale = _require_bfloat16_scale(torch, "a_scale", _require_contiguous("a_scale", a_scale))
+    b_scale = _require_bfloat16_scale(torch, "b_scale", _require_contiguous("b_scale", b_scale))
+    m, n, k = _logical_problem_shape(kernel, a, b)
+    want_dtype = _output_torch_dtype(torch, kernel)
+    if c is None:
+        c = torch.empty((m, n), device=a.device, dtype=want_dtype)
+    c = _require_contiguous("c", c)
+    if c.dtype != want_dtype:
+        raise ValueError(f"output dtype must be {want_dtype}; got {c.dtype}")
+    if tuple(c.shape[-2:]) != (m, n):
+        raise ValueError(f"output shape must be {(m, n)}; got {tuple(c.shape[-2:])}")
+    LaunchShape(m, n, k).validate_for(kernel)
+    _validate_scale_shapes(kernel, m=m, n=n, k=k, a_scale=a_scale, b_scale=b_scale)
+
+    variant = make_variant(
+        dtype=kernel.a_dtype,
+        layout=kernel.layout,
+        scale=kernel.scale,
+        epilogue=kernel.epilogue,
+        out_dtype=OUT_F32 if want_dtype is torch.float32 else OUT_BF16,
+        split_k=kernel.tile.split_k,
+        path=path,
+        group_m=kernel.tile.group_size_m,
+        schedule=kernel.schedule,
+    )
+    launch_dense(
+        variant,
+        device_index=_device_index(a),
+        stream_handle=_stream_handle(torch, a, stream),
+        a_ptr=a.data_ptr(),
+        b_ptr=b.data_ptr(),
+        a_scale_ptr=a_scale.data_ptr(),
+        b_scale_ptr=b_scale.data_ptr(),
+        c_ptr=c.data_ptr(),
+        m=m,
+        n=n,
+        k=k,
+        library_path=library_path,
+    )
+    return c
+
+
+def launch_accumulators(
+    a: Any,
+    b: Any,
+    *,
+    dtype: OperandDType,
+    layout: GemmLayout = GemmLayout.NN,
+    path: int = PATH_AUTO,
+    library_path: str | Path | None = None,
+    stream: Any | None = None,
+) -> Any:
+    """Raw int32 accumulators ``A_q @ B_q`` of the device path, for bit-exact checks."""
+    torch = _torch()
+    if not getattr(a, "is_cuda", False):
+        raise RuntimeError("native generated kernels require CUDA tensors")
+    probe = KernelMetadata(
+        kernel_id="accumulators", arch="", a_dtype=dtype, b_dtype=dtype, acc_dtype="int32",
+        output_dtype="int32", scale_dtype="bfloat16", scale=ScaleSpec(ScaleMode.PER_CHANNEL),
+        epilogue=Epilogue.NONE, tile=None, device_kernel="", layout=layout,  # type: ignore[arg-type]
+    )
+    m, n, k = _logical_problem_shape(probe, _require_contiguous("a", a), _require_contiguous("b", b))
+    c = torch.empty((m, n), device=a.device, dtype=torch.int32)
+    variant = make_variant(dtype=dtype, layout=layout, scale=probe.scale, epilogue=Epilogue.NONE,
+                           out_dtype=OUT_S32, path=path)
+    launch_dense(
+        variant, device_index=_device_index(a), stream_handle=_stream_handle(torch, a, stream),
+        a_ptr=a.data_ptr(), b_ptr=b.data_ptr(), a_scale_ptr=0, b_scale_ptr=0, c_ptr=c.data_ptr(),
+        m=m, n=n, k=k, library_path=library_path,
+    )
+    return c
+
+
+def launch_ragged_fwd_kernel(
+    lhs: Any,
+    rhs: Any,
+    *,
+    group_info: Any,
+    a_scale: Any,
+    b_scale: Any,
+    out: Any,
+    scale: ScaleSpec,
+    config: Any,
+    layout: GemmLayout,
+    variant: str = "",
+    rows: int,
+    cols: int,
+    k_packed: int,
+    scale_cols: int,
+    root: str | Path | None = None,
+    library_path: str | Path | None = None,
+    stream: Any | None = None,
+    path: int = PATH_AUTO,
+) -> Any:
+    """Grouped forward launch over prebuilt row-block tasks (reference native.py:533-600)."""
+    torch = _torch()
+    if not torch.cuda.is_available() or not getattr(lhs, "is_cuda", False):
+        raise RuntimeError("native ragged kernels require CUDA tensors")
+    a_scale = _require_bfloat16_scale(torch, "a_scale", _require_contiguous("a_scale", a_scale))
+    b_scale = _require_bfloat16_scale(torch, "b_scale", _require_contiguous("b_scale", b_scale))
+    out = _require_contiguous("out", out)
+    if group_info.num_tasks == 0:
+        return out
+    if library_path is None and root is not None:
+        library_path = native_library_path(root=root)
+    library = load_dispatch_library(library_path)
+    record = make_variant(
+        dtype=OperandDType.INT4, layout=layout, scale=scale, epilogue=Epilogue.NONE,
+        out_dtype=OUT_F32 if out.dtype is torch.float32 else OUT_BF16, path=path,
+    )
+    groups = int(rhs.shape[0])
+    rc = library.b200_int4_gemms_launch_ragged_fwd(
+        ctypes.byref(record), _device_index(lhs), _stream_handle(torch, lhs, stream),
+        ctypes.c_void_p(lhs.data_ptr()), ctypes.c_void_p(rhs.data_ptr()),
+        ctypes.c_void_p(a_scale.data_ptr()), ctypes.c_void_p(b_scale.data_ptr()),
+        ctypes.c_void_p(group_info.group_id.data_ptr()), ctypes.c_void_p(group_info.block_start.data_ptr()),
+        ctypes.c_void_p(group_info.actual_start.data_ptr()), ctypes.c_void_p(group_info.actual_end.data_ptr()),
+        ctypes.c_void_p(out.data_ptr()),
+        int(rows), int(cols), int(k_packed), int(scale_cols), int(group_info.num_tasks), groups,
+        int(config.block_m),
+    )
+    if rc != 0:
+        raise RuntimeError(_library_last_error(library))
+    return out
+
+
+def launch_ragged_bwd_kernel(
+    lhs: Any,
+    rhs: Any,
+    group_sizes: Any,
+    *,
+    a_scale: Any,
+    b_scale: Any,
+    out: Any,
+    scale: ScaleSpec,
+    config: Any,
+    layout: GemmLayout,
+    variant: str = "",
+    rows: int,
+    cols: int,
+    k_packed: int,
+    scale_cols: int,
+    root: str | Path | None = None,
+    library_path: str | Path | None = None,
+    stream: Any | None = None,
+    path: int = PATH_AUTO,
+) -> Any:
+    """Grouped K-ragged backward launch (reference native.py:603-667); ``group_sizes`` int64 on device."""
+    torch = _torch()
+    if not torch.cuda.is_available() or not getattr(lhs, "is_cuda", False):
+        raise RuntimeError("native ragged kernels require CUDA tensors")
+    a_scale = _require_bfloat16_scale(torch, "a_scale", _require_contiguous("a_scale", a_scale))
+    b_scale = _require_bfloat16_scale(torch, "b_scale", _require_contiguous("b_scale", b_scale))
+    out = _require_contiguous("out", out)
+    if group_sizes.dtype != torch.int64 or not group_sizes.is_contiguous():
+        group_sizes = group_sizes.to(torch.int64).contiguous()
+    if library_path is None and root is not None:
+        library_path = native_library_path(root=root)
+    library = load_dispatch_library(library_path)
+    record = make_variant(
+        dtype=OperandDType.INT4, layout=layout, scale=scale, epilogue=Epilogue.NONE, out_dtype=OUT_F32, path=path,
+    )
+    groups = int(lhs.shape[0])
+    if groups == 0 or rows == 0 or cols == 0:
+        return out
+    rc = library.b200_int4_gemms_launch_ragged_bwd(
+        ctypes.byref(record), _device_index(lhs), _stream_handle(torch, lhs, stream),
+        ctypes.c_void_p(lhs.data_ptr()), ctypes.c_void_p(rhs.data_ptr()),
+        ctypes.c_void_p(a_scale.data_ptr()), ctypes.c_void_p(b_scale.data_ptr()),
+        ctypes.c_void_p(group_sizes.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+        int(rows), int(cols), int(k_packed), int(scale_cols), groups,
+    )
+    if rc != 0:
+        raise RuntimeError(_library_last_error(library))
+    return out
+
+
+def unpack_int4_on_device(packed: Any, *, library_path: str | Path | None = None, stream: Any | None = None) -> Any:
+    """uint8 ``[rows, Kb]`` -> int8 ``[rows, 2*Kb]`` on the GPU (the pre-expand path of the A/B comparison)."""
+    torch = _torch()
+    if not getattr(packed, "is_cuda", False):
+        raise RuntimeError("native kernels require CUDA tensors")
+    packed = _require_contiguous("packed", packed)
+    rows = int(packed.numel() // packed.shape[-1]) if packed.numel() else 0
+    out = torch.empty((*packed.shape[:-1], packed.shape[-1] * 2), device=packed.device, dtype=torch.int8)
+    library = load_dispatch_library(library_path)
+    rc = library.b200_int4_gemms_unpack_int4(
+        _device_index(packed), _stream_handle(torch, packed, stream),
+        ctypes.c_void_p(packed.data_ptr()), ctypes.c_void_p(out.data_ptr()), rows, int(packed.shape[-1]),
+    )
+    if rc != 0:
+        raise RuntimeError(_library_last_error(library))
+    return out

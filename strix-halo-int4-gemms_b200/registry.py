@@ -1,0 +1,249 @@
+"""Registry of sm_100a GEMM variants and the selection rule of the dense API.
+
+Same surface as the reference's ``registry.py`` (``KernelRegistry.register/get/all/select/
+select_reference/with_status`` :254-349, ``default_registry`` :352, ``seed_tile_configs`` :112,
+``iter_supported_kernel_metadata`` :202) with the variant matrix re-keyed to this library:
+
+    2 operand types x 5 scale specs x 3 layouts x 2 schedules x 88 tile records = 5280 entries
+
+A tile record names the shape multiples it is registered for (rows 128/64/32/16, columns
+256/128, K step 32), the split-K factor (plain epilogue only), and whether K must be a
+multiple of ``block_k * split_k`` (``evenk``) or not (``maskk``).  Selection keeps the
+reference's rule: among even-K entries whose multiples divide the shape, take the one with
+the best measured TOPS, ties broken by the largest ``block_m * block_n``.
+"""
+from __future__ import annotations
+
+from dataclasses import replace
+from typing import Iterable, Iterator
+
+from .metadata import (
+    ACC_DTYPE,
+    ARCH,
+    SCALE_DTYPE_BF16,
+    SUPPORTED_GEMM_LAYOUTS,
+    SUPPORTED_SPLIT_K,
+    Epilogue,
+    GemmLayout,
+    KernelMetadata,
+    KernelSchedule,
+    KernelStatus,
+    OperandDType,
+    ScaleMode,
+    ScaleSpec,
+    TileConfig,
+    make_kernel_id,
+    output_dtype_for_split_k,
+    supported_scale_specs,
+)
+from .template_config import LaunchShape, is_tile_multiple_shape
+
+ROW_MULTIPLES = (128, 64, 32, 16)
+COLUMN_MULTIPLES = (256, 128)
+SWIGLU_COLUMN_MULTIPLES = (128,)  # one tile = 128 up columns + the matching 128 gate columns
+K_STEP = 32                       # one tcgen05.mma kind::i8 instruction reduces 32 K values
+RASTER_GROUP_M = 8
+DEVICE_KERNEL = "b200::gemm_i8_tcgen05_kernel"
+
+
+def cta_warps(dtype: OperandDType, scale: ScaleSpec) -> int:
+    """TMA + MMA warps, 4 (per-channel) or 8 (subchannel) epilogue warps, 4 unpack warps for int4."""
+    epilogue_warps = 8 if scale.mode is ScaleMode.SUBCHANNEL else 4
+    unpack_warps = 4 if dtype is OperandDType.INT4 else 0
+    return 2 + epilogue_warps + unpack_warps
+
+
+def pipeline_stages(dtype: OperandDType) -> int:
+    return 3 if dtype is OperandDType.INT4 else 4
+
+
+def seed_tile_configs(
+    dtype: OperandDType = OperandDType.INT4,
+    *,
+    epilogue: Epilogue | None = None,
+    scale: ScaleSpec | None = None,
+) -> tuple[TileConfig, ...]:
+    """Tile records registered for one (dtype, scale, epilogue) cell of the matrix."""
+    if dtype not in (OperandDType.INT4, OperandDType.INT8):
+        raise ValueError(f"unsupported dtype: {dtype}")
+    scale = scale if scale is not None else ScaleSpec(ScaleMode.PER_CHANNEL)
+    epilogue = epilogue if epilogue is not None else Epilogue.NONE
+    columns = SWIGLU_COLUMN_MULTIPLES if epilogue is Epilogue.SWIGLU else COLUMN_MULTIPLES
+    splits = SUPPORTED_SPLIT_K if epilogue is Epilogue.NONE else (1,)
+    warps = cta_warps(dtype, scale)
+    stages = pipeline_stages(dtype)
+    return tuple(
+        TileConfig(
+            block_m=rows,
+            block_n=cols,
+            block_k=K_STEP,
+            group_size_m=RASTER_GROUP_M,
+            num_warps=warps,
+            num_stages=stages,
+            waves_per_eu=0,
+            even_k=even_k,
+            split_k=split_k,
+        )
+        for split_k in splits
+        for cols in columns
+        for even_k in (True, False)
+        for rows in ROW_MULTIPLES
+    )
+
+
+def _describe(
+    dtype: OperandDType,
+    scale: ScaleSpec,
+    epilogue: Epilogue,
+    tile: TileConfig,
+    layout: GemmLayout,
+    schedule: KernelSchedule,
+) -> KernelMetadata:
+    return KernelMetadata(
+        kernel_id=make_kernel_id(dtype, scale, epilogue, tile, layout=layout, schedule=schedule),
+        arch=ARCH,
+        a_dtype=dtype,
+        b_dtype=dtype,
+        acc_dtype=ACC_DTYPE,
+        output_dtype=output_dtype_for_split_k(tile.split_k),
+        scale_dtype=SCALE_DTYPE_BF16,
+        scale=scale,
+        epilogue=epilogue,
+        tile=tile,
+        device_kernel=DEVICE_KERNEL,
+        layout=layout,
+        schedule=schedule,
+        status=KernelStatus.COMPILED,
+    )
+
+
+def iter_supported_kernel_metadata(
+    *, tiles: Iterable[TileConfig] | None = None
+) -> Iterator[KernelMetadata]:
+    """Every registered variant; ``tiles`` replaces the seed tile list of every cell."""
+    forced = None if tiles is None else tuple(tiles)
+    for schedule in (KernelSchedule.STANDARD, KernelSchedule.PERSISTENT):
+        for dtype in (OperandDType.INT4, OperandDType.INT8):
+            for scale in supported_scale_specs():
+                for epilogue in (Epilogue.NONE, Epilogue.RELU2, Epilogue.SWIGLU):
+                    cell = forced if forced is not None else seed_tile_configs(dtype, epilogue=epilogue, scale=scale)
+                    for layout in SUPPORTED_GEMM_LAYOUTS:
+                        for tile in cell:
+                            yield _describe(dtype, scale, epilogue, tile, layout, schedule)
+
+
+_CellKey = tuple[OperandDType, ScaleSpec, Epilogue, GemmLayout, KernelSchedule]
+
+
+def _cell_of(kernel: KernelMetadata) -> _CellKey:
+    return (kernel.a_dtype, kernel.scale, kernel.epilogue, kernel.layout, kernel.schedule)
+
+
+def _preference(kernel: KernelMetadata) -> tuple[float, int]:
+    return (kernel.measured_tops or 0.0, kernel.tile.block_m * kernel.tile.block_n)
+
+
+class KernelRegistry:
+    """Kernel metadata by id, with an index per (dtype, scale, epilogue, layout, schedule) cell."""
+
+    def __init__(self, kernels: Iterable[KernelMetadata] = ()) -> None:
+        self._kernels: dict[str, KernelMetadata] = {}
+        self._cells: dict[_CellKey, list[str]] = {}
+        for kernel in kernels:
+            self.register(kernel)
+
+    def register(self, kernel: KernelMetadata) -> None:
+        if kernel.kernel_id in self._kernels:
+            raise ValueError(f"duplicate kernel id: {kernel.kernel_id}")
+        if kernel.a_dtype is not kernel.b_dtype:
+            raise ValueError("mixed operand types are not supported")
+        self._kernels[kernel.kernel_id] = kernel
+        self._cells.setdefault(_cell_of(kernel), []).append(kernel.kernel_id)
+
+    def get(self, kernel_id: str) -> KernelMetadata:
+        return self._kernels[kernel_id]
+
+    def all(self) -> tuple[KernelMetadata, ...]:
+        return tuple(self._kernels.values())
+
+    def __len__(self) -> int:
+        return len(self._kernels)
+
+    def _eligible(
+        self,
+        dtype: OperandDType,
+        scale: ScaleSpec,
+        epilogue: Epilogue,
+        layout: GemmLayout,
+        schedule: KernelSchedule,
+        split_k: int | None,
+    ) -> list[KernelMetadata]:
+        found = []
+        for kernel_id in self._cells.get((dtype, scale, epilogue, layout, schedule), ()):
+            kernel = self._kernels[kernel_id]
+            if not kernel.tile.even_k:
+                continue
+            if epilogue is not Epilogue.NONE and kernel.tile.split_k != 1:
+                continue
+            if split_k is not None and kernel.tile.split_k != split_k:
+                continue
+            found.append(kernel)
+        return found
+
+    def select(
+        self,
+        *,
+        dtype: OperandDType,
+        scale: ScaleSpec,
+        epilogue: Epilogue,
+        m: int,
+        n: int,
+        k: int,
+        layout: GemmLayout = GemmLayout.NN,
+        split_k: int | None = None,
+        schedule: KernelSchedule = KernelSchedule.STANDARD,
+        require_compiled: bool = False,
+    ) -> KernelMetadata:
+        shape = LaunchShape(m, n, k)
+        fits = [
+            kernel
+            for kernel in self._eligible(dtype, scale, epilogue, layout, schedule, split_k)
+            if is_tile_multiple_shape(kernel, shape)
+        ]
+        if require_compiled:
+            ready = (KernelStatus.COMPILED, KernelStatus.BENCHMARKED)
+            fits = [kernel for kernel in fits if kernel.status in ready]
+        if not fits:
+            raise LookupError(
+                f"no kernel for dtype={dtype.value}, scale={scale.label}, epilogue={epilogue.value}, "
+                f"layout={layout.value}, schedule={schedule.value}, "
+                f"shape=({m}, {n}, {k})"
+            )
+        return max(fits, key=_preference)
+
+    def select_reference(
+        self,
+        *,
+        dtype: OperandDType,
+        scale: ScaleSpec,
+        epilogue: Epilogue,
+        layout: GemmLayout = GemmLayout.NN,
+        split_k: int | None = 1,
+        schedule: KernelSchedule = KernelSchedule.STANDARD,
+    ) -> KernelMetadata:
+        """Metadata for the CPU reference math: any shape, so no tile-multiple filter."""
+        fits = self._eligible(dtype, scale, epilogue, layout, schedule, split_k)
+        if not fits:
+            raise LookupError(
+                f"no reference kernel metadata for dtype={dtype.value}, scale={scale.label}, "
+                f"epilogue={epilogue.value}, layout={layout.value}, schedule={schedule.value}"
+            )
+        return max(fits, key=_preference)
+
+    def with_status(self, kernel_id: str, status: KernelStatus, **updates: object) -> "KernelRegistry":
+        """A copy of the registry in which one entry has a new status (and other fields)."""
+        changed = replace(self._kernels[kernel_id], status=status, **updates)
+        return KernelRegistry(changed if k.kernel_id == kernel_id else k for k in self._kernels.values())
+
+
+default_registry = KernelRegistry(iter_supported_kernel_metadata())
