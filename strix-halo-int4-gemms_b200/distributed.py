@@ -158,8 +158,9 @@ def all_gather_columns(local_out: Any, column_ranges: Sequence[tuple[int, int]],
     m = int(local_out.shape[0])
     padded = local_out.new_zeros((m, widest))
     padded[:, : local_out.shape[1]] = local_out
-    gathered = local_out.new_empty((world, m, widest))
-    dist.all_gather_into_tensor(gathered, padded, group=group)
+    flat = local_out.new_empty((world * m, widest))  # concatenation along dim 0 suits every backend
+    dist.all_gather_into_tensor(flat, padded, group=group)
+    gathered = flat.view(world, m, widest)
     total = max(hi for _lo, hi in column_ranges)
     full = local_out.new_empty((m, total))
     for r, (lo, hi) in enumerate(column_ranges):
@@ -177,8 +178,9 @@ def all_gather_rows(local_out: Any, row_indices: Sequence[Any], total_rows: int,
     n = int(local_out.shape[1])
     padded = local_out.new_zeros((most, n))
     padded[: local_out.shape[0]] = local_out
-    gathered = local_out.new_empty((world, most, n))
-    dist.all_gather_into_tensor(gathered, padded, group=group)
+    flat = local_out.new_empty((world * most, n))
+    dist.all_gather_into_tensor(flat, padded, group=group)
+    gathered = flat.view(world, most, n)
     full = local_out.new_zeros((total_rows, n))
     for r, idx in enumerate(row_indices):
         full[idx.to(full.device)] = gathered[r, : idx.numel()]

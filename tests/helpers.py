@@ -69,3 +69,50 @@ def assert_close_rms(got: np.ndarray, want: np.ndarray, *, rtol=1e-2, atol_rms=1
     bound = atol_rms * rms + rtol * np.abs(want)
     bad = np.abs(got - want) > bound
     assert not bad.any(), f"{what}: {int(bad.sum())} of {bad.size} elements outside tolerance; worst {np.abs(got - want).max()}"
+
+
+# ----------------------------------------------------------------------------------------------
+# GPU side: calls through the C ABI (ctypes) with arbitrary shapes
+# ----------------------------------------------------------------------------------------------
+def abi_dense(pkg, case, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue="none", out="bf16", path=0, schedule="persistent"):
+    """One dense launch through ``b200_int4_gemms_launch_dense``; returns the CUDA output tensor."""
+    from strix_halo_int4_gemms_b200 import native
+
+    out_dtype = {"bf16": torch.bfloat16, "f32": torch.float32, "s32": torch.int32}[out]
+    code = {"bf16": native.OUT_BF16, "f32": native.OUT_F32, "s32": native.OUT_S32}[out]
+    dev = {name: case[name].cuda() for name in ("a", "b", "a_scale", "b_scale")}
+    c = torch.empty((m, n), device="cuda", dtype=out_dtype)
+    c.fill_(-77 if out == "s32" else float("nan"))
+    variant = native.make_variant(
+        dtype=pkg.OperandDType(dtype), layout=getattr(pkg.GemmLayout, layout.upper()), scale=scale_spec(pkg, sub),
+        epilogue=pkg.Epilogue(epilogue), out_dtype=code, path=path,
+        schedule=pkg.KernelSchedule.STANDARD if schedule == "standard" else pkg.KernelSchedule.PERSISTENT,
+    )
+    native.launch_dense(
+        variant, device_index=0, stream_handle=torch.cuda.current_stream().cuda_stream,
+        a_ptr=dev["a"].data_ptr(), b_ptr=dev["b"].data_ptr(), a_scale_ptr=dev["a_scale"].data_ptr(),
+        b_scale_ptr=dev["b_scale"].data_ptr(), c_ptr=c.data_ptr(), m=m, n=n, k=k,
+    )
+    torch.cuda.synchronize()
+    status, detail = native.device_status(0)
+    assert status == 0, f"device status {status} {detail}"
+    return c
+
+
+def check_dense(pkg, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue="none", out="bf16", path=0, seed=0, exact=None, schedule="persistent"):
+    """Run one dense case on the GPU and compare with the oracle.  ``exact`` defaults to bit
+    equality for everything except SwiGLU (whose exp() is implementation-defined to an ulp)."""
+    case = dense_case(pkg, m=m, n=n, k=k, dtype=dtype, layout=layout, sub=sub, epilogue=epilogue, seed=seed)
+    got = abi_dense(pkg, case, m=m, n=n, k=k, dtype=dtype, layout=layout, sub=sub, epilogue=epilogue, out=out, path=path, schedule=schedule)
+    if out == "s32":
+        want = oracle.int32_accumulators(case["a"].numpy(), case["b"].numpy(), int4=dtype == "int4", layout=layout)
+        np.testing.assert_array_equal(got.cpu().numpy(), want)
+        return
+    want = oracle_dense(case, dtype=dtype, layout=layout, sub=sub, epilogue=epilogue, out_bf16=out == "bf16")
+    got = as_f32(got)
+    assert not np.isnan(got).any()
+    assert_close_rms(got, want, what=f"{dtype} {layout} sub={sub} {epilogue} {m}x{n}x{k}")
+    if exact is None:
+        exact = epilogue != "swiglu"
+    if exact:
+        np.testing.assert_array_equal(got, want)

@@ -1,0 +1,171 @@
+"""Dense GEMM parity on a B200: CUDA path (through the C ABI) against the oracle on the same seeded inputs.
+
+Bar: int32 accumulators and packing bit-exact; bf16 / fp32 outputs within rtol 1e-2 and
+atol 1e-2 x RMS of the reference output (and in fact bit-equal wherever the arithmetic is
+fully specified: everything except the SwiGLU's exp)."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import abi_dense, as_f32, assert_close_rms, bits_to_bf16, check_dense, dense_case, oracle_dense, scale_spec
+from oracle import reference_math as oracle
+
+pytestmark = pytest.mark.gpu
+TCGEN05, SIMT = 1, 2
+
+
+@pytest.mark.parametrize("dtype", ["int4", "int8"])
+@pytest.mark.parametrize("shape", [(128, 256, 128), (256, 512, 512), (384, 768, 1024), (128, 1024, 64)])
+def test_accumulators_bit_exact(pkg, dtype, shape):
+    m, n, k = shape
+    check_dense(pkg, m=m, n=n, k=k, dtype=dtype, out="s32", path=TCGEN05)
+
+
+def test_accumulator_headroom_extreme_values(pkg):
+    """All operands at -8 (int4) / -127..127 extremes: the 16x nibble encoding must not overflow."""
+    m, n, k = 128, 256, 8192
+    a = torch.full((m, k), -8, dtype=torch.int8)
+    b = torch.full((k, n), -8, dtype=torch.int8)
+    b[:, ::2] = 7
+    case = {"a": pkg.pack_int4_k_major(a), "b": pkg.pack_int4_k_major(b.t()).t().contiguous(),
+            "a_scale": torch.ones(m, dtype=torch.bfloat16), "b_scale": torch.ones(n, dtype=torch.bfloat16)}
+    got = abi_dense(pkg, case, m=m, n=n, k=k, out="s32", path=TCGEN05).cpu()
+    assert got[:, 1::2].unique().tolist() == [64 * k] and got[:, ::2].unique().tolist() == [-56 * k]
+
+
+@pytest.mark.parametrize("dtype", ["int4", "int8"])
+@pytest.mark.parametrize("epilogue", ["none", "relu2", "swiglu"])
+@pytest.mark.parametrize("sub", [0, 32, 64, 128, 256])
+def test_scale_modes_and_epilogues(pkg, dtype, epilogue, sub):
+    check_dense(pkg, m=256, n=384, k=512, dtype=dtype, sub=sub, epilogue=epilogue, path=TCGEN05, seed=sub + 1)
+
+
+@pytest.mark.parametrize("layout", ["nn", "tn", "nt"])
+@pytest.mark.parametrize("dtype", ["int4", "int8"])
+def test_layouts(pkg, layout, dtype):
+    check_dense(pkg, m=256, n=512, k=512, dtype=dtype, layout=layout, seed=3)
+    check_dense(pkg, m=256, n=512, k=512, dtype=dtype, layout=layout, sub=128, epilogue="relu2", seed=4)
+
+
+@pytest.mark.parametrize("shape", [(1, 16, 32), (200, 272, 160), (129, 48, 96), (17, 1040, 4128), (513, 2064, 32)])
+def test_partial_tiles_on_the_tensor_core_path(pkg, shape):
+    m, n, k = shape
+    check_dense(pkg, m=m, n=n, k=k, path=TCGEN05)
+    check_dense(pkg, m=m, n=n, k=k, out="f32", path=TCGEN05)
+    check_dense(pkg, m=m, n=n, k=k, sub=32, epilogue="swiglu" if n % 32 == 0 else "relu2", path=TCGEN05)
+
+
+@pytest.mark.parametrize("shape", [(17, 129, 65), (3, 7, 5), (64, 40, 33)])
+def test_unaligned_shapes_take_the_cuda_core_kernel(pkg, shape):
+    """Pitches that are not multiples of 16 bytes cannot be described to TMA; AUTO falls to the plain kernel."""
+    m, n, k = shape
+    for dtype in ("int4", "int8"):
+        check_dense(pkg, m=m, n=n, k=k, dtype=dtype)
+        check_dense(pkg, m=m, n=n, k=k, dtype=dtype, sub=32, epilogue="relu2")
+        check_dense(pkg, m=m, n=n, k=k, dtype=dtype, out="s32")
+    from strix_halo_int4_gemms_b200 import native
+
+    case = dense_case(pkg, m=17, n=129, k=65)
+    with pytest.raises(RuntimeError, match="tcgen05 kernel needs"):
+        abi_dense(pkg, case, m=17, n=129, k=65, path=native.PATH_TCGEN05)
+
+
+def test_both_kernels_agree_bit_for_bit(pkg):
+    for sub, epilogue in ((0, "none"), (64, "relu2")):
+        case = dense_case(pkg, m=192, n=320, k=384, sub=sub, epilogue=epilogue, seed=8)
+        tc = abi_dense(pkg, case, m=192, n=320, k=384, sub=sub, epilogue=epilogue, path=TCGEN05)
+        simt = abi_dense(pkg, case, m=192, n=320, k=384, sub=sub, epilogue=epilogue, path=SIMT)
+        assert torch.equal(tc, simt)
+
+
+def test_standard_and_persistent_schedules_agree(pkg):
+    case = dense_case(pkg, m=2048, n=2048, k=256, seed=9)
+    a = abi_dense(pkg, case, m=2048, n=2048, k=256, schedule="standard")
+    b = abi_dense(pkg, case, m=2048, n=2048, k=256, schedule="persistent")
+    assert torch.equal(a, b)
+
+
+def test_reference_fixtures_on_the_gpu(pkg, golden):
+    """The 54 dense cells the reference package produced on CPU, recomputed by the CUDA path."""
+    for key in (str(n) for n in golden["dense/names"]):
+        dtype, layout, scale, epilogue = key.split("/")[1].split("_")
+        sub = 0 if scale == "pc" else int(scale[2:])
+        case = {"a": torch.from_numpy(golden[f"{key}/a"]), "b": torch.from_numpy(golden[f"{key}/b"]),
+                "a_scale": bits_to_bf16(golden[f"{key}/a_scale_bits"]), "b_scale": bits_to_bf16(golden[f"{key}/b_scale_bits"])}
+        got = abi_dense(pkg, case, m=24, n=32, k=96, dtype=dtype, layout=layout, sub=sub, epilogue=epilogue)
+        want = bits_to_bf16(golden[f"{key}/out_bits"])
+        if epilogue == "swiglu":
+            assert_close_rms(as_f32(got), as_f32(want), what=key)
+        else:
+            assert torch.equal(got.cpu(), want), key
+
+
+def test_quickstart_configuration(pkg, golden):
+    """BASELINE configuration 1 through the public API: mm() on packed operands with unit scales."""
+    a = torch.from_numpy(golden["quickstart/a"]).cuda()
+    b = torch.from_numpy(golden["quickstart/b"]).cuda()
+    out = pkg.mm(a, b, a_scale=torch.ones(128, dtype=torch.bfloat16, device="cuda"), b_scale=torch.ones(1024, dtype=torch.bfloat16, device="cuda"))
+    assert out.dtype is torch.bfloat16 and tuple(out.shape) == (128, 1024)
+    assert torch.equal(out.cpu(), bits_to_bf16(golden["quickstart/out_bits"]))
+
+
+def test_public_api_dispatch(pkg):
+    """mm / fused_swiglu_up_gate / explicit_mm / torch_gemm on CUDA tensors against reference mode."""
+    case = dense_case(pkg, m=256, n=512, k=256, sub=256, epilogue="swiglu", seed=12)
+    dev = {k: v.cuda() for k, v in case.items() if k in ("a", "b", "a_scale", "b_scale")}
+    sc = scale_spec(pkg, 256)
+    got = pkg.fused_swiglu_up_gate(dev["a"], dev["b"], a_scale=dev["a_scale"], b_scale=dev["b_scale"], scale=sc)
+    want = pkg.fused_swiglu_up_gate(case["a"], case["b"], a_scale=case["a_scale"], b_scale=case["b_scale"], scale=sc, use_reference=True)
+    assert_close_rms(as_f32(got), as_f32(want), what="swiglu api")
+    case = dense_case(pkg, m=128, n=256, k=512, dtype="int8", epilogue="relu2", seed=13)
+    dev = {k: v.cuda() for k, v in case.items() if k in ("a", "b", "a_scale", "b_scale")}
+    for schedule in (pkg.KernelSchedule.STANDARD, pkg.KernelSchedule.PERSISTENT):
+        got = pkg.mm(dev["a"], dev["b"], a_scale=dev["a_scale"], b_scale=dev["b_scale"], dtype=pkg.OperandDType.INT8,
+                     epilogue=pkg.Epilogue.RELU2, schedule=schedule)
+        want = pkg.mm(case["a"], case["b"], a_scale=case["a_scale"], b_scale=case["b_scale"], dtype=pkg.OperandDType.INT8,
+                      epilogue=pkg.Epilogue.RELU2, use_reference=True)
+        assert torch.equal(got.cpu(), want)
+    kernel = pkg.default_registry.select(dtype=pkg.OperandDType.INT8, scale=scale_spec(pkg, 0), epilogue=pkg.Epilogue.NONE, m=128, n=256, k=512, split_k=4)
+    got = pkg.explicit_mm(dev["a"], dev["b"], kernel=kernel, a_scale=dev["a_scale"], b_scale=dev["b_scale"])
+    assert got.dtype is torch.float32
+    np.testing.assert_array_equal(got.cpu().numpy(), oracle_dense(case, dtype="int8", out_bf16=False))
+    op_out = pkg.torch_gemm(dev["a"], dev["b"], kernel=kernel, a_scale=dev["a_scale"], b_scale=dev["b_scale"])
+    assert torch.equal(op_out, got)
+    with pytest.raises(ValueError, match="requires tile-multiple shape"):
+        pkg.explicit_mm(dev["a"][:100].contiguous(), dev["b"], kernel=kernel, a_scale=dev["a_scale"][:100].contiguous(), b_scale=dev["b_scale"])
+    with pytest.raises(ValueError, match="must have dtype torch.bfloat16"):
+        pkg.launch_generated_kernel(dev["a"], dev["b"], kernel=kernel, a_scale=dev["a_scale"].float(), b_scale=dev["b_scale"])
+    with pytest.raises(ValueError, match="must be contiguous"):
+        pkg.launch_generated_kernel(dev["a"].t(), dev["b"], kernel=kernel, a_scale=dev["a_scale"], b_scale=dev["b_scale"])
+
+
+def test_runs_are_deterministic(pkg):
+    case = dense_case(pkg, m=512, n=768, k=1024, sub=256, seed=21)
+    first = abi_dense(pkg, case, m=512, n=768, k=1024, sub=256, out="f32")
+    for _ in range(3):
+        assert torch.equal(first, abi_dense(pkg, case, m=512, n=768, k=1024, sub=256, out="f32"))
+
+
+def test_unpack_kernel_matches_oracle(pkg):
+    g = torch.Generator().manual_seed(4)
+    for shape in ((64, 2048), (3, 41), (1, 16)):
+        packed = torch.randint(0, 256, shape, generator=g, dtype=torch.uint8)
+        got = pkg.unpack_int4_on_device(packed.cuda())
+        np.testing.assert_array_equal(got.cpu().numpy(), oracle.unpack_int4_k_major(packed.numpy()))
+
+
+def test_pre_expanded_int8_path_equals_fused_int4_path(pkg):
+    """A/B partner of the fused unpack: expand int4 -> int8 once, then the int8 GEMM; same bits out."""
+    case = dense_case(pkg, m=256, n=512, k=1024, seed=30)
+    fused = abi_dense(pkg, case, m=256, n=512, k=1024)
+    a8 = pkg.unpack_int4_on_device(case["a"].cuda())
+    b8 = pkg.unpack_int4_on_device(case["b"].t().contiguous().cuda()).t().contiguous()
+    expanded = abi_dense(pkg, {"a": a8.cpu(), "b": b8.cpu(), "a_scale": case["a_scale"], "b_scale": case["b_scale"]}, m=256, n=512, k=1024, dtype="int8")
+    assert torch.equal(fused, expanded)
+
+
+def test_autotune_on_device_with_validation(pkg):
+    result = pkg.autotune(m=256, n=256, k=256, dtype=pkg.OperandDType.INT4, scale=scale_spec(pkg, 0), epilogue=pkg.Epilogue.RELU2,
+                          warmup_ms=1, rep_ms=3, validate=True)
+    assert len(result.records) == 8 and all(r.success and r.tops > 0 for r in result.records)
+    assert result.best_record.metadata["timing_backend"] == "cuda_events" and result.best_record.metadata["validated"] is True
