@@ -47,9 +47,15 @@ def _is_stale(target: Path) -> bool:
     return any(dep.stat().st_mtime > built for dep in deps if dep.exists())
 
 
-def build_native(*, force: bool = False, verbose: bool = False) -> Path:
-    """Compile the library if it is missing or older than its sources; return its path."""
-    target = library_path()
+def build_native(*, force: bool = False, verbose: bool = False, defines: tuple[str, ...] = (), output: Path | None = None) -> Path:
+    """Compile the library if it is missing or older than its sources; return its path.
+
+    ``defines`` (e.g. ``("B200_UNPACK_WARPS=4",)``) and ``output`` build a tuning variant beside
+    the default library; the B200_NVCC_DEFINES environment variable (comma separated) adds more.
+    """
+    target = Path(output) if output is not None else library_path()
+    env_defines = tuple(d for d in os.environ.get("B200_NVCC_DEFINES", "").split(",") if d)
+    defines = tuple(defines) + env_defines
     if not force and not _is_stale(target):
         return target
     LIB_DIR.mkdir(parents=True, exist_ok=True)
@@ -66,6 +72,7 @@ def build_native(*, force: bool = False, verbose: bool = False) -> Path:
         "-diag-suppress",
         "128",
     ]
+    cmd += [f"-D{item}" for item in defines]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += ["-o", str(target)]

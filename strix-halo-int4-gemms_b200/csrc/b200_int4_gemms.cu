@@ -97,32 +97,49 @@ cudaError_t set_smem(Kernel kernel, int bytes) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
 
-#define B200_FOR_EACH_TC_KERNEL(X)                                   \
-  /*  int4  A-MN  scale     epilogue    out       maskK */           \
-  X(true, false, SCALE_PC, EPI_NONE, OUT_BF16, false)                \
-  X(true, false, SCALE_PC, EPI_RELU2, OUT_BF16, false)               \
-  X(true, false, SCALE_PC, EPI_SWIGLU, OUT_BF16, false)              \
-  X(true, false, SCALE_PC, EPI_NONE, OUT_F32, false)                 \
-  X(true, false, SCALE_PC, EPI_NONE, OUT_S32, false)                 \
-  X(true, false, SCALE_SC, EPI_NONE, OUT_BF16, false)                \
-  X(true, false, SCALE_SC, EPI_RELU2, OUT_BF16, false)               \
-  X(true, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false)              \
-  X(true, false, SCALE_SC, EPI_NONE, OUT_F32, false)                 \
-  X(true, true, SCALE_PC, EPI_NONE, OUT_BF16, false)                 \
-  X(true, true, SCALE_PC, EPI_NONE, OUT_F32, false)                  \
-  X(true, true, SCALE_SC, EPI_NONE, OUT_BF16, false)                 \
-  X(true, false, SCALE_PC, EPI_NONE, OUT_F32, true)                  \
-  X(true, true, SCALE_PC, EPI_NONE, OUT_F32, true)                   \
-  X(true, false, SCALE_SC, EPI_NONE, OUT_F32, true)                  \
-  X(true, true, SCALE_SC, EPI_NONE, OUT_F32, true)                   \
-  X(false, false, SCALE_PC, EPI_NONE, OUT_BF16, false)               \
-  X(false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false)              \
-  X(false, false, SCALE_PC, EPI_SWIGLU, OUT_BF16, false)             \
-  X(false, false, SCALE_PC, EPI_NONE, OUT_F32, false)                \
-  X(false, false, SCALE_PC, EPI_NONE, OUT_S32, false)                \
-  X(false, false, SCALE_SC, EPI_NONE, OUT_BF16, false)               \
-  X(false, false, SCALE_SC, EPI_RELU2, OUT_BF16, false)              \
-  X(false, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false)
+#define B200_FOR_EACH_TC_KERNEL(X)                                          \
+  /*  int4  A-MN   B-MN  scale     epilogue    out       maskK */           \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false)                 \
+  X(true, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false)                \
+  X(true, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false)               \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, false)                  \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_S32, false)                  \
+  X(true, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false)                 \
+  X(true, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false)                \
+  X(true, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false)               \
+  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, false)                  \
+  X(true, true, true, SCALE_PC, EPI_NONE, OUT_BF16, false)                  \
+  X(true, true, true, SCALE_PC, EPI_NONE, OUT_F32, false)                   \
+  X(true, true, true, SCALE_SC, EPI_NONE, OUT_BF16, false)                  \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, true)                   \
+  X(true, true, true, SCALE_PC, EPI_NONE, OUT_F32, true)                    \
+  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, true)                   \
+  X(true, true, true, SCALE_SC, EPI_NONE, OUT_F32, true)                    \
+  X(true, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false)                \
+  X(true, false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false)               \
+  X(true, false, false, SCALE_PC, EPI_SWIGLU, OUT_BF16, false)              \
+  X(true, false, false, SCALE_PC, EPI_NONE, OUT_F32, false)                 \
+  X(true, false, false, SCALE_PC, EPI_NONE, OUT_S32, false)                 \
+  X(true, false, false, SCALE_SC, EPI_NONE, OUT_BF16, false)                \
+  X(true, false, false, SCALE_SC, EPI_RELU2, OUT_BF16, false)               \
+  X(true, false, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false)              \
+  X(true, false, false, SCALE_SC, EPI_NONE, OUT_F32, false)                 \
+  X(false, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false)                \
+  X(false, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false)               \
+  X(false, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false)              \
+  X(false, false, true, SCALE_PC, EPI_NONE, OUT_F32, false)                 \
+  X(false, false, true, SCALE_PC, EPI_NONE, OUT_S32, false)                 \
+  X(false, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false)                \
+  X(false, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false)               \
+  X(false, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false)              \
+  X(false, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false)               \
+  X(false, false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false)              \
+  X(false, false, false, SCALE_PC, EPI_SWIGLU, OUT_BF16, false)             \
+  X(false, false, false, SCALE_PC, EPI_NONE, OUT_F32, false)                \
+  X(false, false, false, SCALE_PC, EPI_NONE, OUT_S32, false)                \
+  X(false, false, false, SCALE_SC, EPI_NONE, OUT_BF16, false)               \
+  X(false, false, false, SCALE_SC, EPI_RELU2, OUT_BF16, false)              \
+  X(false, false, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false)
 
 int ensure_device(int device_index, DeviceState** out) {
   if (device_index < 0 || device_index >= kMaxDevices) return fail("device_index out of range");
@@ -146,9 +163,9 @@ int ensure_device(int device_index, DeviceState** out) {
     std::memset(st.status_host, 0, 4 * sizeof(int));
     err = cudaHostGetDevicePointer(reinterpret_cast<void**>(&st.status_dev), st.status_host, 0);
     if (err != cudaSuccess) return fail_cuda("cudaHostGetDevicePointer(status)", err);
-#define X(I4, AMN, SC, EP, OT, MK)                                                              \
-  err = set_smem(gemm_i8_tcgen05_kernel<I4, AMN, SC, EP, OT, MK>,                               \
-                 KernelTraits<I4, AMN, SC, EP, OT, MK>::kSmemBytes);                            \
+#define X(I4, AMN, BMN, SC, EP, OT, MK)                                                             \
+  err = set_smem(gemm_i8_tcgen05_kernel<I4, AMN, BMN, SC, EP, OT, MK>,                               \
+                 KernelTraits<I4, AMN, BMN, SC, EP, OT, MK>::kSmemBytes);                            \
   if (err != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(max dynamic shared memory)", err);
     B200_FOR_EACH_TC_KERNEL(X)
 #undef X
@@ -161,17 +178,17 @@ int ensure_device(int device_index, DeviceState** out) {
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 struct TcLaunch {
-  bool int4, a_mn, mask_k;
+  bool int4, a_mn, b_mn, mask_k;
   int scale, epi, out;
 };
 
 int launch_tc(const TcLaunch& l, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
               int grid, cudaStream_t stream) {
-#define X(I4, AMN, SC, EP, OT, MK)                                                               \
-  if (l.int4 == I4 && l.a_mn == AMN && l.scale == SC && l.epi == EP && l.out == OT &&           \
+#define X(I4, AMN, BMN, SC, EP, OT, MK)                                                              \
+  if (l.int4 == I4 && l.a_mn == AMN && l.b_mn == BMN && l.scale == SC && l.epi == EP && l.out == OT &&           \
       l.mask_k == MK) {                                                                          \
-    using T = KernelTraits<I4, AMN, SC, EP, OT, MK>;                                             \
-    gemm_i8_tcgen05_kernel<I4, AMN, SC, EP, OT, MK>                                              \
+    using T = KernelTraits<I4, AMN, BMN, SC, EP, OT, MK>;                                             \
+    gemm_i8_tcgen05_kernel<I4, AMN, BMN, SC, EP, OT, MK>                                              \
         <<<grid, T::kThreads, T::kSmemBytes, stream>>>(ta, tb, p);                               \
     cudaError_t err = cudaGetLastError();                                                        \
     if (err != cudaSuccess) return fail_cuda("tcgen05 GEMM kernel launch", err);                 \
@@ -183,8 +200,8 @@ int launch_tc(const TcLaunch& l, const CUtensorMap& ta, const CUtensorMap& tb, c
 }
 
 bool tc_has(const TcLaunch& l) {
-#define X(I4, AMN, SC, EP, OT, MK)                                                               \
-  if (l.int4 == I4 && l.a_mn == AMN && l.scale == SC && l.epi == EP && l.out == OT &&           \
+#define X(I4, AMN, BMN, SC, EP, OT, MK)                                                              \
+  if (l.int4 == I4 && l.a_mn == AMN && l.b_mn == BMN && l.scale == SC && l.epi == EP && l.out == OT &&           \
       l.mask_k == MK)                                                                            \
     return true;
   B200_FOR_EACH_TC_KERNEL(X)
@@ -309,13 +326,13 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
   const int sc_mode = (v->scale_mode == B200_SCALE_SUBCHANNEL) ? SCALE_SC : SCALE_PC;
   const int scale_cols = sc_mode == SCALE_SC ? (k + v->subchannel - 1) / v->subchannel : 1;
 
-  TcLaunch tl{int4, a_t, false, sc_mode, v->epilogue, v->out_dtype};
-  bool tc_ok = !b_t && tc_has(tl) && aligned16(a) && aligned16(b);
-  // TMA needs 16-byte pitches; vector stores need an aligned output pitch.
-  tc_ok = tc_ok && ((a_t ? m : kb) % 16 == 0) && (b_cols % 16 == 0);
+  TcLaunch tl{int4, a_t, !b_t, false, sc_mode, v->epilogue, v->out_dtype};
+  bool tc_ok = tc_has(tl) && aligned16(a) && aligned16(b);
+  // TMA needs 16-byte pitches
+  tc_ok = tc_ok && ((a_t ? m : kb) % 16 == 0) && ((b_t ? kb : b_cols) % 16 == 0);
   if (v->path == B200_PATH_SIMT) tc_ok = false;
   if (v->path == B200_PATH_TCGEN05 && !tc_ok)
-    return fail("the tcgen05 kernel needs B stored [K, N], 16-byte aligned operands and operand pitches that are multiples of 16 bytes");
+    return fail("the tcgen05 kernel needs 16-byte aligned operands, operand pitches that are multiples of 16 bytes, and a layout other than TT");
 
   if (!tc_ok) {
     SimtParams sp{};
@@ -348,14 +365,22 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
     } else {
       if (int rc = make_map_2d(&ta, a, kb, m, kb, BK / 2, BM, false, "A"); rc != 0) return rc;
     }
-    if (int rc = make_map_2d(&tb, b, b_cols, kb, b_cols, NBLK, BK / 2, false, "B"); rc != 0) return rc;
+    if (b_t) {
+      if (int rc = make_map_2d(&tb, b, kb, b_cols, kb, BK / 2, NBLK, false, "B"); rc != 0) return rc;
+    } else {
+      if (int rc = make_map_2d(&tb, b, b_cols, kb, b_cols, NBLK, BK / 2, false, "B"); rc != 0) return rc;
+    }
   } else {
     if (a_t) {
       if (int rc = make_map_2d(&ta, a, m, kb, m, NBLK, BK, true, "A"); rc != 0) return rc;
     } else {
       if (int rc = make_map_2d(&ta, a, kb, m, kb, BK, BM, true, "A"); rc != 0) return rc;
     }
-    if (int rc = make_map_2d(&tb, b, b_cols, kb, b_cols, NBLK, BK, true, "B"); rc != 0) return rc;
+    if (b_t) {
+      if (int rc = make_map_2d(&tb, b, kb, b_cols, kb, BK, NBLK, true, "B"); rc != 0) return rc;
+    } else {
+      if (int rc = make_map_2d(&tb, b, b_cols, kb, b_cols, NBLK, BK, true, "B"); rc != 0) return rc;
+    }
   }
 
   GemmParams p{};
@@ -415,7 +440,7 @@ extern "C" int b200_int4_gemms_launch_ragged_fwd(
   if (sc_mode == SCALE_SC && scale_cols != (k + v->subchannel - 1) / v->subchannel)
     return fail("scale_cols does not match ceil(K / subchannel)");
 
-  TcLaunch tl{true, a_t, false, sc_mode, EPI_NONE, v->out_dtype};
+  TcLaunch tl{true, a_t, true, false, sc_mode, EPI_NONE, v->out_dtype};
   bool tc_ok = !b_t && !a_t && tc_has(tl) && aligned16(lhs) && aligned16(rhs) && (k_packed % 16 == 0) && (n % 16 == 0);
   if (v->path == B200_PATH_SIMT) tc_ok = false;
   if (v->path == B200_PATH_TCGEN05 && !tc_ok)
@@ -512,7 +537,7 @@ extern "C" int b200_int4_gemms_launch_ragged_bwd(const b200_gemm_variant* v, int
   if (sc_mode == SCALE_SC && scale_cols != (k + v->subchannel - 1) / v->subchannel)
     return fail("scale_cols does not match ceil(K / subchannel)");
 
-  TcLaunch tl{true, a_t, true, sc_mode, EPI_NONE, OUT_F32};
+  TcLaunch tl{true, a_t, true, true, sc_mode, EPI_NONE, OUT_F32};
   bool tc_ok = !b_t && tc_has(tl) && aligned16(lhs) && aligned16(rhs) && ((a_t ? m : k_packed) % 16 == 0) && (n % 16 == 0);
   if (v->path == B200_PATH_SIMT) tc_ok = false;
   if (v->path == B200_PATH_TCGEN05 && !tc_ok)

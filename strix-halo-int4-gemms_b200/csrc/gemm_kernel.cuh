@@ -6,7 +6,7 @@
 //   warp 0        TMA producer: brings packed-int4 (or int8) operand tiles into shared memory
 //   warp 1        MMA issuer: one thread issues tcgen05.mma kind::i8 (s8 x s8 -> s32 in TMEM)
 //   warps 2..     epilogue: tcgen05.ld the accumulator, scale in fp32, activation, store
-//   last 4 warps  (int4 only) unpack: expand nibbles to int8 into the swizzled UMMA tiles
+//   last 8 warps  (int4 only) unpack: expand nibbles to int8 into the swizzled UMMA tiles
 //
 // int4 operands.  Blackwell tensor cores have no int4 MMA, so each nibble v becomes the
 // int8 value 16*v (the nibble moved to the top of its byte, no sign-extension arithmetic).
@@ -161,29 +161,42 @@ __device__ __forceinline__ void expand_word(uint32_t w, uint32_t& lo, uint32_t& 
   hi = w & 0xF0F0F0F0u;
 }
 
-template <bool kInt4, bool kAMn, int kScale, int kEpi, int kOut, bool kMaskK>
+template <bool kInt4, bool kAMn, bool kBMn, int kScale, int kEpi, int kOut, bool kMaskK>
 struct KernelTraits {
-  static constexpr int kUnpackWarps = kInt4 ? 4 : 0;
+#ifndef B200_UNPACK_WARPS
+#define B200_UNPACK_WARPS 8
+#endif
+#ifndef B200_INT4_STAGES
+#define B200_INT4_STAGES 3
+#endif
+#ifndef B200_INT4_PK_STAGES
+#define B200_INT4_PK_STAGES 3
+#endif
+  static constexpr int kUnpackWarps = kInt4 ? B200_UNPACK_WARPS : 0;
   static constexpr int kEpiWarps = (kScale == SCALE_SC) ? 8 : 4;
   static constexpr int kThreads = (2 + kEpiWarps + kUnpackWarps) * 32;
-  static constexpr int kStages = kInt4 ? 3 : 4;   // int8 UMMA stages
-  static constexpr int kPkStages = kInt4 ? 3 : 0; // packed staging stages
+#ifndef B200_INT8_STAGES
+#define B200_INT8_STAGES 4
+#endif
+  static constexpr int kStages = kInt4 ? B200_INT4_STAGES : B200_INT8_STAGES;  // int8 UMMA stages
+  static constexpr int kPkStages = kInt4 ? B200_INT4_PK_STAGES : 0; // packed staging stages
   static constexpr int kA8Bytes = BM * BK;        // 16 KB
   static constexpr int kB8Bytes = BN * BK;        // 32 KB
   static constexpr int kStageBytes = kA8Bytes + kB8Bytes;
   static constexpr int kPkABytes = BM * BK / 2;   // 8 KB
   static constexpr int kPkBBytes = BN * BK / 2;   // 16 KB
   static constexpr int kPkStageBytes = kPkABytes + kPkBBytes;
-  static constexpr int kBarBytes = 256;
+  static constexpr int kBarBytes = 512;
   static constexpr int kSmemBytes =
       1024 + kStages * kStageBytes + kPkStages * kPkStageBytes + kBarBytes;
 };
 
-template <bool kInt4, bool kAMn, int kScale, int kEpi, int kOut, bool kMaskK>
-__global__ void __launch_bounds__(KernelTraits<kInt4, kAMn, kScale, kEpi, kOut, kMaskK>::kThreads, 1)
+template <bool kInt4, bool kAMn, bool kBMn, int kScale, int kEpi, int kOut, bool kMaskK>
+__global__ void __launch_bounds__(KernelTraits<kInt4, kAMn, kBMn, kScale, kEpi, kOut, kMaskK>::kThreads, 1)
 gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
-  using T = KernelTraits<kInt4, kAMn, kScale, kEpi, kOut, kMaskK>;
+  using T = KernelTraits<kInt4, kAMn, kBMn, kScale, kEpi, kOut, kMaskK>;
+  static_assert(kBMn || !kMaskK, "K masking is applied to an MN-major B operand");
   constexpr int S = T::kStages;
   constexpr int PS = T::kPkStages;
 
@@ -197,14 +210,15 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint8_t* bar_gen = smem_gen + S * T::kStageBytes + PS * T::kPkStageBytes;
 
   // barrier slots (8 bytes each)
+  static_assert(S <= 8 && PS <= 8, "barrier slots are laid out for at most 8 stages");
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (4 + s); };
-  auto pk_full_bar = [&](int s) { return bar_base + 8u * (8 + s); };
-  auto pk_empty_bar = [&](int s) { return bar_base + 8u * (12 + s); };
-  auto acc_full_bar = [&](int b) { return bar_base + 8u * (16 + b); };
-  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (18 + b); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * 20);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 8 * 20 + 4);
+  auto empty_bar = [&](int s) { return bar_base + 8u * (8 + s); };
+  auto pk_full_bar = [&](int s) { return bar_base + 8u * (16 + s); };
+  auto pk_empty_bar = [&](int s) { return bar_base + 8u * (24 + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (32 + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (34 + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * 36);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 8 * 36 + 4);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -260,71 +274,125 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             } else {
               tma_load_2d(dst, &tmap_a, w.a_x + kb * (BK / 2), w.a_y, pk_full_bar(s));
             }
-            tma_load_2d(dst + T::kPkABytes, &tmap_b, w.n0, w.b_y + kb * (BK / 2), pk_full_bar(s));
-            tma_load_2d(dst + T::kPkABytes + T::kPkBBytes / 2, &tmap_b, w.n1,
-                        w.b_y + kb * (BK / 2), pk_full_bar(s));
+            if constexpr (kBMn) {
+              tma_load_2d(dst + T::kPkABytes, &tmap_b, w.n0, w.b_y + kb * (BK / 2), pk_full_bar(s));
+              tma_load_2d(dst + T::kPkABytes + T::kPkBBytes / 2, &tmap_b, w.n1,
+                          w.b_y + kb * (BK / 2), pk_full_bar(s));
+            } else {
+              tma_load_2d(dst + T::kPkABytes, &tmap_b, kb * (BK / 2), w.b_y + w.n0, pk_full_bar(s));
+              tma_load_2d(dst + T::kPkABytes + T::kPkBBytes / 2, &tmap_b, kb * (BK / 2), w.b_y + w.n1,
+                          pk_full_bar(s));
+            }
           } else {
             const int s = it % S;
             const uint32_t ph = (it / S) & 1;
             if (!mbar_wait(empty_bar(s), ph ^ 1u, ctx, 11)) { ok = false; break; }
             const uint32_t dst = stage_base + s * T::kStageBytes;
+#if defined(B200_DBG_SKIP_ALL_LOADS)
+            mbar_arrive(full_bar(s));
+            continue;
+#elif defined(B200_DBG_SKIP_B_LOAD)
+            mbar_arrive_expect_tx(full_bar(s), T::kA8Bytes);
+#else
             mbar_arrive_expect_tx(full_bar(s), T::kStageBytes);
+#endif
             if constexpr (kAMn) {
               tma_load_2d(dst, &tmap_a, w.a_x, w.a_y + kb * BK, full_bar(s));
             } else {
               tma_load_2d(dst, &tmap_a, w.a_x + kb * BK, w.a_y, full_bar(s));
             }
-            tma_load_2d(dst + T::kA8Bytes, &tmap_b, w.n0, w.b_y + kb * BK, full_bar(s));
-            tma_load_2d(dst + T::kA8Bytes + T::kB8Bytes / 2, &tmap_b, w.n1, w.b_y + kb * BK,
-                        full_bar(s));
+#ifdef B200_DBG_SKIP_B_LOAD
+            continue;
+#endif
+            if constexpr (kBMn) {
+              tma_load_2d(dst + T::kA8Bytes, &tmap_b, w.n0, w.b_y + kb * BK, full_bar(s));
+              tma_load_2d(dst + T::kA8Bytes + T::kB8Bytes / 2, &tmap_b, w.n1, w.b_y + kb * BK,
+                          full_bar(s));
+            } else {
+              tma_load_2d(dst + T::kA8Bytes, &tmap_b, kb * BK, w.b_y + w.n0, full_bar(s));
+              tma_load_2d(dst + T::kA8Bytes + T::kB8Bytes / 2, &tmap_b, kb * BK, w.b_y + w.n1,
+                          full_bar(s));
+            }
           }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_i8(BM, BN, kAMn, true);
-      int it = 0;
-      int grp = 0;  // accumulator hand-over counter (one per K-group)
-      bool ok = true;
-      for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
-        const TileWork w = decode_tile<kAMn>(p, t);
-        const int total_mma = (w.k_len + 31) / 32;  // K=32 steps that hold real data
+    // The whole warp walks the schedule and waits on barriers together (so that loop control
+    // stays warp-uniform); one elected lane issues the MMAs and the commits.
+    constexpr uint32_t idesc = umma_idesc_i8(BM, BN, kAMn, kBMn);
+    // descriptor = {lo: start address >> 4 | LBO >> 4 << 16, hi: SBO >> 4 | version | swizzle}
+    constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    constexpr uint32_t kALboField = (kAMn ? (BK * NBLK) >> 4 : 1u) << 16;
+    constexpr uint32_t kBLboField = (kBMn ? (BK * NBLK) >> 4 : 1u) << 16;
+    constexpr uint32_t kAStep = (kAMn ? 32 * NBLK : 32) >> 4;   // one K=32 step, in 16-byte units
+    constexpr uint32_t kBStep = (kBMn ? 32 * NBLK : 32) >> 4;
+    const uint32_t a_lo0 = ((stage_base & 0x3FFFFu) >> 4) | kALboField;
+    const uint32_t b_lo0 = (((stage_base + T::kA8Bytes) & 0x3FFFFu) >> 4) | kBLboField;
+    auto make_desc = [&](uint32_t lo) -> uint64_t { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
+    int it = 0;
+    int grp = 0;  // accumulator hand-over counter (one per K-group)
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+      const TileWork w = decode_tile<kAMn>(p, t);
+      const int total_mma = (w.k_len + 31) / 32;  // K=32 steps that hold real data
+      if constexpr (kScale == SCALE_PC) {
+        if (w.num_kb == 0) continue;
+        const int b = grp & 1;
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait(acc_empty_bar(b), ((grp >> 1) & 1) ^ 1u, ctx, 21))) { ok = false; break; }
+        for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!__all_sync(0xFFFFFFFFu, mbar_wait(full_bar(s), ph, ctx, 20))) { ok = false; break; }
+          tc_fence_after_sync();
+          if (elect_one()) {
+            const uint32_t a_lo = a_lo0 + s * (T::kStageBytes >> 4);
+            const uint32_t b_lo = b_lo0 + s * (T::kStageBytes >> 4);
+            const int left = total_mma - kb * (BK / 32);
+#pragma unroll
+            for (int k = 0; k < BK / 32; ++k) {
+              if (k < left)
+                umma_i8(tmem_base + b * BN, make_desc(a_lo + k * kAStep), make_desc(b_lo + k * kBStep), idesc,
+                        (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(empty_bar(s));
+            if (kb == w.num_kb - 1) umma_commit(acc_full_bar(b));
+          }
+          __syncwarp();
+        }
+        ++grp;
+      } else {
         int j = 0;  // MMA step within the tile
         for (int kb = 0; kb < w.num_kb && ok; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
-          if (!mbar_wait(full_bar(s), ph, ctx, 20)) { ok = false; break; }
+          if (!__all_sync(0xFFFFFFFFu, mbar_wait(full_bar(s), ph, ctx, 20))) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t a_smem = stage_base + s * T::kStageBytes;
-          const uint32_t b_smem = a_smem + T::kA8Bytes;
+          const uint32_t a_lo = a_lo0 + s * (T::kStageBytes >> 4);
+          const uint32_t b_lo = b_lo0 + s * (T::kStageBytes >> 4);
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k, ++j) {
             if (j >= total_mma) break;
-            const int in_group = (kScale == SCALE_SC) ? (j % mma_per_group) : j;
+            const int in_group = j % mma_per_group;
             const int b = grp & 1;
             if (in_group == 0) {
-              const uint32_t aph = (grp >> 1) & 1;
-              if (!mbar_wait(acc_empty_bar(b), aph ^ 1u, ctx, 21)) { ok = false; break; }
+              if (!__all_sync(0xFFFFFFFFu, mbar_wait(acc_empty_bar(b), ((grp >> 1) & 1) ^ 1u, ctx, 21))) { ok = false; break; }
               tc_fence_after_sync();
             }
-            uint64_t a_desc, b_desc;
-            if constexpr (kAMn) {
-              a_desc = umma_smem_desc_sw128(a_smem + k * 32 * NBLK, BK * NBLK, 1024);
-            } else {
-              a_desc = umma_smem_desc_sw128(a_smem + k * 32, 16, 1024);
+            const bool group_end = (in_group == mma_per_group - 1) || (j == total_mma - 1);
+            if (elect_one()) {
+              umma_i8(tmem_base + b * BN, make_desc(a_lo + k * kAStep), make_desc(b_lo + k * kBStep), idesc,
+                      in_group != 0 ? 1u : 0u);
+              if (group_end) umma_commit(acc_full_bar(b));
             }
-            b_desc = umma_smem_desc_sw128(b_smem + k * 32 * NBLK, BK * NBLK, 1024);
-            umma_i8(tmem_base + b * BN, a_desc, b_desc, idesc, in_group != 0 ? 1u : 0u);
-            const bool group_end = (kScale == SCALE_SC) ? (in_group == mma_per_group - 1 || j == total_mma - 1)
-                                                        : (j == total_mma - 1);
-            if (group_end) {
-              umma_commit(acc_full_bar(b));
-              ++grp;
-            }
+            __syncwarp();
+            if (group_end) ++grp;
           }
-          if (ok) umma_commit(empty_bar(s));
+          if (ok) {
+            if (elect_one()) umma_commit(empty_bar(s));
+            __syncwarp();
+          }
         }
       }
     }
@@ -388,7 +456,11 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t aph = (grp >> 1) & 1;
         if (!__all_sync(0xFFFFFFFFu, mbar_wait(acc_full_bar(b), aph, ctx, 30))) { ok = false; break; }
         tc_fence_after_sync();
+#ifdef B200_DBG_SKIP_EPILOGUE
+        constexpr int kOutChunks = 0;
+#else
         constexpr int kOutChunks = (kEpi == EPI_SWIGLU) ? 4 : 8;
+#endif
 #pragma unroll 1
         for (int c = 0; c < kOutChunks; ++c) {
           uint32_t r[32];
@@ -572,15 +644,30 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else {
     // ------------------------------------------------------------------ unpack (int4 only)
     if constexpr (kInt4) {
-      const int ut = threadIdx.x - (2 + T::kEpiWarps) * 32;  // 0..127
-      // A, K-major: item (r, c): packed row r (0..127), 16-byte chunk c (0..3)
+      constexpr int UT = T::kUnpackWarps * 32;           // unpack threads: 128 or 256
+      const int ut = threadIdx.x - (2 + T::kEpiWarps) * 32;
+      // Every item is one 16-byte load of packed data (32 nibbles) that becomes two 16-byte
+      // chunks of int8.  Per-thread offsets are fixed; successive passes add a constant.
+      //
+      // A, K-major.  Packed tile [128 rows][64 B].  Item (r, c): row r, packed chunk c (0..3)
+      // -> int8 chunks 2c (low nibbles) and 2c+1 (high nibbles) of row r, XOR-swizzled by r & 7.
+      constexpr int kARowsPerPass = UT / 4;               // 32 or 64 (multiple of 8: r & 7 is fixed)
       const int a_r0 = ut >> 2, a_c = ut & 3;
       const uint32_t a_src0 = a_r0 * 64 + a_c * 16;
-      const uint32_t a_dst_lo0 = (a_r0 >> 3) * 1024 + (a_r0 & 7) * 128 + (((2 * a_c) ^ (a_r0 & 7)) << 4);
-      const uint32_t a_dst_hi0 = (a_r0 >> 3) * 1024 + (a_r0 & 7) * 128 + (((2 * a_c + 1) ^ (a_r0 & 7)) << 4);
-      // MN-major operand block of 128 columns: item (pr, cn): packed K row pr, chunk cn (0..7)
-      const int m_p0 = ut >> 3, m_cn = ut & 7;      // A (MN-major): 16 rows per pass, 4 passes
-      const int b_p0 = ut >> 4, b_cn = ut & 15;     // B: 8 rows per pass, 8 passes, 16 chunks (2 blocks)
+      const uint32_t a_row_off = (a_r0 >> 3) * 1024 + (a_r0 & 7) * 128;
+      const uint32_t a_dst_lo0 = a_row_off + (((2 * a_c) ^ (a_r0 & 7)) << 4);
+      const uint32_t a_dst_hi0 = a_row_off + (((2 * a_c + 1) ^ (a_r0 & 7)) << 4);
+      // MN-major block of 128 columns.  Packed tile [64 K rows][128 B].  Item (pr, cn): packed
+      // row pr -> K slots 32*(pr/16) + pr%16 (low) and +16 (high), chunk cn swizzled by slot & 7.
+      constexpr int kMRowsPerPass = UT / 8;               // A (one block): 16 or 32 packed rows per pass
+      const int m_p0 = ut >> 3, m_cn = ut & 7;
+      const int m_slot0 = 32 * (m_p0 >> 4) + (m_p0 & 15);
+      const uint32_t m_src0 = m_p0 * 128 + m_cn * 16;
+      const uint32_t m_dst0 = m_slot0 * 128 + ((m_cn ^ (m_slot0 & 7)) << 4);
+      constexpr int kBRowsPerPass = UT / 16;              // B (two blocks): 8 or 16 packed rows per pass
+      const int b_p0 = ut >> 4, b_blk = (ut >> 3) & 1, b_cn = ut & 7;
+      const uint32_t b_src0 = b_blk * (T::kPkBBytes / 2) + b_p0 * 128 + b_cn * 16;
+      const uint32_t b_dst0 = b_blk * (T::kB8Bytes / 2) + b_p0 * 128 + ((b_cn ^ (b_p0 & 7)) << 4);
       int it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
@@ -591,58 +678,63 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
           if (!__all_sync(0xFFFFFFFFu, mbar_wait(pk_full_bar(ps), pph, ctx, 40))) { ok = false; break; }
-          if (!__all_sync(0xFFFFFFFFu, mbar_wait(empty_bar(s), ph ^ 1u, ctx, 41))) { ok = false; break; }
           const uint8_t* pk_a = smem_gen + S * T::kStageBytes + ps * T::kPkStageBytes;
           const uint8_t* pk_b = pk_a + T::kPkABytes;
+          // all loads of the stage first: they do not depend on the int8 stage being free
+          uint4 xa[512 / UT];
+          uint4 xb[1024 / UT];  // K-major B: packed tile [256 rows][64 B], same item scheme as K-major A
+#pragma unroll
+          for (int j = 0; j < 512 / UT; ++j) {
+            if constexpr (!kAMn) xa[j] = *reinterpret_cast<const uint4*>(pk_a + a_src0 + j * (kARowsPerPass * 64));
+            else xa[j] = *reinterpret_cast<const uint4*>(pk_a + m_src0 + j * (kMRowsPerPass * 128));
+          }
+#pragma unroll
+          for (int j = 0; j < 1024 / UT; ++j) {
+            if constexpr (kBMn) xb[j] = *reinterpret_cast<const uint4*>(pk_b + b_src0 + j * (kBRowsPerPass * 128));
+            else xb[j] = *reinterpret_cast<const uint4*>(pk_b + a_src0 + j * (kARowsPerPass * 64));
+          }
+          if (!__all_sync(0xFFFFFFFFu, mbar_wait(empty_bar(s), ph ^ 1u, ctx, 41))) { ok = false; break; }
           uint8_t* a8 = smem_gen + s * T::kStageBytes;
           uint8_t* b8 = a8 + T::kA8Bytes;
-          if constexpr (!kAMn) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint4 x = *reinterpret_cast<const uint4*>(pk_a + a_src0 + j * 2048);
-              uint4 lo, hi;
-              expand_word(x.x, lo.x, hi.x);
-              expand_word(x.y, lo.y, hi.y);
-              expand_word(x.z, lo.z, hi.z);
-              expand_word(x.w, lo.w, hi.w);
-              *reinterpret_cast<uint4*>(a8 + a_dst_lo0 + j * 4096) = lo;
-              *reinterpret_cast<uint4*>(a8 + a_dst_hi0 + j * 4096) = hi;
-            }
-          } else {
-            // packed tile [64 K rows][128 B of M]
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int pr = m_p0 + 16 * j;  // 0..63
-              const uint4 x = *reinterpret_cast<const uint4*>(pk_a + pr * 128 + m_cn * 16);
-              uint4 lo, hi;
-              expand_word(x.x, lo.x, hi.x);
-              expand_word(x.y, lo.y, hi.y);
-              expand_word(x.z, lo.z, hi.z);
-              expand_word(x.w, lo.w, hi.w);
-              const int slot = 32 * (pr >> 4) + (pr & 15);
-              const uint32_t d = slot * 128 + ((m_cn ^ (slot & 7)) << 4);
+          for (int j = 0; j < 512 / UT; ++j) {
+            uint4 lo, hi;
+            expand_word(xa[j].x, lo.x, hi.x);
+            expand_word(xa[j].y, lo.y, hi.y);
+            expand_word(xa[j].z, lo.z, hi.z);
+            expand_word(xa[j].w, lo.w, hi.w);
+            if constexpr (!kAMn) {
+              *reinterpret_cast<uint4*>(a8 + a_dst_lo0 + j * (kARowsPerPass * 128)) = lo;
+              *reinterpret_cast<uint4*>(a8 + a_dst_hi0 + j * (kARowsPerPass * 128)) = hi;
+            } else {
+              // packed rows advance by a multiple of 16 per pass: 32 K slots per 16 packed rows
+              const uint32_t d = m_dst0 + j * ((kMRowsPerPass / 16) * 32 * 128);
               *reinterpret_cast<uint4*>(a8 + d) = lo;
               *reinterpret_cast<uint4*>(a8 + d + 16 * 128) = hi;
             }
           }
-          // B: packed tile = two blocks of [64 K rows][128 B of N]
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int pr = b_p0 + 8 * j;  // 0..63
-            const int blk = b_cn >> 3, cn = b_cn & 7;
-            uint4 x = *reinterpret_cast<const uint4*>(pk_b + blk * (T::kPkBBytes / 2) + pr * 128 + cn * 16);
+          for (int j = 0; j < 1024 / UT; ++j) {
             uint4 lo, hi;
-            expand_word(x.x, lo.x, hi.x);
-            expand_word(x.y, lo.y, hi.y);
-            expand_word(x.z, lo.z, hi.z);
-            expand_word(x.w, lo.w, hi.w);
+            expand_word(xb[j].x, lo.x, hi.x);
+            expand_word(xb[j].y, lo.y, hi.y);
+            expand_word(xb[j].z, lo.z, hi.z);
+            expand_word(xb[j].w, lo.w, hi.w);
+            if constexpr (!kBMn) {
+              *reinterpret_cast<uint4*>(b8 + a_dst_lo0 + j * (kARowsPerPass * 128)) = lo;
+              *reinterpret_cast<uint4*>(b8 + a_dst_hi0 + j * (kARowsPerPass * 128)) = hi;
+              continue;
+            }
+            // packed row of this pass: b_p0 + kBRowsPerPass * j  (b_p0 < kBRowsPerPass <= 16)
+            constexpr int R = kBRowsPerPass;
+            const int row_adv = R * j;                       // compile-time after unrolling
+            const int slot_adv = 32 * (row_adv >> 4) + (row_adv & 15);
             if constexpr (kMaskK) {
-              const int k_lo = kb * BK + 2 * pr;
+              const int k_lo = kb * BK + 2 * (b_p0 + row_adv);
               if (k_lo >= w.k_valid) lo = make_uint4(0, 0, 0, 0);
               if (k_lo + 1 >= w.k_valid) hi = make_uint4(0, 0, 0, 0);
             }
-            const int slot = 32 * (pr >> 4) + (pr & 15);
-            const uint32_t d = blk * (T::kB8Bytes / 2) + slot * 128 + ((cn ^ (slot & 7)) << 4);
+            const uint32_t d = b_dst0 + slot_adv * 128;
             *reinterpret_cast<uint4*>(b8 + d) = lo;
             *reinterpret_cast<uint4*>(b8 + d + 16 * 128) = hi;
           }

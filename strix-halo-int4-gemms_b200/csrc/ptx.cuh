@@ -95,6 +95,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const A
   }
 }
 
+// One lane of a converged warp (the same lane every time within a call site is not guaranteed).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xFFFFFFFF;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ----------------------------------------------------------------------------
 // fences
 // ----------------------------------------------------------------------------

@@ -153,8 +153,9 @@ def test_backward_is_deterministic_and_split_k_is_a_no_op(pkg):
         again, _ = _bwd(pkg, [256, 100, 0, 384], 256, 256, k_capacity=384, seed=6, config=pkg.RaggedBwdDotConfig(split_k=split))
         assert torch.equal(first, again)
     with pytest.raises(ValueError, match="group_sizes entries must be <= logical padded K 64; got 65"):
-        z = torch.zeros((2, 32, 16), dtype=torch.uint8, device="cuda")
-        pkg.ragged_dot_int4_bwd(z, z, torch.tensor([65, 1]).cuda())
+        lhs = torch.zeros((2, 16, 32), dtype=torch.uint8, device="cuda")   # [G, M, K/2], K capacity 64
+        rhs = torch.zeros((2, 32, 48), dtype=torch.uint8, device="cuda")   # [G, K/2, N]
+        pkg.ragged_dot_int4_bwd(lhs, rhs, torch.tensor([65, 1]).cuda())
 
 
 def test_ragged_autotune_on_device(pkg):
