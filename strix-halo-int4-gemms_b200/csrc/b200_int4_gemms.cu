@@ -59,7 +59,7 @@ EncodeTiledFn encode_tiled_fn() {
 
 // 2-D byte tensor map: inner extent `inner_bytes` (pitch `pitch_bytes`), `rows` rows.
 int make_map_2d(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_t rows,
-                uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows, bool swizzle128,
+                uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows, int swizzle_bytes,
                 const char* name) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return fail("cuTensorMapEncodeTiled is not available from this CUDA driver");
@@ -69,7 +69,8 @@ int make_map_2d(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64
   const cuuint32_t elem_strides[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
                   elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                       : (swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     return fail(std::string("cuTensorMapEncodeTiled failed for ") + name + " (CUresult " +
@@ -177,19 +178,32 @@ int ensure_device(int device_index, DeviceState** out) {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Output map for the TMA-store epilogue: [rows, n] elements of 2 (bf16) or 4 (f32) bytes, box of
+// 32 rows x 64 bytes, 64-byte swizzle.  Returns 1 in *enabled when the output qualifies.
+int make_output_map(CUtensorMap* map, void* out, int out_dtype, uint64_t rows, uint64_t n, int* enabled) {
+  *enabled = 0;
+  std::memset(map, 0, sizeof(*map));
+  if (out_dtype == OUT_S32) return 0;
+  const uint64_t esize = out_dtype == OUT_F32 ? 4 : 2;
+  if (!aligned16(out) || (n * esize) % 16 != 0) return 0;
+  if (int rc = make_map_2d(map, out, n * esize, rows, n * esize, 64, 32, 64, "C"); rc != 0) return rc;
+  *enabled = 1;
+  return 0;
+}
+
 struct TcLaunch {
   bool int4, a_mn, b_mn, mask_k;
   int scale, epi, out;
 };
 
-int launch_tc(const TcLaunch& l, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
-              int grid, cudaStream_t stream) {
+int launch_tc(const TcLaunch& l, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+              const GemmParams& p, int grid, cudaStream_t stream) {
 #define X(I4, AMN, BMN, SC, EP, OT, MK)                                                              \
   if (l.int4 == I4 && l.a_mn == AMN && l.b_mn == BMN && l.scale == SC && l.epi == EP && l.out == OT &&           \
       l.mask_k == MK) {                                                                          \
     using T = KernelTraits<I4, AMN, BMN, SC, EP, OT, MK>;                                             \
     gemm_i8_tcgen05_kernel<I4, AMN, BMN, SC, EP, OT, MK>                                              \
-        <<<grid, T::kThreads, T::kSmemBytes, stream>>>(ta, tb, p);                               \
+        <<<grid, T::kThreads, T::kSmemBytes, stream>>>(ta, tb, tc, p);                               \
     cudaError_t err = cudaGetLastError();                                                        \
     if (err != cudaSuccess) return fail_cuda("tcgen05 GEMM kernel launch", err);                 \
     return 0;                                                                                    \
@@ -361,25 +375,25 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
   CUtensorMap ta, tb;
   if (int4) {
     if (a_t) {
-      if (int rc = make_map_2d(&ta, a, m, kb, m, NBLK, BK / 2, false, "A"); rc != 0) return rc;
+      if (int rc = make_map_2d(&ta, a, m, kb, m, NBLK, BK / 2, 0, "A"); rc != 0) return rc;
     } else {
-      if (int rc = make_map_2d(&ta, a, kb, m, kb, BK / 2, BM, false, "A"); rc != 0) return rc;
+      if (int rc = make_map_2d(&ta, a, kb, m, kb, BK / 2, BM, 0, "A"); rc != 0) return rc;
     }
     if (b_t) {
-      if (int rc = make_map_2d(&tb, b, kb, b_cols, kb, BK / 2, NBLK, false, "B"); rc != 0) return rc;
+      if (int rc = make_map_2d(&tb, b, kb, b_cols, kb, BK / 2, NBLK, 0, "B"); rc != 0) return rc;
     } else {
-      if (int rc = make_map_2d(&tb, b, b_cols, kb, b_cols, NBLK, BK / 2, false, "B"); rc != 0) return rc;
+      if (int rc = make_map_2d(&tb, b, b_cols, kb, b_cols, NBLK, BK / 2, 0, "B"); rc != 0) return rc;
     }
   } else {
     if (a_t) {
-      if (int rc = make_map_2d(&ta, a, m, kb, m, NBLK, BK, true, "A"); rc != 0) return rc;
+      if (int rc = make_map_2d(&ta, a, m, kb, m, NBLK, BK, 128, "A"); rc != 0) return rc;
     } else {
-      if (int rc = make_map_2d(&ta, a, kb, m, kb, BK, BM, true, "A"); rc != 0) return rc;
+      if (int rc = make_map_2d(&ta, a, kb, m, kb, BK, BM, 128, "A"); rc != 0) return rc;
     }
     if (b_t) {
-      if (int rc = make_map_2d(&tb, b, kb, b_cols, kb, BK, NBLK, true, "B"); rc != 0) return rc;
+      if (int rc = make_map_2d(&tb, b, kb, b_cols, kb, BK, NBLK, 128, "B"); rc != 0) return rc;
     } else {
-      if (int rc = make_map_2d(&tb, b, b_cols, kb, b_cols, NBLK, BK, true, "B"); rc != 0) return rc;
+      if (int rc = make_map_2d(&tb, b, b_cols, kb, b_cols, NBLK, BK, 128, "B"); rc != 0) return rc;
     }
   }
 
@@ -402,9 +416,11 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
   p.b_scale = static_cast<const __nv_bfloat16*>(b_scale);
   p.out = c;
   p.status = dev->status_dev;
+  CUtensorMap tc;
+  if (int rc = make_output_map(&tc, c, v->out_dtype, m, n, &p.tma_store); rc != 0) return rc;
   int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
   if (v->schedule == B200_SCHEDULE_STANDARD) grid = p.num_tiles;
-  int rc = launch_tc(tl, ta, tb, p, grid, stream);
+  int rc = launch_tc(tl, ta, tb, tc, p, grid, stream);
   if (rc < 0) return fail("internal: no tcgen05 instantiation for this variant");
   return rc;
 }
@@ -476,8 +492,8 @@ extern "C" int b200_int4_gemms_launch_ragged_fwd(
   }
 
   CUtensorMap ta, tb;
-  if (int rc = make_map_2d(&ta, lhs, k_packed, m, k_packed, BK / 2, BM, false, "lhs"); rc != 0) return rc;
-  if (int rc = make_map_2d(&tb, rhs, n, static_cast<uint64_t>(groups) * k_packed, n, NBLK, BK / 2, false, "rhs"); rc != 0)
+  if (int rc = make_map_2d(&ta, lhs, k_packed, m, k_packed, BK / 2, BM, 0, "lhs"); rc != 0) return rc;
+  if (int rc = make_map_2d(&tb, rhs, n, static_cast<uint64_t>(groups) * k_packed, n, NBLK, BK / 2, 0, "rhs"); rc != 0)
     return rc;
   GemmParams p{};
   p.mode = MODE_RAGGED_FWD;
@@ -504,8 +520,10 @@ extern "C" int b200_int4_gemms_launch_ragged_fwd(
   p.b_scale = static_cast<const __nv_bfloat16*>(rhs_scale);
   p.out = out;
   p.status = dev->status_dev;
+  CUtensorMap tc;
+  if (int rc = make_output_map(&tc, out, v->out_dtype, m, n, &p.tma_store); rc != 0) return rc;
   const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
-  int rc = launch_tc(tl, ta, tb, p, grid, stream);
+  int rc = launch_tc(tl, ta, tb, tc, p, grid, stream);
   if (rc < 0) return fail("internal: no tcgen05 instantiation for this variant");
   return rc;
 }
@@ -571,13 +589,13 @@ extern "C" int b200_int4_gemms_launch_ragged_bwd(const b200_gemm_variant* v, int
 
   CUtensorMap ta, tb;
   if (a_t) {
-    if (int rc = make_map_2d(&ta, lhs, m, static_cast<uint64_t>(groups) * k_packed, m, NBLK, BK / 2, false, "lhs"); rc != 0)
+    if (int rc = make_map_2d(&ta, lhs, m, static_cast<uint64_t>(groups) * k_packed, m, NBLK, BK / 2, 0, "lhs"); rc != 0)
       return rc;
   } else {
-    if (int rc = make_map_2d(&ta, lhs, k_packed, static_cast<uint64_t>(groups) * m, k_packed, BK / 2, BM, false, "lhs"); rc != 0)
+    if (int rc = make_map_2d(&ta, lhs, k_packed, static_cast<uint64_t>(groups) * m, k_packed, BK / 2, BM, 0, "lhs"); rc != 0)
       return rc;
   }
-  if (int rc = make_map_2d(&tb, rhs, n, static_cast<uint64_t>(groups) * k_packed, n, NBLK, BK / 2, false, "rhs"); rc != 0)
+  if (int rc = make_map_2d(&tb, rhs, n, static_cast<uint64_t>(groups) * k_packed, n, NBLK, BK / 2, 0, "rhs"); rc != 0)
     return rc;
   GemmParams p{};
   p.mode = MODE_RAGGED_BWD;
@@ -602,8 +620,10 @@ extern "C" int b200_int4_gemms_launch_ragged_bwd(const b200_gemm_variant* v, int
   p.b_scale = static_cast<const __nv_bfloat16*>(rhs_scale);
   p.out = out;
   p.status = dev->status_dev;
+  CUtensorMap tc;
+  if (int rc = make_output_map(&tc, out, OUT_F32, static_cast<uint64_t>(groups) * m, n, &p.tma_store); rc != 0) return rc;
   const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
-  int rc = launch_tc(tl, ta, tb, p, grid, stream);
+  int rc = launch_tc(tl, ta, tb, tc, p, grid, stream);
   if (rc < 0) return fail("internal: no tcgen05 instantiation for this variant");
   return rc;
 }

@@ -59,6 +59,7 @@ struct GemmParams {
   int subchannel;        // K-group length for subchannel scales (0 = per-channel)
   int scale_cols;        // number of K-groups (subchannel) per row
   int lds_b;             // pitch (elements) of one b_scale K-group row
+  int tma_store;         // 1: tmap_c describes the output and the epilogue may use TMA stores
   // ragged
   int num_groups;
   int rows_per_group_a;  // rows of the stacked A map per group (bwd)
@@ -84,6 +85,7 @@ struct TileWork {
   int out_row0;      // output row of tile row 0
   int row_lo, row_hi;// valid output rows [lo, hi)
   long long out_off; // element offset added to out (bwd: g*M*N)
+  int out_row_base;  // row offset of the tile's output in the 2-D view [rows, N] (bwd: g*M)
   long long sa_off;  // element offset of this tile's a_scale base
   long long sb_off;  // element offset of this tile's b_scale base
 };
@@ -93,6 +95,7 @@ __device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t) {
   TileWork w;
   w.k_valid = 0x7FFFFFFF;
   w.out_off = 0;
+  w.out_row_base = 0;
   w.sa_off = 0;
   w.sb_off = 0;
   if (p.mode == MODE_DENSE) {
@@ -149,6 +152,7 @@ __device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t) {
     w.row_lo = w.out_row0;
     w.row_hi = min(p.M, w.out_row0 + BM);
     w.out_off = static_cast<long long>(g) * p.M * p.ldc;
+    w.out_row_base = g * p.M;
     w.sa_off = static_cast<long long>(g) * p.M * (p.subchannel ? p.scale_cols : 1);
     w.sb_off = static_cast<long long>(g) * p.lds_b * (p.subchannel ? p.scale_cols : 1);
   }
@@ -187,14 +191,18 @@ struct KernelTraits {
   static constexpr int kPkBBytes = BN * BK / 2;   // 16 KB
   static constexpr int kPkStageBytes = kPkABytes + kPkBBytes;
   static constexpr int kBarBytes = 512;
+  // results leave through shared memory + TMA stores (per-channel kernels; 2 KB per epilogue warp)
+  static constexpr bool kTmaStore = (kScale == SCALE_PC) && (kOut != OUT_S32);
+  static constexpr int kStagingBytes = kTmaStore ? 4 * 2048 : 0;
   static constexpr int kSmemBytes =
-      1024 + kStages * kStageBytes + kPkStages * kPkStageBytes + kBarBytes;
+      1024 + kStages * kStageBytes + kPkStages * kPkStageBytes + kStagingBytes + kBarBytes;
 };
 
 template <bool kInt4, bool kAMn, bool kBMn, int kScale, int kEpi, int kOut, bool kMaskK>
 __global__ void __launch_bounds__(KernelTraits<kInt4, kAMn, kBMn, kScale, kEpi, kOut, kMaskK>::kThreads, 1)
 gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                       const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+                       const __grid_constant__ CUtensorMap tmap_b,
+                       const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
   using T = KernelTraits<kInt4, kAMn, kBMn, kScale, kEpi, kOut, kMaskK>;
   static_assert(kBMn || !kMaskK, "K masking is applied to an MN-major B operand");
   constexpr int S = T::kStages;
@@ -203,11 +211,11 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  // layout: [S x (A8 | B8)] [PS x (pkA | pkB)] [barriers]
+  // layout: [S x (A8 | B8)] [PS x (pkA | pkB)] [output staging] [barriers]
   const uint32_t stage_base = smem_base;
   const uint32_t pk_base = stage_base + S * T::kStageBytes;
-  const uint32_t bar_base = pk_base + PS * T::kPkStageBytes;
-  uint8_t* bar_gen = smem_gen + S * T::kStageBytes + PS * T::kPkStageBytes;
+  const uint32_t bar_base = pk_base + PS * T::kPkStageBytes + T::kStagingBytes;
+  uint8_t* bar_gen = smem_gen + S * T::kStageBytes + PS * T::kPkStageBytes + T::kStagingBytes;
 
   // barrier slots (8 bytes each)
   static_assert(S <= 8 && PS <= 8, "barrier slots are laid out for at most 8 stages");
@@ -223,6 +231,9 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   AbortCtx ctx{abort_flag, p.status};
+  // per-epilogue-warp 2 KB staging buffer of the TMA store path (warps 2..5 -> slots 0..3)
+  uint8_t* stage_out = smem_gen + S * T::kStageBytes + PS * T::kPkStageBytes + ((warp - 2) & 3) * 2048;
+  const uint32_t stage_out_u32 = stage_base + S * T::kStageBytes + PS * T::kPkStageBytes + ((warp - 2) & 3) * 2048;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -433,29 +444,18 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if constexpr (kScale == SCALE_PC) {
         float sa = 0.f;
         if (row_ok) sa = __bfloat162float(p.a_scale[sa_row]);
-        if (w.num_kb == 0) {
-          // nothing to reduce (empty group): the result is zero
-          if (row_ok) {
-#pragma unroll 1
-            for (int c = 0; c < 8; ++c) {
-              const int col0 = w.n0 + 32 * c;
-              for (int i = 0; i < 32; ++i) {
-                const int col = col0 + i;
-                if (col < p.N) {
-                  const long long o = w.out_off + static_cast<long long>(row) * p.ldc + col;
-                  if constexpr (kOut == OUT_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(0.f);
-                  else if constexpr (kOut == OUT_F32) reinterpret_cast<float*>(p.out)[o] = 0.f;
-                  else reinterpret_cast<int*>(p.out)[o] = 0;
-                }
-              }
-            }
-          }
-          continue;
+        const bool zero_tile = (w.num_kb == 0);  // nothing to reduce (empty group): the result is zero
+        int b = 0;
+        if (!zero_tile) {
+          b = grp & 1;
+          if (!__all_sync(0xFFFFFFFFu, mbar_wait(acc_full_bar(b), (grp >> 1) & 1, ctx, 30))) { ok = false; break; }
+          tc_fence_after_sync();
         }
-        const int b = grp & 1;
-        const uint32_t aph = (grp >> 1) & 1;
-        if (!__all_sync(0xFFFFFFFFu, mbar_wait(acc_full_bar(b), aph, ctx, 30))) { ok = false; break; }
-        tc_fence_after_sync();
+        // TMA store path: the warp's 32 rows must all be rows this tile owns (rows past the end of a
+        // dense output are clipped by the tensor map itself)
+        const int wrow0 = w.out_row0 + q * 32;
+        const bool use_tma = T::kTmaStore && p.tma_store != 0 &&
+                             (p.mode == MODE_DENSE || (wrow0 >= w.row_lo && wrow0 + 32 <= w.row_hi));
 #ifdef B200_DBG_SKIP_EPILOGUE
         constexpr int kOutChunks = 0;
 #else
@@ -465,8 +465,13 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         for (int c = 0; c < kOutChunks; ++c) {
           uint32_t r[32];
           float v[32];
-          tmem_ld_32x32b_x32(tmem_base + lane_addr + b * BN + 32 * c, r);
-          tmem_ld_wait();
+          if (!zero_tile) {
+            tmem_ld_32x32b_x32(tmem_base + lane_addr + b * BN + 32 * c, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
           const int col0 = w.n0 + 32 * c;  // output column of this chunk
           if constexpr (kOut == OUT_S32) {
             if (row_ok) {
@@ -480,80 +485,138 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
               }
             }
-            continue;
-          }
-          if constexpr (kOut != OUT_S32) {
-          // scales for the columns (uniform across the warp -> broadcast loads)
+          } else {
+            // column scales: the same 32 values for every lane (broadcast loads), vectorised when aligned
+            float sbv[32];
+            const long long sb_idx = w.sb_off + col0;
+            if (col0 + 32 <= p.N && (sb_idx & 7) == 0) {
+              const uint4* src = reinterpret_cast<const uint4*>(p.b_scale + sb_idx);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = col0 + i;
-            int a = static_cast<int>(r[i]);
-            if constexpr (kInt4) a >>= 8;
-            float sb = (col < p.N) ? __bfloat162float(p.b_scale[w.sb_off + col]) : 0.f;
-            v[i] = __fmul_rn(__fmul_rn(static_cast<float>(a), sa), sb);
-          }
-          if constexpr (kEpi == EPI_SWIGLU) {
-            uint32_t g[32];
-            tmem_ld_32x32b_x32(tmem_base + lane_addr + b * BN + NBLK + 32 * c, g);
-            tmem_ld_wait();
+              for (int i = 0; i < 4; ++i) {
+                const uint4 x = __ldg(src + i);
+                const uint32_t ws[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                for (int k2 = 0; k2 < 4; ++k2) {
+                  sbv[8 * i + 2 * k2] = __uint_as_float(ws[k2] << 16);
+                  sbv[8 * i + 2 * k2 + 1] = __uint_as_float(ws[k2] & 0xFFFF0000u);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) sbv[i] = (col0 + i < p.N) ? __bfloat162float(p.b_scale[sb_idx + i]) : 0.f;
+            }
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              const int col = col0 + i;
-              int a = static_cast<int>(g[i]);
+              int a = static_cast<int>(r[i]);
               if constexpr (kInt4) a >>= 8;
-              float sb = (col < p.N) ? __bfloat162float(p.b_scale[w.sb_off + p.gate_col_offset + col]) : 0.f;
-              const float gate = __fmul_rn(__fmul_rn(static_cast<float>(a), sa), sb);
-              v[i] = v[i] * (gate / (1.0f + __expf(-gate)));
+              v[i] = __fmul_rn(__fmul_rn(static_cast<float>(a), sa), sbv[i]);
             }
-          } else if constexpr (kEpi == EPI_RELU2) {
+            if constexpr (kEpi == EPI_SWIGLU) {
+              uint32_t g[32];
+              tmem_ld_32x32b_x32(tmem_base + lane_addr + b * BN + NBLK + 32 * c, g);
+              tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float x = fmaxf(v[i], 0.f);
-              v[i] = x * x;
+              for (int i = 0; i < 32; ++i) {
+                const int col = col0 + i;
+                int a = static_cast<int>(g[i]);
+                if constexpr (kInt4) a >>= 8;
+                float sb = (col < p.N) ? __bfloat162float(p.b_scale[w.sb_off + p.gate_col_offset + col]) : 0.f;
+                const float gate = __fmul_rn(__fmul_rn(static_cast<float>(a), sa), sb);
+                v[i] = v[i] * (gate / (1.0f + __expf(-gate)));
+              }
+            } else if constexpr (kEpi == EPI_RELU2) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const float x = fmaxf(v[i], 0.f);
+                v[i] = x * x;
+              }
             }
-          }
-          if (row_ok) {
-            const long long o = w.out_off + static_cast<long long>(row) * p.ldc + col0;
-            if constexpr (kOut == OUT_BF16) {
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + o;
-              if (col0 + 32 <= p.N && (p.ldc % 8 == 0)) {
+            if (zero_tile) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = 0.f;
+            }
+            if (use_tma) {
+              // stage 32 rows x 64 bytes in shared memory (64-byte swizzle: chunk ^ ((row >> 1) & 3)),
+              // then one TMA store writes whole lines; columns past N are clipped by the tensor map
+              uint8_t* dst = stage_out + lane * 64;
+              const int sw = (lane >> 1) & 3;
+              constexpr int kHalves = (kOut == OUT_F32) ? 2 : 1;
+#pragma unroll
+              for (int h = 0; h < kHalves; ++h) {
+                if (lane == 0) bulk_wait_read_all();
+                __syncwarp();
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                   uint4 pk;
-                  __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i + 0], v[8 * i + 1]);
-                  __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
-                  __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
-                  __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
-                  pk.x = *reinterpret_cast<uint32_t*>(&h0);
-                  pk.y = *reinterpret_cast<uint32_t*>(&h1);
-                  pk.z = *reinterpret_cast<uint32_t*>(&h2);
-                  pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                  reinterpret_cast<uint4*>(dst)[i] = pk;
+                  if constexpr (kOut == OUT_BF16) {
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i + 0], v[8 * i + 1]);
+                    __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
+                    __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
+                    pk.x = *reinterpret_cast<uint32_t*>(&h0);
+                    pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                    pk.z = *reinterpret_cast<uint32_t*>(&h2);
+                    pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                  } else {
+                    pk.x = __float_as_uint(v[16 * h + 4 * i + 0]);
+                    pk.y = __float_as_uint(v[16 * h + 4 * i + 1]);
+                    pk.z = __float_as_uint(v[16 * h + 4 * i + 2]);
+                    pk.w = __float_as_uint(v[16 * h + 4 * i + 3]);
+                  }
+                  *reinterpret_cast<uint4*>(dst + ((i ^ sw) << 4)) = pk;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                  const int xbytes = (kOut == OUT_BF16) ? col0 * 2 : (col0 + 16 * h) * 4;
+                  tma_store_2d(&tmap_c, stage_out_u32, xbytes, w.out_row_base + wrow0);
+                  bulk_commit_group();
+                }
+              }
+            } else if (row_ok) {
+              const long long o = w.out_off + static_cast<long long>(row) * p.ldc + col0;
+              if constexpr (kOut == OUT_BF16) {
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + o;
+                if (col0 + 32 <= p.N && (p.ldc % 8 == 0)) {
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    uint4 pk;
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i + 0], v[8 * i + 1]);
+                    __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
+                    __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
+                    pk.x = *reinterpret_cast<uint32_t*>(&h0);
+                    pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                    pk.z = *reinterpret_cast<uint32_t*>(&h2);
+                    pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                    reinterpret_cast<uint4*>(dst)[i] = pk;
+                  }
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i)
+                    if (col0 + i < p.N) dst[i] = __float2bfloat16_rn(v[i]);
                 }
               } else {
+                float* dst = reinterpret_cast<float*>(p.out) + o;
+                if (col0 + 32 <= p.N && (p.ldc % 4 == 0)) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                  if (col0 + i < p.N) dst[i] = __float2bfloat16_rn(v[i]);
-              }
-            } else {
-              float* dst = reinterpret_cast<float*>(p.out) + o;
-              if (col0 + 32 <= p.N && (p.ldc % 4 == 0)) {
+                  for (int i = 0; i < 8; ++i)
+                    reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                } else {
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                  reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-              } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                  if (col0 + i < p.N) dst[i] = v[i];
+                  for (int i = 0; i < 32; ++i)
+                    if (col0 + i < p.N) dst[i] = v[i];
+                }
               }
             }
           }
-          }  // kOut != OUT_S32
         }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(acc_empty_bar(b));
-        ++grp;
+        if (!zero_tile) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty_bar(b));
+          ++grp;
+        }
       } else {
         // ---------------------------------------------------------------- subchannel scales
         float acc[kOwnCols];
@@ -641,6 +704,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
+    if (lane == 0) bulk_wait_all();  // TMA stores issued by this lane have landed
   } else {
     // ------------------------------------------------------------------ unpack (int4 only)
     if constexpr (kInt4) {
