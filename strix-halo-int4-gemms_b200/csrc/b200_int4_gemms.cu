@@ -179,14 +179,16 @@ int ensure_device(int device_index, DeviceState** out) {
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Output map for the TMA-store epilogue: [rows, n] elements of 2 (bf16) or 4 (f32) bytes, box of
-// 32 rows x 64 bytes, 64-byte swizzle.  Returns 1 in *enabled when the output qualifies.
+// 32 rows x 32 columns (64 or 128 bytes, swizzle of the same width).  Returns 1 in *enabled when the output qualifies.
 int make_output_map(CUtensorMap* map, void* out, int out_dtype, uint64_t rows, uint64_t n, int* enabled) {
   *enabled = 0;
   std::memset(map, 0, sizeof(*map));
   if (out_dtype == OUT_S32) return 0;
   const uint64_t esize = out_dtype == OUT_F32 ? 4 : 2;
   if (!aligned16(out) || (n * esize) % 16 != 0) return 0;
-  if (int rc = make_map_2d(map, out, n * esize, rows, n * esize, 64, 32, 64, "C"); rc != 0) return rc;
+  // bf16: 32 columns = 64 bytes per row; f32: 32 columns = 128 bytes per row
+  const uint32_t inner = out_dtype == OUT_F32 ? 128 : 64;
+  if (int rc = make_map_2d(map, out, n * esize, rows, n * esize, inner, 32, static_cast<int>(inner), "C"); rc != 0) return rc;
   *enabled = 1;
   return 0;
 }

@@ -174,7 +174,7 @@ struct KernelTraits {
 #define B200_INT4_STAGES 3
 #endif
 #ifndef B200_INT4_PK_STAGES
-#define B200_INT4_PK_STAGES 3
+#define B200_INT4_PK_STAGES 2
 #endif
   static constexpr int kUnpackWarps = kInt4 ? B200_UNPACK_WARPS : 0;
   static constexpr int kEpiWarps = (kScale == SCALE_SC) ? 8 : 4;
@@ -193,9 +193,11 @@ struct KernelTraits {
   static constexpr int kBarBytes = 512;
   // results leave through shared memory + TMA stores (per-channel kernels; 2 KB per epilogue warp)
   static constexpr bool kTmaStore = (kScale == SCALE_PC) && (kOut != OUT_S32);
-  static constexpr int kStagingBytes = kTmaStore ? 4 * 2048 : 0;
+  static constexpr int kStagingSlots = 2;  // per warp: the next chunk is staged while TMA still reads the previous one
+  static constexpr int kStagingBytes = kTmaStore ? 4 * kStagingSlots * 2048 : 0;
+  static constexpr int kScaleStripBytes = (kScale == SCALE_PC) ? 4 * 1024 : 0;  // 256 fp32 column scales per epilogue warp
   static constexpr int kSmemBytes =
-      1024 + kStages * kStageBytes + kPkStages * kPkStageBytes + kStagingBytes + kBarBytes;
+      1024 + kStages * kStageBytes + kPkStages * kPkStageBytes + kStagingBytes + kScaleStripBytes + kBarBytes;
 };
 
 template <bool kInt4, bool kAMn, bool kBMn, int kScale, int kEpi, int kOut, bool kMaskK>
@@ -211,11 +213,11 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  // layout: [S x (A8 | B8)] [PS x (pkA | pkB)] [output staging] [barriers]
+  // layout: [S x (A8 | B8)] [PS x (pkA | pkB)] [output staging] [column-scale strips] [barriers]
   const uint32_t stage_base = smem_base;
   const uint32_t pk_base = stage_base + S * T::kStageBytes;
-  const uint32_t bar_base = pk_base + PS * T::kPkStageBytes + T::kStagingBytes;
-  uint8_t* bar_gen = smem_gen + S * T::kStageBytes + PS * T::kPkStageBytes + T::kStagingBytes;
+  const uint32_t bar_base = pk_base + PS * T::kPkStageBytes + T::kStagingBytes + T::kScaleStripBytes;
+  uint8_t* bar_gen = smem_gen + S * T::kStageBytes + PS * T::kPkStageBytes + T::kStagingBytes + T::kScaleStripBytes;
 
   // barrier slots (8 bytes each)
   static_assert(S <= 8 && PS <= 8, "barrier slots are laid out for at most 8 stages");
@@ -232,8 +234,9 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int lane = threadIdx.x & 31;
   AbortCtx ctx{abort_flag, p.status};
   // per-epilogue-warp 2 KB staging buffer of the TMA store path (warps 2..5 -> slots 0..3)
-  uint8_t* stage_out = smem_gen + S * T::kStageBytes + PS * T::kPkStageBytes + ((warp - 2) & 3) * 2048;
-  const uint32_t stage_out_u32 = stage_base + S * T::kStageBytes + PS * T::kPkStageBytes + ((warp - 2) & 3) * 2048;
+  uint8_t* stage_out = smem_gen + S * T::kStageBytes + PS * T::kPkStageBytes + ((warp - 2) & 3) * (T::kStagingSlots * 2048);
+  float* sb_strip = reinterpret_cast<float*>(smem_gen + S * T::kStageBytes + PS * T::kPkStageBytes + T::kStagingBytes + ((warp - 2) & 3) * 1024);
+  const uint32_t stage_out_u32 = stage_base + S * T::kStageBytes + PS * T::kPkStageBytes + ((warp - 2) & 3) * (T::kStagingSlots * 2048);
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -415,6 +418,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int row_in_tile = q * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     int grp = 0;
+    int store_count = 0;  // TMA stores issued by this warp (selects the staging slot)
     bool ok = true;
     // Columns of the 256-wide accumulator this warp owns:
     //   per-channel, 4 warps: all 256 (SwiGLU: up 0..127 with gate 128..255)
@@ -443,8 +447,36 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
       if constexpr (kScale == SCALE_PC) {
         float sa = 0.f;
-        if (row_ok) sa = __bfloat162float(p.a_scale[sa_row]);
+        if constexpr (kOut != OUT_S32) {
+          if (row_ok) sa = __bfloat162float(p.a_scale[sa_row]);
+        }
         const bool zero_tile = (w.num_kb == 0);  // nothing to reduce (empty group): the result is zero
+        // Column scales of the tile, once per tile, into this warp's strip of shared memory as fp32
+        // (lane l brings the 8 columns 8l..8l+7 of the 256-wide accumulator).  One global-load
+        // latency per tile, overlapped with the wait for the accumulator.
+        if constexpr (kOut != OUT_S32) {
+          const int tc = 8 * lane;
+          const int bcol = (tc < NBLK) ? (w.n0 + tc) : (w.n1 + tc - NBLK);                 // column of b_scale
+          const int ocol = (tc < NBLK || kEpi != EPI_SWIGLU) ? (w.n0 + tc) : (w.n0 + tc - NBLK);  // output column
+          const long long idx = w.sb_off + bcol;
+          float f[8];
+          if (ocol + 8 <= p.N && (idx & 7) == 0) {
+            const uint4 x = __ldg(reinterpret_cast<const uint4*>(p.b_scale + idx));
+            const uint32_t ws[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+            for (int k2 = 0; k2 < 4; ++k2) {
+              f[2 * k2] = __uint_as_float(ws[k2] << 16);
+              f[2 * k2 + 1] = __uint_as_float(ws[k2] & 0xFFFF0000u);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = (ocol + i < p.N) ? __bfloat162float(p.b_scale[idx + i]) : 0.f;
+          }
+          __syncwarp();  // every lane is done reading the previous tile's scales
+          reinterpret_cast<float4*>(sb_strip)[2 * lane] = make_float4(f[0], f[1], f[2], f[3]);
+          reinterpret_cast<float4*>(sb_strip)[2 * lane + 1] = make_float4(f[4], f[5], f[6], f[7]);
+          __syncwarp();
+        }
         int b = 0;
         if (!zero_tile) {
           b = grp & 1;
@@ -456,22 +488,10 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int wrow0 = w.out_row0 + q * 32;
         const bool use_tma = T::kTmaStore && p.tma_store != 0 &&
                              (p.mode == MODE_DENSE || (wrow0 >= w.row_lo && wrow0 + 32 <= w.row_hi));
-#ifdef B200_DBG_SKIP_EPILOGUE
-        constexpr int kOutChunks = 0;
-#else
-        constexpr int kOutChunks = (kEpi == EPI_SWIGLU) ? 4 : 8;
-#endif
-#pragma unroll 1
-        for (int c = 0; c < kOutChunks; ++c) {
-          uint32_t r[32];
-          float v[32];
-          if (!zero_tile) {
-            tmem_ld_32x32b_x32(tmem_base + lane_addr + b * BN + 32 * c, r);
-            tmem_ld_wait();
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = 0u;
-          }
+        const uint32_t acc_addr = tmem_base + lane_addr + b * BN;
+
+        // one 32-column chunk: scale, activation, store
+        auto process = [&](uint32_t (&r)[32], int c) {
           const int col0 = w.n0 + 32 * c;  // output column of this chunk
           if constexpr (kOut == OUT_S32) {
             if (row_ok) {
@@ -486,42 +506,27 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               }
             }
           } else {
-            // column scales: the same 32 values for every lane (broadcast loads), vectorised when aligned
-            float sbv[32];
-            const long long sb_idx = w.sb_off + col0;
-            if (col0 + 32 <= p.N && (sb_idx & 7) == 0) {
-              const uint4* src = reinterpret_cast<const uint4*>(p.b_scale + sb_idx);
+            float v[32];
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const uint4 x = __ldg(src + i);
-                const uint32_t ws[4] = {x.x, x.y, x.z, x.w};
+            for (int i4 = 0; i4 < 8; ++i4) {
+              const float4 sb4 = reinterpret_cast<const float4*>(sb_strip)[8 * c + i4];  // broadcast read
+              const float sbv[4] = {sb4.x, sb4.y, sb4.z, sb4.w};
 #pragma unroll
-                for (int k2 = 0; k2 < 4; ++k2) {
-                  sbv[8 * i + 2 * k2] = __uint_as_float(ws[k2] << 16);
-                  sbv[8 * i + 2 * k2 + 1] = __uint_as_float(ws[k2] & 0xFFFF0000u);
-                }
+              for (int k2 = 0; k2 < 4; ++k2) {
+                int a = static_cast<int>(r[4 * i4 + k2]);
+                if constexpr (kInt4) a >>= 8;
+                v[4 * i4 + k2] = __fmul_rn(__fmul_rn(static_cast<float>(a), sa), sbv[k2]);
               }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) sbv[i] = (col0 + i < p.N) ? __bfloat162float(p.b_scale[sb_idx + i]) : 0.f;
-            }
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              int a = static_cast<int>(r[i]);
-              if constexpr (kInt4) a >>= 8;
-              v[i] = __fmul_rn(__fmul_rn(static_cast<float>(a), sa), sbv[i]);
             }
             if constexpr (kEpi == EPI_SWIGLU) {
               uint32_t g[32];
-              tmem_ld_32x32b_x32(tmem_base + lane_addr + b * BN + NBLK + 32 * c, g);
+              tmem_ld_32x32b_x32(acc_addr + NBLK + 32 * c, g);
               tmem_ld_wait();
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
-                const int col = col0 + i;
                 int a = static_cast<int>(g[i]);
                 if constexpr (kInt4) a >>= 8;
-                float sb = (col < p.N) ? __bfloat162float(p.b_scale[w.sb_off + p.gate_col_offset + col]) : 0.f;
-                const float gate = __fmul_rn(__fmul_rn(static_cast<float>(a), sa), sb);
+                const float gate = __fmul_rn(__fmul_rn(static_cast<float>(a), sa), sb_strip[NBLK + 32 * c + i]);
                 v[i] = v[i] * (gate / (1.0f + __expf(-gate)));
               }
             } else if constexpr (kEpi == EPI_RELU2) {
@@ -531,45 +536,57 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 v[i] = x * x;
               }
             }
-            if (zero_tile) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = 0.f;
-            }
+#ifdef B200_DBG_NO_STORE
+            if (v[0] == 123.456f)
+#endif
             if (use_tma) {
-              // stage 32 rows x 64 bytes in shared memory (64-byte swizzle: chunk ^ ((row >> 1) & 3)),
-              // then one TMA store writes whole lines; columns past N are clipped by the tensor map
-              uint8_t* dst = stage_out + lane * 64;
-              const int sw = (lane >> 1) & 3;
-              constexpr int kHalves = (kOut == OUT_F32) ? 2 : 1;
-#pragma unroll
-              for (int h = 0; h < kHalves; ++h) {
-                if (lane == 0) bulk_wait_read_all();
+              // stage 32 rows in shared memory, then one TMA store writes whole lines; columns past N
+              // are clipped by the tensor map.  bf16: 64 B per row, two 2 KB slots, 64-byte swizzle
+              // (chunk ^ ((row >> 1) & 3)).  fp32: 128 B per row, one 4 KB slot, 128-byte swizzle.
+              if constexpr (kOut == OUT_BF16) {
+                const int slot = store_count & 1;
+                ++store_count;
+                uint8_t* dst = stage_out + slot * 2048 + lane * 64;
+                const int sw = (lane >> 1) & 3;
+                if (lane == 0) bulk_wait_read_keep1();
                 __syncwarp();
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                   uint4 pk;
-                  if constexpr (kOut == OUT_BF16) {
-                    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i + 0], v[8 * i + 1]);
-                    __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
-                    __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
-                    pk.x = *reinterpret_cast<uint32_t*>(&h0);
-                    pk.y = *reinterpret_cast<uint32_t*>(&h1);
-                    pk.z = *reinterpret_cast<uint32_t*>(&h2);
-                    pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                  } else {
-                    pk.x = __float_as_uint(v[16 * h + 4 * i + 0]);
-                    pk.y = __float_as_uint(v[16 * h + 4 * i + 1]);
-                    pk.z = __float_as_uint(v[16 * h + 4 * i + 2]);
-                    pk.w = __float_as_uint(v[16 * h + 4 * i + 3]);
-                  }
+                  __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i + 0], v[8 * i + 1]);
+                  __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
+                  __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
+                  __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
+                  pk.x = *reinterpret_cast<uint32_t*>(&h0);
+                  pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                  pk.z = *reinterpret_cast<uint32_t*>(&h2);
+                  pk.w = *reinterpret_cast<uint32_t*>(&h3);
                   *reinterpret_cast<uint4*>(dst + ((i ^ sw) << 4)) = pk;
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                  const int xbytes = (kOut == OUT_BF16) ? col0 * 2 : (col0 + 16 * h) * 4;
-                  tma_store_2d(&tmap_c, stage_out_u32, xbytes, w.out_row_base + wrow0);
+                  tma_store_2d(&tmap_c, stage_out_u32 + slot * 2048, col0 * 2, w.out_row_base + wrow0);
+                  bulk_commit_group();
+                }
+              } else {
+                uint8_t* dst = stage_out + lane * 128;
+                const int sw = lane & 7;
+                if (lane == 0) bulk_wait_read_all();
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  uint4 pk;
+                  pk.x = __float_as_uint(v[4 * i + 0]);
+                  pk.y = __float_as_uint(v[4 * i + 1]);
+                  pk.z = __float_as_uint(v[4 * i + 2]);
+                  pk.w = __float_as_uint(v[4 * i + 3]);
+                  *reinterpret_cast<uint4*>(dst + ((i ^ sw) << 4)) = pk;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                  tma_store_2d(&tmap_c, stage_out_u32, col0 * 4, w.out_row_base + wrow0);
                   bulk_commit_group();
                 }
               }
@@ -610,6 +627,30 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               }
             }
           }
+        };
+
+#ifdef B200_DBG_SKIP_EPILOGUE
+        constexpr int kOutChunks = 0;
+#else
+        constexpr int kOutChunks = (kEpi == EPI_SWIGLU) ? 4 : 8;
+#endif
+        // two register sets: the TMEM read of the next chunk is in flight while this one is processed
+        uint32_t ra[32], rb[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { ra[i] = 0u; rb[i] = 0u; }
+        if (!zero_tile && kOutChunks > 0) tmem_ld_32x32b_x32(acc_addr, ra);
+#pragma unroll 1
+        for (int c = 0; c < kOutChunks; c += 2) {
+          if (!zero_tile) {
+            tmem_ld_wait();
+            tmem_ld_32x32b_x32(acc_addr + 32 * (c + 1), rb);
+          }
+          process(ra, c);
+          if (!zero_tile) {
+            tmem_ld_wait();
+            if (c + 2 < kOutChunks) tmem_ld_32x32b_x32(acc_addr + 32 * (c + 2), ra);
+          }
+          process(rb, c + 1);
         }
         if (!zero_tile) {
           tc_fence_before_sync();
