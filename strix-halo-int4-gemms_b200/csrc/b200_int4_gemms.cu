@@ -167,7 +167,16 @@ int ensure_device(int device_index, DeviceState** out) {
 #define X(I4, AMN, BMN, SC, EP, OT, MK)                                                             \
   err = set_smem(gemm_i8_tcgen05_kernel<I4, AMN, BMN, SC, EP, OT, MK>,                               \
                  KernelTraits<I4, AMN, BMN, SC, EP, OT, MK>::kSmemBytes);                            \
-  if (err != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(max dynamic shared memory)", err);
+  if (err != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(max dynamic shared memory)", err);   \
+  if (KernelTraits<I4, AMN, BMN, SC, EP, OT, MK>::kRegPoolNeeded > 0) {                                  \
+    /* setmaxnreg.inc would wait for ever if the CTA's register pool were smaller than the roles ask for */ \
+    cudaFuncAttributes attr;                                                                             \
+    err = cudaFuncGetAttributes(&attr, gemm_i8_tcgen05_kernel<I4, AMN, BMN, SC, EP, OT, MK>);           \
+    if (err != cudaSuccess) return fail_cuda("cudaFuncGetAttributes", err);                              \
+    if (attr.numRegs * KernelTraits<I4, AMN, BMN, SC, EP, OT, MK>::kThreads <                            \
+        KernelTraits<I4, AMN, BMN, SC, EP, OT, MK>::kRegPoolNeeded)                                      \
+      return fail("a subchannel kernel was compiled with too few registers for its register re-balance"); \
+  }
     B200_FOR_EACH_TC_KERNEL(X)
 #undef X
     st.ready = true;

@@ -176,9 +176,19 @@ struct KernelTraits {
 #ifndef B200_INT4_PK_STAGES
 #define B200_INT4_PK_STAGES 2
 #endif
-  static constexpr int kUnpackWarps = kInt4 ? B200_UNPACK_WARPS : 0;
+  // Subchannel kernels re-balance registers between roles with setmaxnreg, which works on warpgroups
+  // (4 consecutive warps): warps 0..3 = TMA, MMA and two idle warps, 4..11 = epilogue, 12..15 = unpack.
+  static constexpr bool kRegBalance = (kScale == SCALE_SC);
+  static constexpr int kUnpackWarps = kInt4 ? (kRegBalance ? 4 : B200_UNPACK_WARPS) : 0;
   static constexpr int kEpiWarps = (kScale == SCALE_SC) ? 8 : 4;
-  static constexpr int kThreads = (2 + kEpiWarps + kUnpackWarps) * 32;
+  static constexpr int kEpiWarp0 = kRegBalance ? 4 : 2;
+  static constexpr int kUnpackWarp0 = kEpiWarp0 + kEpiWarps;
+  static constexpr int kThreads = (kUnpackWarp0 + kUnpackWarps) * 32;
+  static constexpr int kRegsLight = 48;    // TMA / MMA warpgroup
+  static constexpr int kRegsUnpack = 80;
+  static constexpr int kRegsEpilogue = 184;
+  // registers the CTA needs after the re-balance; the host checks this against regs-per-thread x threads
+  static constexpr int kRegPoolNeeded = kRegBalance ? (128 * kRegsLight + 256 * kRegsEpilogue + kUnpackWarps * 32 * kRegsUnpack) : 0;
 #ifndef B200_INT8_STAGES
 #define B200_INT8_STAGES 4
 #endif
@@ -192,10 +202,13 @@ struct KernelTraits {
   static constexpr int kPkStageBytes = kPkABytes + kPkBBytes;
   static constexpr int kBarBytes = 512;
   // results leave through shared memory + TMA stores (per-channel kernels; 2 KB per epilogue warp)
-  static constexpr bool kTmaStore = (kScale == SCALE_PC) && (kOut != OUT_S32);
-  static constexpr int kStagingSlots = 2;  // per warp: the next chunk is staged while TMA still reads the previous one
-  static constexpr int kStagingBytes = kTmaStore ? 4 * kStagingSlots * 2048 : 0;
-  static constexpr int kScaleStripBytes = (kScale == SCALE_PC) ? 4 * 1024 : 0;  // 256 fp32 column scales per epilogue warp
+  static constexpr bool kTmaStore = (kScale == SCALE_PC) ? (kOut != OUT_S32) : (kOut == OUT_BF16);
+  static constexpr int kStagingSlots = 2;
+  // per-channel: per warp 2 slots x 2 KB (bf16) or 1 x 4 KB (fp32); subchannel: 2 KB per warp
+  static constexpr int kStagingPerWarp = (kScale == SCALE_PC) ? kStagingSlots * 2048 : 2048;
+  static constexpr int kStagingBytes = kTmaStore ? kEpiWarps * kStagingPerWarp : 0;
+  // column scales as fp32: per-channel 256 per warp; subchannel 2 x 128 per warp (double-buffered by K-group)
+  static constexpr int kScaleStripBytes = kEpiWarps * 1024;
   static constexpr int kSmemBytes =
       1024 + kStages * kStageBytes + kPkStages * kPkStageBytes + kStagingBytes + kScaleStripBytes + kBarBytes;
 };
@@ -234,9 +247,10 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int lane = threadIdx.x & 31;
   AbortCtx ctx{abort_flag, p.status};
   // per-epilogue-warp 2 KB staging buffer of the TMA store path (warps 2..5 -> slots 0..3)
-  uint8_t* stage_out = smem_gen + S * T::kStageBytes + PS * T::kPkStageBytes + ((warp - 2) & 3) * (T::kStagingSlots * 2048);
-  float* sb_strip = reinterpret_cast<float*>(smem_gen + S * T::kStageBytes + PS * T::kPkStageBytes + T::kStagingBytes + ((warp - 2) & 3) * 1024);
-  const uint32_t stage_out_u32 = stage_base + S * T::kStageBytes + PS * T::kPkStageBytes + ((warp - 2) & 3) * (T::kStagingSlots * 2048);
+  const int epi_slot = (warp - T::kEpiWarp0) & (T::kEpiWarps - 1);
+  uint8_t* stage_out = smem_gen + S * T::kStageBytes + PS * T::kPkStageBytes + epi_slot * T::kStagingPerWarp;
+  float* sb_strip = reinterpret_cast<float*>(smem_gen + S * T::kStageBytes + PS * T::kPkStageBytes + T::kStagingBytes + epi_slot * 1024);
+  const uint32_t stage_out_u32 = stage_base + S * T::kStageBytes + PS * T::kPkStageBytes + epi_slot * T::kStagingPerWarp;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -264,6 +278,9 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if constexpr (T::kRegBalance) {
+    if (warp < 4) reg_dealloc<T::kRegsLight>();  // all four warps of warpgroup 0, the idle ones included
+  }
 
   // K-groups: number of K=32 MMA steps between accumulator hand-overs to the epilogue.
   // Per-channel: the whole tile is one group.
@@ -410,9 +427,10 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
-  } else if (warp < 2 + T::kEpiWarps) {
+  } else if (warp >= T::kEpiWarp0 && warp < T::kUnpackWarp0) {
     // ------------------------------------------------------------------ epilogue
-    const int e = warp - 2;
+    if constexpr (T::kRegBalance) reg_alloc<T::kRegsEpilogue>();
+    const int e = warp - T::kEpiWarp0;
     const int q = warp & 3;                  // TMEM lane quarter this warp may read
     const int half = e >> 2;                 // column half (subchannel mode runs 8 warps)
     const int row_in_tile = q * 32 + lane;
@@ -424,26 +442,11 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     //   per-channel, 4 warps: all 256 (SwiGLU: up 0..127 with gate 128..255)
     //   subchannel, 8 warps : plain -> [128*half, +128); SwiGLU -> up [64*half,+64) with gate 128+[64*half,+64)
     constexpr int kOwnCols = (kScale == SCALE_SC) ? 128 : 256;
-    constexpr int kChunks = kOwnCols / 32;
     for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
       const TileWork w = decode_tile<kAMn>(p, t);
       const int row = w.out_row0 + row_in_tile;
       const bool row_ok = (row >= w.row_lo) && (row < w.row_hi);
       const long long sa_row = w.sa_off + static_cast<long long>(row) * (kScale == SCALE_SC ? p.scale_cols : 1);
-
-      // TMEM column of chunk c, and the output / scale column it maps to.
-      auto tmem_col = [&](int c) -> int {
-        if constexpr (kScale == SCALE_SC) {
-          if constexpr (kEpi == EPI_SWIGLU) return (c < 2) ? (64 * half + 32 * c) : (128 + 64 * half + 32 * (c - 2));
-          else return 128 * half + 32 * c;
-        } else {
-          return 32 * c;
-        }
-      };
-      auto scale_col = [&](int c) -> int {  // column index into b_scale
-        const int tc = tmem_col(c);
-        return (tc < NBLK) ? (w.n0 + tc) : (w.n1 + tc - NBLK);
-      };
 
       if constexpr (kScale == SCALE_PC) {
         float sa = 0.f;
@@ -660,32 +663,91 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       } else {
         // ---------------------------------------------------------------- subchannel scales
+        // Running fp32 sums of the warp's 128 accumulator columns stay in registers:
+        //   out += (f32(acc_g) * sa_g) * sb_g   for K-groups g in ascending order, out starting at 0.
+        // int -> float without a convert instruction: for |x| <= 2^22 the float with bit pattern
+        // 0x4B400000 + x is exactly 1.5 * 2^23 + x, so fma(that, sa, -(1.5 * 2^23) * sa) is the single
+        // rounding of x * sa (the subtrahend is exact: sa has 8 significant bits).  A K-group has at
+        // most 256 terms, |x| <= 256 * 64 * 256 = 2^22 (int4, values carried as 16 v) or 127^2 * 256.
+        // For int4 the accumulator holds 256 * sum; sa is pre-multiplied by 2^-8, which is exact.
+        constexpr uint32_t kMagicBits = 0x4B400000u;
+        constexpr float kMagic = 12582912.0f;
+        constexpr float kPreScale = kInt4 ? (1.0f / 256.0f) : 1.0f;
         float acc[kOwnCols];
 #pragma unroll
         for (int i = 0; i < kOwnCols; ++i) acc[i] = 0.f;
         const int total_mma = (w.k_len + 31) / 32;
         const int num_groups = (total_mma + mma_per_group - 1) / mma_per_group;
+
+        // Column scales: strip entry j (0..127) belongs to accumulator column j of this warp.
+        // Lane l owns entries 4l..4l+3 (always on one side of the up / gate split).
+        const int j0 = 4 * lane;
+        int bcol, ocol;  // column of b_scale, output column (for the N edge)
+        if constexpr (kEpi == EPI_SWIGLU) {
+          const int tc = 64 * half + (j0 & 63);
+          bcol = (j0 < 64) ? (w.n0 + tc) : (w.n1 + tc);
+          ocol = w.n0 + tc;
+        } else {
+          const int tc = 128 * half + j0;
+          bcol = (tc < NBLK) ? (w.n0 + tc) : (w.n1 + tc - NBLK);
+          ocol = w.n0 + tc;
+        }
+        auto load_sb = [&](int gi, float (&f)[4]) {
+          const long long idx = w.sb_off + static_cast<long long>(gi) * p.lds_b + bcol;
+          if (ocol + 4 <= p.N && (idx & 3) == 0) {
+            const uint2 x = __ldg(reinterpret_cast<const uint2*>(p.b_scale + idx));
+            f[0] = __uint_as_float(x.x << 16);
+            f[1] = __uint_as_float(x.x & 0xFFFF0000u);
+            f[2] = __uint_as_float(x.y << 16);
+            f[3] = __uint_as_float(x.y & 0xFFFF0000u);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) f[i] = (ocol + i < p.N) ? __bfloat162float(p.b_scale[idx + i]) : 0.f;
+          }
+        };
+        auto load_sa = [&](int gi) -> float {
+          return row_ok ? __bfloat162float(p.a_scale[sa_row + gi]) * kPreScale : 0.f;
+        };
+        float sb_next[4] = {0.f, 0.f, 0.f, 0.f};
+        float sa_next = 0.f;
+        if (num_groups > 0) {
+          load_sb(0, sb_next);
+          sa_next = load_sa(0);
+        }
         for (int gi = 0; gi < num_groups && ok; ++gi, ++grp) {
+          // publish this group's column scales (fetched one group ago), then fetch the next group's
+          float* strip = sb_strip + (gi & 1) * 128;
+          __syncwarp();
+          *reinterpret_cast<float4*>(strip + j0) = make_float4(sb_next[0], sb_next[1], sb_next[2], sb_next[3]);
+          const float sa = sa_next;
+          if (gi + 1 < num_groups) {
+            load_sb(gi + 1, sb_next);
+            sa_next = load_sa(gi + 1);
+          }
+          __syncwarp();
           const int b = grp & 1;
-          const uint32_t aph = (grp >> 1) & 1;
-          if (!__all_sync(0xFFFFFFFFu, mbar_wait(acc_full_bar(b), aph, ctx, 31))) { ok = false; break; }
+          if (!__all_sync(0xFFFFFFFFu, mbar_wait(acc_full_bar(b), (grp >> 1) & 1, ctx, 31))) { ok = false; break; }
           tc_fence_after_sync();
-          float sa = 0.f;
-          if (row_ok) sa = __bfloat162float(p.a_scale[sa_row + gi]);
-          const __nv_bfloat16* sb_row = p.b_scale + w.sb_off + static_cast<long long>(gi) * p.lds_b;
+          const float csa = -(kMagic * sa);
 #pragma unroll
-          for (int c = 0; c < kChunks; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tmem_base + lane_addr + b * BN + tmem_col(c), r);
+          for (int c = 0; c < kOwnCols / 16; ++c) {
+            // 16 columns at a time; accumulator columns of this warp in strip order
+            int tcol;
+            if constexpr (kEpi == EPI_SWIGLU) tcol = (c < 4) ? (64 * half + 16 * c) : (NBLK + 64 * half + 16 * (c - 4));
+            else tcol = 128 * half + 16 * c;
+            uint32_t r[16];
+            tmem_ld_32x32b_x16(tmem_base + lane_addr + b * BN + tcol, r);
             tmem_ld_wait();
-            const int sc0 = scale_col(c);
-            const int lim = (kEpi == EPI_SWIGLU) ? 2 * p.N : p.N;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              int a = static_cast<int>(r[i]);
-              if constexpr (kInt4) a >>= 8;
-              const float sb = (sc0 + i < lim) ? __bfloat162float(sb_row[sc0 + i]) : 0.f;
-              acc[32 * c + i] = __fadd_rn(acc[32 * c + i], __fmul_rn(__fmul_rn(static_cast<float>(a), sa), sb));
+            for (int i4 = 0; i4 < 4; ++i4) {
+              const float4 s4 = *reinterpret_cast<const float4*>(strip + 16 * c + 4 * i4);  // broadcast read
+              const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+              for (int k2 = 0; k2 < 4; ++k2) {
+                const float y = __uint_as_float(r[4 * i4 + k2] + kMagicBits);
+                const float t2 = __fmaf_rn(y, sa, csa);
+                acc[16 * c + 4 * i4 + k2] = __fadd_rn(acc[16 * c + 4 * i4 + k2], __fmul_rn(t2, sv[k2]));
+              }
             }
           }
           tc_fence_before_sync();
@@ -693,7 +755,10 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (lane == 0) mbar_arrive(acc_empty_bar(b));
         }
         if (!ok) break;
-        // activation + store
+        // activation + store, 32 output columns at a time
+        const int wrow0 = w.out_row0 + q * 32;
+        const bool use_tma = T::kTmaStore && p.tma_store != 0 &&
+                             (p.mode == MODE_DENSE || (wrow0 >= w.row_lo && wrow0 + 32 <= w.row_hi));
         constexpr int kOutChunksSc = (kEpi == EPI_SWIGLU) ? 2 : 4;
 #pragma unroll
         for (int c = 0; c < kOutChunksSc; ++c) {
@@ -702,7 +767,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int i = 0; i < 32; ++i) {
             float x = acc[32 * c + i];
             if constexpr (kEpi == EPI_SWIGLU) {
-              const float gate = acc[32 * (c + 2) + i];
+              const float gate = acc[64 + 32 * c + i];
               x = x * (gate / (1.0f + __expf(-gate)));
             } else if constexpr (kEpi == EPI_RELU2) {
               x = fmaxf(x, 0.f);
@@ -710,31 +775,42 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
             v[i] = x;
           }
-          const int col0 = w.n0 + tmem_col(c);  // up / plain columns sit in block 0 or 1
-          const int ocol0 = (kEpi == EPI_SWIGLU) ? col0 : ((tmem_col(c) < NBLK) ? col0 : (w.n1 + tmem_col(c) - NBLK));
+          const int ocol0 = w.n0 + ((kEpi == EPI_SWIGLU) ? 64 * half : 128 * half) + 32 * c;
+          if constexpr (T::kTmaStore) {
+            if (use_tma) {
+              uint8_t* dst = stage_out + lane * 64;
+              const int sw = (lane >> 1) & 3;
+              if (lane == 0) bulk_wait_read_all();
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint4 pk;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i + 0], v[8 * i + 1]);
+                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
+                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
+                pk.x = *reinterpret_cast<uint32_t*>(&h0);
+                pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                pk.z = *reinterpret_cast<uint32_t*>(&h2);
+                pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                *reinterpret_cast<uint4*>(dst + ((i ^ sw) << 4)) = pk;
+              }
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_2d(&tmap_c, stage_out_u32, ocol0 * 2, w.out_row_base + wrow0);
+                bulk_commit_group();
+              }
+              continue;
+            }
+          }
           if (row_ok) {
             const long long o = w.out_off + static_cast<long long>(row) * p.ldc + ocol0;
             if constexpr (kOut == OUT_BF16) {
               __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + o;
-              if (ocol0 + 32 <= p.N && (p.ldc % 8 == 0)) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  uint4 pk;
-                  __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i + 0], v[8 * i + 1]);
-                  __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
-                  __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
-                  __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
-                  pk.x = *reinterpret_cast<uint32_t*>(&h0);
-                  pk.y = *reinterpret_cast<uint32_t*>(&h1);
-                  pk.z = *reinterpret_cast<uint32_t*>(&h2);
-                  pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                  reinterpret_cast<uint4*>(dst)[i] = pk;
-                }
-              } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                  if (ocol0 + i < p.N) dst[i] = __float2bfloat16_rn(v[i]);
-              }
+              for (int i = 0; i < 32; ++i)
+                if (ocol0 + i < p.N) dst[i] = __float2bfloat16_rn(v[i]);
             } else {
               float* dst = reinterpret_cast<float*>(p.out) + o;
 #pragma unroll
@@ -746,11 +822,12 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
     if (lane == 0) bulk_wait_all();  // TMA stores issued by this lane have landed
-  } else {
+  } else if (warp >= T::kUnpackWarp0) {
     // ------------------------------------------------------------------ unpack (int4 only)
+    if constexpr (T::kRegBalance) reg_dealloc<T::kRegsUnpack>();
     if constexpr (kInt4) {
       constexpr int UT = T::kUnpackWarps * 32;           // unpack threads: 128 or 256
-      const int ut = threadIdx.x - (2 + T::kEpiWarps) * 32;
+      const int ut = threadIdx.x - T::kUnpackWarp0 * 32;
       // Every item is one 16-byte load of packed data (32 nibbles) that becomes two 16-byte
       // chunks of int8.  Per-thread offsets are fixed; successive passes add a constant.
       //
