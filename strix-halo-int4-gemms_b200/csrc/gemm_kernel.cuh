@@ -184,8 +184,8 @@ struct KernelTraits {
   static constexpr int kEpiWarp0 = kRegBalance ? 4 : 2;
   static constexpr int kUnpackWarp0 = kEpiWarp0 + kEpiWarps;
   static constexpr int kThreads = (kUnpackWarp0 + kUnpackWarps) * 32;
-  static constexpr int kRegsLight = 48;    // TMA / MMA warpgroup
-  static constexpr int kRegsUnpack = 80;
+  static constexpr int kRegsLight = 40;    // TMA / MMA warpgroup
+  static constexpr int kRegsUnpack = 96;
   static constexpr int kRegsEpilogue = 184;
   // registers the CTA needs after the re-balance; the host checks this against regs-per-thread x threads
   static constexpr int kRegPoolNeeded = kRegBalance ? (128 * kRegsLight + 256 * kRegsEpilogue + kUnpackWarps * 32 * kRegsUnpack) : 0;
@@ -393,6 +393,37 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           __syncwarp();
         }
         ++grp;
+      } else if (mma_per_group >= BK / 32) {
+        // K-groups of 128 or 256: a K block never straddles two groups, so a block is issued in
+        // one go exactly like the per-channel case, with the accumulator hand-over at group ends
+        const int kb_per_group = mma_per_group / (BK / 32);
+        for (int kb = 0; kb < w.num_kb && ok; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          const int b = grp & 1;
+          const bool group_start = (kb % kb_per_group) == 0;
+          const bool group_end = ((kb + 1) % kb_per_group) == 0 || kb == w.num_kb - 1;
+          if (group_start) {
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(acc_empty_bar(b), ((grp >> 1) & 1) ^ 1u, ctx, 21))) { ok = false; break; }
+          }
+          if (!__all_sync(0xFFFFFFFFu, mbar_wait(full_bar(s), ph, ctx, 20))) { ok = false; break; }
+          tc_fence_after_sync();
+          if (elect_one()) {
+            const uint32_t a_lo = a_lo0 + s * (T::kStageBytes >> 4);
+            const uint32_t b_lo = b_lo0 + s * (T::kStageBytes >> 4);
+            const int left = total_mma - kb * (BK / 32);
+#pragma unroll
+            for (int k = 0; k < BK / 32; ++k) {
+              if (k < left)
+                umma_i8(tmem_base + b * BN, make_desc(a_lo + k * kAStep), make_desc(b_lo + k * kBStep), idesc,
+                        (group_start && k == 0) ? 0u : 1u);
+            }
+            umma_commit(empty_bar(s));
+            if (group_end) umma_commit(acc_full_bar(b));
+          }
+          __syncwarp();
+          if (group_end) ++grp;
+        }
       } else {
         int j = 0;  // MMA step within the tile
         for (int kb = 0; kb < w.num_kb && ok; ++kb, ++it) {
@@ -736,8 +767,17 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if constexpr (kEpi == EPI_SWIGLU) tcol = (c < 4) ? (64 * half + 16 * c) : (NBLK + 64 * half + 16 * (c - 4));
             else tcol = 128 * half + 16 * c;
             uint32_t r[16];
+#ifdef B200_DBG_SC_NO_TMEM_LD
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r[i] = tcol + i;
+#else
             tmem_ld_32x32b_x16(tmem_base + lane_addr + b * BN + tcol, r);
             tmem_ld_wait();
+#endif
+#ifdef B200_DBG_SC_NO_MATH
+            if (r[0] == 0x12345u) acc[16 * c] += 1.f;
+            if (true) continue;
+#endif
 #pragma unroll
             for (int i4 = 0; i4 < 4; ++i4) {
               const float4 s4 = *reinterpret_cast<const float4*>(strip + 16 * c + 4 * i4);  // broadcast read
@@ -863,18 +903,22 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint8_t* pk_a = smem_gen + S * T::kStageBytes + ps * T::kPkStageBytes;
           const uint8_t* pk_b = pk_a + T::kPkABytes;
           // all loads of the stage first: they do not depend on the int8 stage being free
+          // B items are handled in batches of at most 4 to bound the registers holding raw data
+          constexpr int kBItems = 1024 / UT;
+          constexpr int kBBatch = kBItems < 4 ? kBItems : 4;
           uint4 xa[512 / UT];
-          uint4 xb[1024 / UT];  // K-major B: packed tile [256 rows][64 B], same item scheme as K-major A
+          uint4 xb[kBBatch];  // K-major B: packed tile [256 rows][64 B], same item scheme as K-major A
+          auto load_b = [&](int j) -> uint4 {
+            if constexpr (kBMn) return *reinterpret_cast<const uint4*>(pk_b + b_src0 + j * (kBRowsPerPass * 128));
+            else return *reinterpret_cast<const uint4*>(pk_b + a_src0 + j * (kARowsPerPass * 64));
+          };
 #pragma unroll
           for (int j = 0; j < 512 / UT; ++j) {
             if constexpr (!kAMn) xa[j] = *reinterpret_cast<const uint4*>(pk_a + a_src0 + j * (kARowsPerPass * 64));
             else xa[j] = *reinterpret_cast<const uint4*>(pk_a + m_src0 + j * (kMRowsPerPass * 128));
           }
 #pragma unroll
-          for (int j = 0; j < 1024 / UT; ++j) {
-            if constexpr (kBMn) xb[j] = *reinterpret_cast<const uint4*>(pk_b + b_src0 + j * (kBRowsPerPass * 128));
-            else xb[j] = *reinterpret_cast<const uint4*>(pk_b + a_src0 + j * (kARowsPerPass * 64));
-          }
+          for (int j = 0; j < kBBatch; ++j) xb[j] = load_b(j);
           if (!__all_sync(0xFFFFFFFFu, mbar_wait(empty_bar(s), ph ^ 1u, ctx, 41))) { ok = false; break; }
           uint8_t* a8 = smem_gen + s * T::kStageBytes;
           uint8_t* b8 = a8 + T::kA8Bytes;
@@ -896,29 +940,34 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
           }
 #pragma unroll
-          for (int j = 0; j < 1024 / UT; ++j) {
-            uint4 lo, hi;
-            expand_word(xb[j].x, lo.x, hi.x);
-            expand_word(xb[j].y, lo.y, hi.y);
-            expand_word(xb[j].z, lo.z, hi.z);
-            expand_word(xb[j].w, lo.w, hi.w);
-            if constexpr (!kBMn) {
-              *reinterpret_cast<uint4*>(b8 + a_dst_lo0 + j * (kARowsPerPass * 128)) = lo;
-              *reinterpret_cast<uint4*>(b8 + a_dst_hi0 + j * (kARowsPerPass * 128)) = hi;
-              continue;
+          for (int jb = 0; jb < kBItems; jb += kBBatch) {
+#pragma unroll
+            for (int jj = 0; jj < kBBatch; ++jj) {
+              const int j = jb + jj;
+              uint4 lo, hi;
+              expand_word(xb[jj].x, lo.x, hi.x);
+              expand_word(xb[jj].y, lo.y, hi.y);
+              expand_word(xb[jj].z, lo.z, hi.z);
+              expand_word(xb[jj].w, lo.w, hi.w);
+              if (jb + kBBatch < kBItems) xb[jj] = load_b(j + kBBatch);  // next batch, in flight during the stores
+              if constexpr (!kBMn) {
+                *reinterpret_cast<uint4*>(b8 + a_dst_lo0 + j * (kARowsPerPass * 128)) = lo;
+                *reinterpret_cast<uint4*>(b8 + a_dst_hi0 + j * (kARowsPerPass * 128)) = hi;
+              } else {
+                // packed row of this pass: b_p0 + kBRowsPerPass * j  (b_p0 < kBRowsPerPass <= 16)
+                constexpr int R = kBRowsPerPass;
+                const int row_adv = R * j;                       // compile-time after unrolling
+                const int slot_adv = 32 * (row_adv >> 4) + (row_adv & 15);
+                if constexpr (kMaskK) {
+                  const int k_lo = kb * BK + 2 * (b_p0 + row_adv);
+                  if (k_lo >= w.k_valid) lo = make_uint4(0, 0, 0, 0);
+                  if (k_lo + 1 >= w.k_valid) hi = make_uint4(0, 0, 0, 0);
+                }
+                const uint32_t d = b_dst0 + slot_adv * 128;
+                *reinterpret_cast<uint4*>(b8 + d) = lo;
+                *reinterpret_cast<uint4*>(b8 + d + 16 * 128) = hi;
+              }
             }
-            // packed row of this pass: b_p0 + kBRowsPerPass * j  (b_p0 < kBRowsPerPass <= 16)
-            constexpr int R = kBRowsPerPass;
-            const int row_adv = R * j;                       // compile-time after unrolling
-            const int slot_adv = 32 * (row_adv >> 4) + (row_adv & 15);
-            if constexpr (kMaskK) {
-              const int k_lo = kb * BK + 2 * (b_p0 + row_adv);
-              if (k_lo >= w.k_valid) lo = make_uint4(0, 0, 0, 0);
-              if (k_lo + 1 >= w.k_valid) hi = make_uint4(0, 0, 0, 0);
-            }
-            const uint32_t d = b_dst0 + slot_adv * 128;
-            *reinterpret_cast<uint4*>(b8 + d) = lo;
-            *reinterpret_cast<uint4*>(b8 + d + 16 * 128) = hi;
           }
           fence_proxy_async_smem();
           __syncwarp();
