@@ -677,11 +677,13 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         for (int c = 0; c < kOutChunks; c += 2) {
           if (!zero_tile) {
             tmem_ld_wait();
+            tmem_ld_fence(ra);
             tmem_ld_32x32b_x32(acc_addr + 32 * (c + 1), rb);
           }
           process(ra, c);
           if (!zero_tile) {
             tmem_ld_wait();
+            tmem_ld_fence(rb);
             if (c + 2 < kOutChunks) tmem_ld_32x32b_x32(acc_addr + 32 * (c + 2), ra);
           }
           process(rb, c + 1);

@@ -50,11 +50,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
+#ifdef B200_TRY_WAIT_HINT_NS
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#endif
       "selp.u32 %0, 1, 0, p;\n\t"
       "}\n"
       : "=r"(ok)
+#ifdef B200_TRY_WAIT_HINT_NS
+      : "r"(bar), "r"(parity), "r"(static_cast<uint32_t>(B200_TRY_WAIT_HINT_NS))
+#else
       : "r"(bar), "r"(parity)
+#endif
       : "memory");
   return ok != 0;
 }
@@ -216,6 +224,16 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
       : "r"(taddr)
       : "memory");
 }
+// tcgen05.ld is asynchronous: its destination registers are valid only after tcgen05.wait::ld.  When
+// other work is placed between the load and the wait, this empty statement (after the wait) ties the
+// registers to the wait so that the compiler cannot schedule a use of them before it.
+__device__ __forceinline__ void tmem_ld_fence(uint32_t (&r)[32]) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 8)
+    asm volatile("" : "+r"(r[i]), "+r"(r[i + 1]), "+r"(r[i + 2]), "+r"(r[i + 3]), "+r"(r[i + 4]), "+r"(r[i + 5]),
+                      "+r"(r[i + 6]), "+r"(r[i + 7])::"memory");
+}
+
 // Register re-balance between warpgroups (all four warps of the warpgroup must execute it).
 template <int kRegs>
 __device__ __forceinline__ void reg_alloc() {
