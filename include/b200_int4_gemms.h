@@ -52,6 +52,12 @@ enum { B200_PATH_AUTO = 0, B200_PATH_TCGEN05 = 1, B200_PATH_SIMT = 2 };
 /* PERSISTENT: one CTA per SM walks the tile list.  STANDARD: one CTA per output tile. */
 enum { B200_SCHEDULE_PERSISTENT = 0, B200_SCHEDULE_STANDARD = 1 };
 
+/* AUTO: the library pairs CTAs (clusters of two SMs, 256 x 256 tiles, tcgen05 cta_group::2) when the
+ * problem has enough 256-row tiles and a paired kernel exists for the variant, else one CTA per
+ * 128 x 256 tile.  SINGLE / PAIR force one of them (PAIR falls back to SINGLE when no paired kernel
+ * exists).  Results are bit-identical either way. */
+enum { B200_CTA_GROUP_AUTO = 0, B200_CTA_GROUP_SINGLE = 1, B200_CTA_GROUP_PAIR = 2 };
+
 typedef struct b200_gemm_variant {
   int32_t dtype;      /* B200_DTYPE_*      */
   int32_t layout;     /* B200_LAYOUT_*     */
@@ -63,7 +69,8 @@ typedef struct b200_gemm_variant {
   int32_t path;       /* B200_PATH_*       */
   int32_t group_m;    /* raster swizzle width in row tiles, 0 = library default */
   int32_t schedule;   /* B200_SCHEDULE_*   */
-  int32_t reserved[6];
+  int32_t cta_group;  /* B200_CTA_GROUP_*: SMs per output tile of the tensor-core kernel */
+  int32_t reserved[5];
 } b200_gemm_variant;
 
 /* Replaces amd_strix_halo_kernels_dispatch_version (dispatch.cpp:206). */

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -87,6 +89,7 @@ struct DeviceState {
   bool ready = false;
   int sm_count = 0;
   int cc_major = 0;
+  int max_pair_clusters = 0;  // clusters of two CTAs the device can hold at once (pair kernels)
   int* status_host = nullptr;  // pinned + mapped
   int* status_dev = nullptr;
 };
@@ -99,48 +102,61 @@ cudaError_t set_smem(Kernel kernel, int bytes) {
 }
 
 #define B200_FOR_EACH_TC_KERNEL(X)                                          \
-  /*  int4  A-MN   B-MN  scale     epilogue    out       maskK */           \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false)                 \
-  X(true, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false)                \
-  X(true, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false)               \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, false)                  \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_S32, false)                  \
-  X(true, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false)                 \
-  X(true, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false)                \
-  X(true, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false)               \
-  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, false)                  \
-  X(true, true, true, SCALE_PC, EPI_NONE, OUT_BF16, false)                  \
-  X(true, true, true, SCALE_PC, EPI_NONE, OUT_F32, false)                   \
-  X(true, true, true, SCALE_SC, EPI_NONE, OUT_BF16, false)                  \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, true)                   \
-  X(true, true, true, SCALE_PC, EPI_NONE, OUT_F32, true)                    \
-  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, true)                   \
-  X(true, true, true, SCALE_SC, EPI_NONE, OUT_F32, true)                    \
-  X(true, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false)                \
-  X(true, false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false)               \
-  X(true, false, false, SCALE_PC, EPI_SWIGLU, OUT_BF16, false)              \
-  X(true, false, false, SCALE_PC, EPI_NONE, OUT_F32, false)                 \
-  X(true, false, false, SCALE_PC, EPI_NONE, OUT_S32, false)                 \
-  X(true, false, false, SCALE_SC, EPI_NONE, OUT_BF16, false)                \
-  X(true, false, false, SCALE_SC, EPI_RELU2, OUT_BF16, false)               \
-  X(true, false, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false)              \
-  X(true, false, false, SCALE_SC, EPI_NONE, OUT_F32, false)                 \
-  X(false, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false)                \
-  X(false, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false)               \
-  X(false, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false)              \
-  X(false, false, true, SCALE_PC, EPI_NONE, OUT_F32, false)                 \
-  X(false, false, true, SCALE_PC, EPI_NONE, OUT_S32, false)                 \
-  X(false, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false)                \
-  X(false, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false)               \
-  X(false, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false)              \
-  X(false, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false)               \
-  X(false, false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false)              \
-  X(false, false, false, SCALE_PC, EPI_SWIGLU, OUT_BF16, false)             \
-  X(false, false, false, SCALE_PC, EPI_NONE, OUT_F32, false)                \
-  X(false, false, false, SCALE_PC, EPI_NONE, OUT_S32, false)                \
-  X(false, false, false, SCALE_SC, EPI_NONE, OUT_BF16, false)               \
-  X(false, false, false, SCALE_SC, EPI_RELU2, OUT_BF16, false)              \
-  X(false, false, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false)
+  /*  int4  A-MN   B-MN  scale     epilogue    out       maskK  pair */          \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, false)                 \
+  X(true, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, false)                \
+  X(true, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false)               \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, false, false)                  \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, false)                  \
+  X(true, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false)                 \
+  X(true, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, false)                \
+  X(true, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false)               \
+  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, false, false)                  \
+  X(true, true, true, SCALE_PC, EPI_NONE, OUT_BF16, false, false)                  \
+  X(true, true, true, SCALE_PC, EPI_NONE, OUT_F32, false, false)                   \
+  X(true, true, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false)                  \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, true, false)                   \
+  X(true, true, true, SCALE_PC, EPI_NONE, OUT_F32, true, false)                    \
+  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, true, false)                   \
+  X(true, true, true, SCALE_SC, EPI_NONE, OUT_F32, true, false)                    \
+  X(true, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, false)                \
+  X(true, false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false, false)               \
+  X(true, false, false, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false)              \
+  X(true, false, false, SCALE_PC, EPI_NONE, OUT_F32, false, false)                 \
+  X(true, false, false, SCALE_PC, EPI_NONE, OUT_S32, false, false)                 \
+  X(true, false, false, SCALE_SC, EPI_NONE, OUT_BF16, false, false)                \
+  X(true, false, false, SCALE_SC, EPI_RELU2, OUT_BF16, false, false)               \
+  X(true, false, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false)              \
+  X(true, false, false, SCALE_SC, EPI_NONE, OUT_F32, false, false)                 \
+  X(false, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, false)                \
+  X(false, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, false)               \
+  X(false, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false)              \
+  X(false, false, true, SCALE_PC, EPI_NONE, OUT_F32, false, false)                 \
+  X(false, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, false)                 \
+  X(false, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false)                \
+  X(false, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, false)               \
+  X(false, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false)              \
+  X(false, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, false)               \
+  X(false, false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false, false)              \
+  X(false, false, false, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false)             \
+  X(false, false, false, SCALE_PC, EPI_NONE, OUT_F32, false, false)                \
+  X(false, false, false, SCALE_PC, EPI_NONE, OUT_S32, false, false)                \
+  X(false, false, false, SCALE_SC, EPI_NONE, OUT_BF16, false, false)               \
+  X(false, false, false, SCALE_SC, EPI_RELU2, OUT_BF16, false, false)              \
+  X(false, false, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false)                \
+  /* CTA pairs (cta_group::2): 256 x 256 output tiles over two SMs */       \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true)           \
+  X(true, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, true)          \
+  X(true, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, true)         \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, false, true)            \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, true)            \
+  X(true, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, true)           \
+  X(true, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, true)         \
+  X(true, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, true)          \
+  X(false, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true)          \
+  X(false, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, true)         \
+  X(false, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, true)        \
+  X(false, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, true)
 
 int ensure_device(int device_index, DeviceState** out) {
   if (device_index < 0 || device_index >= kMaxDevices) return fail("device_index out of range");
@@ -164,21 +180,48 @@ int ensure_device(int device_index, DeviceState** out) {
     std::memset(st.status_host, 0, 4 * sizeof(int));
     err = cudaHostGetDevicePointer(reinterpret_cast<void**>(&st.status_dev), st.status_host, 0);
     if (err != cudaSuccess) return fail_cuda("cudaHostGetDevicePointer(status)", err);
-#define X(I4, AMN, BMN, SC, EP, OT, MK)                                                             \
-  err = set_smem(gemm_i8_tcgen05_kernel<I4, AMN, BMN, SC, EP, OT, MK>,                               \
-                 KernelTraits<I4, AMN, BMN, SC, EP, OT, MK>::kSmemBytes);                            \
+#define X(I4, AMN, BMN, SC, EP, OT, MK, PR)                                                             \
+  err = set_smem(gemm_i8_tcgen05_kernel<I4, AMN, BMN, SC, EP, OT, MK, PR>,                               \
+                 KernelTraits<I4, AMN, BMN, SC, EP, OT, MK, PR>::kSmemBytes);                            \
   if (err != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(max dynamic shared memory)", err);   \
-  if (KernelTraits<I4, AMN, BMN, SC, EP, OT, MK>::kRegPoolNeeded > 0) {                                  \
+  if (KernelTraits<I4, AMN, BMN, SC, EP, OT, MK, PR>::kRegPoolNeeded > 0) {                                  \
     /* setmaxnreg.inc would wait for ever if the CTA's register pool were smaller than the roles ask for */ \
     cudaFuncAttributes attr;                                                                             \
-    err = cudaFuncGetAttributes(&attr, gemm_i8_tcgen05_kernel<I4, AMN, BMN, SC, EP, OT, MK>);           \
+    err = cudaFuncGetAttributes(&attr, gemm_i8_tcgen05_kernel<I4, AMN, BMN, SC, EP, OT, MK, PR>);           \
     if (err != cudaSuccess) return fail_cuda("cudaFuncGetAttributes", err);                              \
-    if (attr.numRegs * KernelTraits<I4, AMN, BMN, SC, EP, OT, MK>::kThreads <                            \
-        KernelTraits<I4, AMN, BMN, SC, EP, OT, MK>::kRegPoolNeeded)                                      \
+    if (attr.numRegs * KernelTraits<I4, AMN, BMN, SC, EP, OT, MK, PR>::kThreads <                            \
+        KernelTraits<I4, AMN, BMN, SC, EP, OT, MK, PR>::kRegPoolNeeded)                                      \
       return fail("a subchannel kernel was compiled with too few registers for its register re-balance"); \
   }
     B200_FOR_EACH_TC_KERNEL(X)
 #undef X
+    // CTA-pair kernels are persistent: every cluster of the grid must be resident at once, so the grid
+    // is sized by what the device can co-schedule (not every SM can always be paired).
+    st.max_pair_clusters = st.sm_count / 2;
+#define X(I4, AMN, BMN, SC, EP, OT, MK, PR)                                                            \
+  if (PR) {                                                                                          \
+    using T = KernelTraits<I4, AMN, BMN, SC, EP, OT, MK, PR>;                                         \
+    cudaLaunchConfig_t cfg{};                                                                        \
+    cfg.gridDim = dim3(st.sm_count & ~1);                                                            \
+    cfg.blockDim = dim3(T::kThreads);                                                                \
+    cfg.dynamicSmemBytes = T::kSmemBytes;                                                            \
+    cudaLaunchAttribute attr[1];                                                                     \
+    attr[0].id = cudaLaunchAttributeClusterDimension;                                                \
+    attr[0].val.clusterDim.x = 2;                                                                    \
+    attr[0].val.clusterDim.y = 1;                                                                    \
+    attr[0].val.clusterDim.z = 1;                                                                    \
+    cfg.attrs = attr;                                                                                \
+    cfg.numAttrs = 1;                                                                                \
+    int clusters = 0;                                                                                \
+    err = cudaOccupancyMaxActiveClusters(&clusters, gemm_i8_tcgen05_kernel<I4, AMN, BMN, SC, EP, OT, MK, PR>, &cfg); \
+    if (err != cudaSuccess) return fail_cuda("cudaOccupancyMaxActiveClusters", err);                 \
+    if (clusters < st.max_pair_clusters) st.max_pair_clusters = clusters;                            \
+  }
+    B200_FOR_EACH_TC_KERNEL(X)
+#undef X
+    if (std::getenv("B200_INT4_GEMMS_VERBOSE") != nullptr)
+      std::fprintf(stderr, "b200_int4_gemms: device %d: %d SMs, %d co-resident CTA pairs\n", device_index,
+                   st.sm_count, st.max_pair_clusters);
     st.ready = true;
   }
   *out = &st;
@@ -205,17 +248,30 @@ int make_output_map(CUtensorMap* map, void* out, int out_dtype, uint64_t rows, u
 struct TcLaunch {
   bool int4, a_mn, b_mn, mask_k;
   int scale, epi, out;
+  bool pair = false;  // CTA-pair kernel (clusters of two, 256-row tiles)
 };
 
 int launch_tc(const TcLaunch& l, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
               const GemmParams& p, int grid, cudaStream_t stream) {
-#define X(I4, AMN, BMN, SC, EP, OT, MK)                                                              \
+#define X(I4, AMN, BMN, SC, EP, OT, MK, PR)                                                              \
   if (l.int4 == I4 && l.a_mn == AMN && l.b_mn == BMN && l.scale == SC && l.epi == EP && l.out == OT &&           \
-      l.mask_k == MK) {                                                                          \
-    using T = KernelTraits<I4, AMN, BMN, SC, EP, OT, MK>;                                             \
-    gemm_i8_tcgen05_kernel<I4, AMN, BMN, SC, EP, OT, MK>                                              \
-        <<<grid, T::kThreads, T::kSmemBytes, stream>>>(ta, tb, tc, p);                               \
-    cudaError_t err = cudaGetLastError();                                                        \
+      l.mask_k == MK && l.pair == PR) {                                                                          \
+    using T = KernelTraits<I4, AMN, BMN, SC, EP, OT, MK, PR>;                                             \
+    cudaLaunchConfig_t cfg{};                                                                    \
+    cfg.gridDim = dim3(grid);                                                                    \
+    cfg.blockDim = dim3(T::kThreads);                                                            \
+    cfg.dynamicSmemBytes = T::kSmemBytes;                                                        \
+    cfg.stream = stream;                                                                         \
+    cudaLaunchAttribute attr[1];                                                                 \
+    attr[0].id = cudaLaunchAttributeClusterDimension;                                            \
+    attr[0].val.clusterDim.x = PR ? 2 : 1;                                                       \
+    attr[0].val.clusterDim.y = 1;                                                                \
+    attr[0].val.clusterDim.z = 1;                                                                \
+    cfg.attrs = attr;                                                                            \
+    cfg.numAttrs = 1;                                                                            \
+    cudaError_t err = cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_kernel<I4, AMN, BMN, SC, EP, OT, MK, PR>, \
+                                         ta, tb, tc, p);                                         \
+    if (err == cudaSuccess) err = cudaGetLastError();                                            \
     if (err != cudaSuccess) return fail_cuda("tcgen05 GEMM kernel launch", err);                 \
     return 0;                                                                                    \
   }
@@ -225,9 +281,9 @@ int launch_tc(const TcLaunch& l, const CUtensorMap& ta, const CUtensorMap& tb, c
 }
 
 bool tc_has(const TcLaunch& l) {
-#define X(I4, AMN, BMN, SC, EP, OT, MK)                                                              \
+#define X(I4, AMN, BMN, SC, EP, OT, MK, PR)                                                              \
   if (l.int4 == I4 && l.a_mn == AMN && l.b_mn == BMN && l.scale == SC && l.epi == EP && l.out == OT &&           \
-      l.mask_k == MK)                                                                            \
+      l.mask_k == MK && l.pair == PR)                                                                            \
     return true;
   B200_FOR_EACH_TC_KERNEL(X)
 #undef X
@@ -254,6 +310,7 @@ int check_variant(const b200_gemm_variant* v) {
   if (v->path < B200_PATH_AUTO || v->path > B200_PATH_SIMT) return fail("variant.path is unknown");
   if (v->schedule != B200_SCHEDULE_PERSISTENT && v->schedule != B200_SCHEDULE_STANDARD)
     return fail("variant.schedule is unknown");
+  if (v->cta_group < B200_CTA_GROUP_AUTO || v->cta_group > B200_CTA_GROUP_PAIR) return fail("variant.cta_group is unknown");
   return 0;
 }
 
@@ -414,8 +471,22 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
   p.N = n;
   p.K = k;
   p.tile_cols = swiglu ? NBLK : BN;
-  p.tiles_m = (m + BM - 1) / BM;
   p.tiles_n = (n + p.tile_cols - 1) / p.tile_cols;
+  // CTA pairs: 256-row tiles over two SMs.  Worth it when the paired kernel exists, every pair of SMs
+  // gets at least one tile, and pairing does not pad M by much (an M that is not a multiple of 256
+  // leaves the peer CTA of the last row of tiles with nothing to store).
+  {
+    TcLaunch pl = tl;
+    pl.pair = true;
+    const bool sc_ok = sc_mode == SCALE_PC || v->subchannel >= BK;
+    const int pair_tiles = ((m + 2 * BM - 1) / (2 * BM)) * p.tiles_n;
+    bool want = v->cta_group == B200_CTA_GROUP_PAIR ||
+                (v->cta_group == B200_CTA_GROUP_AUTO && pair_tiles >= dev->sm_count / 2 && m % (2 * BM) == 0);
+    if (v->schedule == B200_SCHEDULE_STANDARD && v->cta_group != B200_CTA_GROUP_PAIR) want = false;
+    if (want && sc_ok && tc_has(pl)) tl = pl;
+  }
+  const int tile_rows = tl.pair ? 2 * BM : BM;
+  p.tiles_m = (m + tile_rows - 1) / tile_rows;
   p.num_tiles = p.tiles_m * p.tiles_n;
   p.group_m = v->group_m > 0 ? v->group_m : 8;
   p.gate_col_offset = swiglu ? n : NBLK;
@@ -429,8 +500,10 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
   p.status = dev->status_dev;
   CUtensorMap tc;
   if (int rc = make_output_map(&tc, c, v->out_dtype, m, n, &p.tma_store); rc != 0) return rc;
-  int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
-  if (v->schedule == B200_SCHEDULE_STANDARD) grid = p.num_tiles;
+  const int cta_per_tile = tl.pair ? 2 : 1;
+  const int max_units = tl.pair ? dev->max_pair_clusters : dev->sm_count;  // tiles in flight
+  int grid = (p.num_tiles < max_units ? p.num_tiles : max_units) * cta_per_tile;
+  if (v->schedule == B200_SCHEDULE_STANDARD) grid = p.num_tiles * cta_per_tile;
   int rc = launch_tc(tl, ta, tb, tc, p, grid, stream);
   if (rc < 0) return fail("internal: no tcgen05 instantiation for this variant");
   return rc;

@@ -90,8 +90,12 @@ struct TileWork {
   long long sb_off;  // element offset of this tile's b_scale base
 };
 
-template <bool kAMn>
-__device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t) {
+// `rank` is the CTA's rank in its pair (always 0 for single-CTA kernels).  A pair works on 256 rows of
+// output: rank r owns rows [128 r, 128 r + 128) of them, and p.tiles_m counts 256-row tiles.
+template <bool kAMn, bool k2Cta>
+__device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t, int rank) {
+  constexpr int RM = k2Cta ? 2 * BM : BM;  // output rows per scheduled tile
+  const int rank_rows = k2Cta ? rank * BM : 0;
   TileWork w;
   w.k_valid = 0x7FFFFFFF;
   w.out_off = 0;
@@ -107,14 +111,14 @@ __device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t) {
     const int local = t - grp * per_group;
     const int mt = first_m + local % rows_here;
     const int nt = local / rows_here;
-    w.a_x = kAMn ? mt * BM : 0;
-    w.a_y = kAMn ? 0 : mt * BM;
+    w.a_x = kAMn ? mt * RM + rank_rows : 0;
+    w.a_y = kAMn ? 0 : mt * RM + rank_rows;
     w.b_y = 0;
     w.n0 = nt * p.tile_cols;
     w.n1 = w.n0 + p.gate_col_offset;
     w.k_len = p.K;
     w.num_kb = (p.K + BK - 1) / BK;
-    w.out_row0 = mt * BM;
+    w.out_row0 = mt * RM + rank_rows;
     w.row_lo = w.out_row0;
     w.row_hi = min(p.M, w.out_row0 + BM);
   } else if (p.mode == MODE_RAGGED_FWD) {
@@ -123,13 +127,13 @@ __device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t) {
     const int g = static_cast<int>(p.task_group_ids[task]);
     const int bs = static_cast<int>(p.task_block_starts[task]);
     w.a_x = 0;
-    w.a_y = bs;
+    w.a_y = bs + rank_rows;
     w.b_y = g * p.rows_per_group_b;
     w.n0 = nt * BN;
     w.n1 = w.n0 + NBLK;
     w.k_len = p.K;
     w.num_kb = (p.K + BK - 1) / BK;
-    w.out_row0 = bs;
+    w.out_row0 = bs + rank_rows;
     w.row_lo = static_cast<int>(p.task_actual_starts[task]);
     w.row_hi = static_cast<int>(p.task_actual_ends[task]);
     w.sb_off = static_cast<long long>(g) * p.lds_b * (p.subchannel ? p.scale_cols : 1);
@@ -140,15 +144,15 @@ __device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t) {
     const int mt = local / p.tiles_n;
     const int nt = local - mt * p.tiles_n;
     const int kg = static_cast<int>(p.group_sizes[g]);
-    w.a_x = kAMn ? mt * BM : 0;
-    w.a_y = kAMn ? g * p.rows_per_group_a : g * p.rows_per_group_a + mt * BM;
+    w.a_x = kAMn ? mt * RM + rank_rows : 0;
+    w.a_y = kAMn ? g * p.rows_per_group_a : g * p.rows_per_group_a + mt * RM + rank_rows;
     w.b_y = g * p.rows_per_group_b;
     w.n0 = nt * BN;
     w.n1 = w.n0 + NBLK;
     w.k_valid = kg;
     w.k_len = kg;
     w.num_kb = (kg + BK - 1) / BK;
-    w.out_row0 = mt * BM;
+    w.out_row0 = mt * RM + rank_rows;
     w.row_lo = w.out_row0;
     w.row_hi = min(p.M, w.out_row0 + BM);
     w.out_off = static_cast<long long>(g) * p.M * p.ldc;
@@ -165,7 +169,7 @@ __device__ __forceinline__ void expand_word(uint32_t w, uint32_t& lo, uint32_t& 
   hi = w & 0xF0F0F0F0u;
 }
 
-template <bool kInt4, bool kAMn, bool kBMn, int kScale, int kEpi, int kOut, bool kMaskK>
+template <bool kInt4, bool kAMn, bool kBMn, int kScale, int kEpi, int kOut, bool kMaskK, bool k2Cta = false>
 struct KernelTraits {
 #ifndef B200_UNPACK_WARPS
 #define B200_UNPACK_WARPS 8
@@ -192,13 +196,26 @@ struct KernelTraits {
 #ifndef B200_INT8_STAGES
 #define B200_INT8_STAGES 4
 #endif
-  static constexpr int kStages = kInt4 ? B200_INT4_STAGES : B200_INT8_STAGES;  // int8 UMMA stages
-  static constexpr int kPkStages = kInt4 ? B200_INT4_PK_STAGES : 0; // packed staging stages
-  static constexpr int kA8Bytes = BM * BK;        // 16 KB
-  static constexpr int kB8Bytes = BN * BK;        // 32 KB
+#ifndef B200_PAIR_INT4_STAGES
+#define B200_PAIR_INT4_STAGES 5
+#endif
+#ifndef B200_PAIR_INT4_PK_STAGES
+#define B200_PAIR_INT4_PK_STAGES 2
+#endif
+#ifndef B200_PAIR_INT8_STAGES
+#define B200_PAIR_INT8_STAGES 6
+#endif
+  // A CTA of a pair holds one 128-wide block of B (the MMA reads the other one from the peer), so
+  // its stages are a third smaller and more of them fit.
+  static constexpr int kBBlocks = k2Cta ? 1 : 2;
+  static constexpr int kStages = kInt4 ? (k2Cta ? B200_PAIR_INT4_STAGES : B200_INT4_STAGES)
+                                       : (k2Cta ? B200_PAIR_INT8_STAGES : B200_INT8_STAGES);  // int8 UMMA stages
+  static constexpr int kPkStages = kInt4 ? (k2Cta ? B200_PAIR_INT4_PK_STAGES : B200_INT4_PK_STAGES) : 0; // packed staging stages
+  static constexpr int kA8Bytes = BM * BK;                  // 16 KB
+  static constexpr int kB8Bytes = kBBlocks * NBLK * BK;     // 32 KB (pair: 16 KB)
   static constexpr int kStageBytes = kA8Bytes + kB8Bytes;
-  static constexpr int kPkABytes = BM * BK / 2;   // 8 KB
-  static constexpr int kPkBBytes = BN * BK / 2;   // 16 KB
+  static constexpr int kPkABytes = BM * BK / 2;             // 8 KB
+  static constexpr int kPkBBytes = kBBlocks * NBLK * BK / 2;  // 16 KB (pair: 8 KB)
   static constexpr int kPkStageBytes = kPkABytes + kPkBBytes;
   static constexpr int kBarBytes = 512;
   // results leave through shared memory + TMA stores (per-channel kernels; 2 KB per epilogue warp)
@@ -213,12 +230,12 @@ struct KernelTraits {
       1024 + kStages * kStageBytes + kPkStages * kPkStageBytes + kStagingBytes + kScaleStripBytes + kBarBytes;
 };
 
-template <bool kInt4, bool kAMn, bool kBMn, int kScale, int kEpi, int kOut, bool kMaskK>
-__global__ void __launch_bounds__(KernelTraits<kInt4, kAMn, kBMn, kScale, kEpi, kOut, kMaskK>::kThreads, 1)
+template <bool kInt4, bool kAMn, bool kBMn, int kScale, int kEpi, int kOut, bool kMaskK, bool k2Cta = false>
+__global__ void __launch_bounds__(KernelTraits<kInt4, kAMn, kBMn, kScale, kEpi, kOut, kMaskK, k2Cta>::kThreads, 1)
 gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b,
                        const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
-  using T = KernelTraits<kInt4, kAMn, kBMn, kScale, kEpi, kOut, kMaskK>;
+  using T = KernelTraits<kInt4, kAMn, kBMn, kScale, kEpi, kOut, kMaskK, k2Cta>;
   static_assert(kBMn || !kMaskK, "K masking is applied to an MN-major B operand");
   constexpr int S = T::kStages;
   constexpr int PS = T::kPkStages;
@@ -240,8 +257,13 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   auto pk_empty_bar = [&](int s) { return bar_base + 8u * (24 + s); };
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (32 + b); };
   auto acc_empty_bar = [&](int b) { return bar_base + 8u * (34 + b); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * 36);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 8 * 36 + 4);
+  auto peer_full_bar = [&](int s) { return bar_base + 8u * (36 + s); };  // leader CTA of a pair only
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * 44);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 8 * 44 + 4);
+  // CTA pairs: the cluster is the scheduling unit; the leader (rank 0) issues the MMAs for both.
+  const int cta_rank = k2Cta ? static_cast<int>(cluster_ctarank()) : 0;
+  const int tile0 = k2Cta ? static_cast<int>(cluster_id_x()) : static_cast<int>(blockIdx.x);
+  const int tile_step = k2Cta ? static_cast<int>(cluster_count_x()) : static_cast<int>(gridDim.x);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -257,6 +279,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     for (int s = 0; s < S; ++s) {
       mbar_init(full_bar(s), kInt4 ? T::kUnpackWarps : 1);
       mbar_init(empty_bar(s), 1);
+      mbar_init(peer_full_bar(s), 1);
     }
     for (int s = 0; s < PS; ++s) {
       mbar_init(pk_full_bar(s), 1);
@@ -264,18 +287,24 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full_bar(b), 1);
-      mbar_init(acc_empty_bar(b), T::kEpiWarps);
+      mbar_init(acc_empty_bar(b), (k2Cta ? 2 : 1) * T::kEpiWarps);  // pair: both CTAs' epilogue warps
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (k2Cta) {
+      tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (k2Cta) cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
+  else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   if constexpr (T::kRegBalance) {
@@ -291,8 +320,8 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (lane == 0) {
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
-        const TileWork w = decode_tile<kAMn>(p, t);
+      for (int t = tile0; t < p.num_tiles && ok; t += tile_step) {
+        const TileWork w = decode_tile<kAMn, k2Cta>(p, t, cta_rank);
         for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
           if constexpr (kInt4) {
             const int s = it % PS;
@@ -305,14 +334,18 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             } else {
               tma_load_2d(dst, &tmap_a, w.a_x + kb * (BK / 2), w.a_y, pk_full_bar(s));
             }
+            // a CTA of a pair brings one block of B: the leader the first, its peer the second
+            const int nb0 = (k2Cta && cta_rank != 0) ? w.n1 : w.n0;
             if constexpr (kBMn) {
-              tma_load_2d(dst + T::kPkABytes, &tmap_b, w.n0, w.b_y + kb * (BK / 2), pk_full_bar(s));
-              tma_load_2d(dst + T::kPkABytes + T::kPkBBytes / 2, &tmap_b, w.n1,
-                          w.b_y + kb * (BK / 2), pk_full_bar(s));
+              tma_load_2d(dst + T::kPkABytes, &tmap_b, nb0, w.b_y + kb * (BK / 2), pk_full_bar(s));
+              if constexpr (!k2Cta)
+                tma_load_2d(dst + T::kPkABytes + T::kPkBBytes / 2, &tmap_b, w.n1,
+                            w.b_y + kb * (BK / 2), pk_full_bar(s));
             } else {
-              tma_load_2d(dst + T::kPkABytes, &tmap_b, kb * (BK / 2), w.b_y + w.n0, pk_full_bar(s));
-              tma_load_2d(dst + T::kPkABytes + T::kPkBBytes / 2, &tmap_b, kb * (BK / 2), w.b_y + w.n1,
-                          pk_full_bar(s));
+              tma_load_2d(dst + T::kPkABytes, &tmap_b, kb * (BK / 2), w.b_y + nb0, pk_full_bar(s));
+              if constexpr (!k2Cta)
+                tma_load_2d(dst + T::kPkABytes + T::kPkBBytes / 2, &tmap_b, kb * (BK / 2), w.b_y + w.n1,
+                            pk_full_bar(s));
             }
           } else {
             const int s = it % S;
@@ -335,14 +368,17 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #ifdef B200_DBG_SKIP_B_LOAD
             continue;
 #endif
+            const int nb0 = (k2Cta && cta_rank != 0) ? w.n1 : w.n0;
             if constexpr (kBMn) {
-              tma_load_2d(dst + T::kA8Bytes, &tmap_b, w.n0, w.b_y + kb * BK, full_bar(s));
-              tma_load_2d(dst + T::kA8Bytes + T::kB8Bytes / 2, &tmap_b, w.n1, w.b_y + kb * BK,
-                          full_bar(s));
+              tma_load_2d(dst + T::kA8Bytes, &tmap_b, nb0, w.b_y + kb * BK, full_bar(s));
+              if constexpr (!k2Cta)
+                tma_load_2d(dst + T::kA8Bytes + T::kB8Bytes / 2, &tmap_b, w.n1, w.b_y + kb * BK,
+                            full_bar(s));
             } else {
-              tma_load_2d(dst + T::kA8Bytes, &tmap_b, kb * BK, w.b_y + w.n0, full_bar(s));
-              tma_load_2d(dst + T::kA8Bytes + T::kB8Bytes / 2, &tmap_b, kb * BK, w.b_y + w.n1,
-                          full_bar(s));
+              tma_load_2d(dst + T::kA8Bytes, &tmap_b, kb * BK, w.b_y + nb0, full_bar(s));
+              if constexpr (!k2Cta)
+                tma_load_2d(dst + T::kA8Bytes + T::kB8Bytes / 2, &tmap_b, kb * BK, w.b_y + w.n1,
+                            full_bar(s));
             }
           }
         }
@@ -352,7 +388,43 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------------------------------------------------ MMA issuer
     // The whole warp walks the schedule and waits on barriers together (so that loop control
     // stays warp-uniform); one elected lane issues the MMAs and the commits.
-    constexpr uint32_t idesc = umma_idesc_i8(BM, BN, kAMn, kBMn);
+    constexpr uint32_t idesc = umma_idesc_i8(k2Cta ? 2 * BM : BM, BN, kAMn, kBMn);
+    // single CTA or pair: the MMA, the commit, and the wait for operands (a pair's leader also waits
+    // for the peer's "stage full" signal, forwarded by the peer's warp 1)
+    auto mma = [&](uint32_t d, uint64_t da, uint64_t db, uint32_t acc_flag) {
+      if constexpr (k2Cta) umma_i8_pair(d, da, db, idesc, acc_flag);
+      else umma_i8(d, da, db, idesc, acc_flag);
+    };
+    auto commit = [&](uint32_t bar) {
+      if constexpr (k2Cta) umma_commit_pair(bar);
+      else umma_commit(bar);
+    };
+    auto wait_operands = [&](int s, uint32_t ph) -> bool {
+      bool got = mbar_wait(full_bar(s), ph, ctx, 20);
+      if constexpr (k2Cta) got = got && mbar_wait<true>(peer_full_bar(s), ph, ctx, 22);
+      return got;
+    };
+    auto wait_acc_empty = [&](int b, uint32_t ph) -> bool { return mbar_wait<k2Cta>(acc_empty_bar(b), ph, ctx, 21); };
+    if (k2Cta && cta_rank != 0) {
+      // Peer CTA of a pair: no MMAs are issued here.  Forward "my stage s is full" to the leader.
+      int it = 0;
+      bool ok = true;
+      for (int t = tile0; t < p.num_tiles && ok; t += tile_step) {
+        const TileWork w = decode_tile<kAMn, k2Cta>(p, t, cta_rank);
+        for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!__all_sync(0xFFFFFFFFu, mbar_wait(full_bar(s), ph, ctx, 23))) { ok = false; break; }
+          if (elect_one()) {
+#ifdef B200_FORWARD_FENCE
+            fence_proxy_async_smem();
+#endif
+            mbar_arrive_cluster(map_to_cta(peer_full_bar(s), 0));
+          }
+          __syncwarp();
+        }
+      }
+    } else {
     // descriptor = {lo: start address >> 4 | LBO >> 4 << 16, hi: SBO >> 4 | version | swizzle}
     constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
     constexpr uint32_t kALboField = (kAMn ? (BK * NBLK) >> 4 : 1u) << 16;
@@ -365,17 +437,17 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int it = 0;
     int grp = 0;  // accumulator hand-over counter (one per K-group)
     bool ok = true;
-    for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
-      const TileWork w = decode_tile<kAMn>(p, t);
+    for (int t = tile0; t < p.num_tiles && ok; t += tile_step) {
+      const TileWork w = decode_tile<kAMn, k2Cta>(p, t, cta_rank);
       const int total_mma = (w.k_len + 31) / 32;  // K=32 steps that hold real data
       if constexpr (kScale == SCALE_PC) {
         if (w.num_kb == 0) continue;
         const int b = grp & 1;
-        if (!__all_sync(0xFFFFFFFFu, mbar_wait(acc_empty_bar(b), ((grp >> 1) & 1) ^ 1u, ctx, 21))) { ok = false; break; }
+        if (!__all_sync(0xFFFFFFFFu, wait_acc_empty(b, ((grp >> 1) & 1) ^ 1u))) { ok = false; break; }
         for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
-          if (!__all_sync(0xFFFFFFFFu, mbar_wait(full_bar(s), ph, ctx, 20))) { ok = false; break; }
+          if (!__all_sync(0xFFFFFFFFu, wait_operands(s, ph))) { ok = false; break; }
           tc_fence_after_sync();
           if (elect_one()) {
             const uint32_t a_lo = a_lo0 + s * (T::kStageBytes >> 4);
@@ -384,11 +456,11 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
             for (int k = 0; k < BK / 32; ++k) {
               if (k < left)
-                umma_i8(tmem_base + b * BN, make_desc(a_lo + k * kAStep), make_desc(b_lo + k * kBStep), idesc,
-                        (kb | k) != 0 ? 1u : 0u);
+                mma(tmem_base + b * BN, make_desc(a_lo + k * kAStep), make_desc(b_lo + k * kBStep),
+                    (kb | k) != 0 ? 1u : 0u);
             }
-            umma_commit(empty_bar(s));
-            if (kb == w.num_kb - 1) umma_commit(acc_full_bar(b));
+            commit(empty_bar(s));
+            if (kb == w.num_kb - 1) commit(acc_full_bar(b));
           }
           __syncwarp();
         }
@@ -404,9 +476,9 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const bool group_start = (kb % kb_per_group) == 0;
           const bool group_end = ((kb + 1) % kb_per_group) == 0 || kb == w.num_kb - 1;
           if (group_start) {
-            if (!__all_sync(0xFFFFFFFFu, mbar_wait(acc_empty_bar(b), ((grp >> 1) & 1) ^ 1u, ctx, 21))) { ok = false; break; }
+            if (!__all_sync(0xFFFFFFFFu, wait_acc_empty(b, ((grp >> 1) & 1) ^ 1u))) { ok = false; break; }
           }
-          if (!__all_sync(0xFFFFFFFFu, mbar_wait(full_bar(s), ph, ctx, 20))) { ok = false; break; }
+          if (!__all_sync(0xFFFFFFFFu, wait_operands(s, ph))) { ok = false; break; }
           tc_fence_after_sync();
           if (elect_one()) {
             const uint32_t a_lo = a_lo0 + s * (T::kStageBytes >> 4);
@@ -415,16 +487,17 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
             for (int k = 0; k < BK / 32; ++k) {
               if (k < left)
-                umma_i8(tmem_base + b * BN, make_desc(a_lo + k * kAStep), make_desc(b_lo + k * kBStep), idesc,
-                        (group_start && k == 0) ? 0u : 1u);
+                mma(tmem_base + b * BN, make_desc(a_lo + k * kAStep), make_desc(b_lo + k * kBStep),
+                    (group_start && k == 0) ? 0u : 1u);
             }
-            umma_commit(empty_bar(s));
-            if (group_end) umma_commit(acc_full_bar(b));
+            commit(empty_bar(s));
+            if (group_end) commit(acc_full_bar(b));
           }
           __syncwarp();
           if (group_end) ++grp;
         }
-      } else {
+      } else if constexpr (!k2Cta) {
+        // K-groups of 32 or 64 (single-CTA kernels only; the host never pairs CTAs for them)
         int j = 0;  // MMA step within the tile
         for (int kb = 0; kb < w.num_kb && ok; ++kb, ++it) {
           const int s = it % S;
@@ -458,6 +531,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
+    }  // leader / single CTA
   } else if (warp >= T::kEpiWarp0 && warp < T::kUnpackWarp0) {
     // ------------------------------------------------------------------ epilogue
     if constexpr (T::kRegBalance) reg_alloc<T::kRegsEpilogue>();
@@ -467,14 +541,19 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int row_in_tile = q * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     int grp = 0;
+    // hand accumulator buffer b back to the MMA issuer (of a pair: the leader CTA's)
+    auto release_acc = [&](int b) {
+      if constexpr (k2Cta) mbar_arrive_cluster(map_to_cta(acc_empty_bar(b), 0));
+      else mbar_arrive(acc_empty_bar(b));
+    };
     int store_count = 0;  // TMA stores issued by this warp (selects the staging slot)
     bool ok = true;
     // Columns of the 256-wide accumulator this warp owns:
     //   per-channel, 4 warps: all 256 (SwiGLU: up 0..127 with gate 128..255)
     //   subchannel, 8 warps : plain -> [128*half, +128); SwiGLU -> up [64*half,+64) with gate 128+[64*half,+64)
     constexpr int kOwnCols = (kScale == SCALE_SC) ? 128 : 256;
-    for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
-      const TileWork w = decode_tile<kAMn>(p, t);
+    for (int t = tile0; t < p.num_tiles && ok; t += tile_step) {
+      const TileWork w = decode_tile<kAMn, k2Cta>(p, t, cta_rank);
       const int row = w.out_row0 + row_in_tile;
       const bool row_ok = (row >= w.row_lo) && (row < w.row_hi);
       const long long sa_row = w.sa_off + static_cast<long long>(row) * (kScale == SCALE_SC ? p.scale_cols : 1);
@@ -691,7 +770,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (!zero_tile) {
           tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive(acc_empty_bar(b));
+          if (lane == 0) release_acc(b);
           ++grp;
         }
       } else {
@@ -794,7 +873,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive(acc_empty_bar(b));
+          if (lane == 0) release_acc(b);
         }
         if (!ok) break;
         // activation + store, 32 output columns at a time
@@ -894,8 +973,8 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t b_dst0 = b_blk * (T::kB8Bytes / 2) + b_p0 * 128 + ((b_cn ^ (b_p0 & 7)) << 4);
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
-        const TileWork w = decode_tile<kAMn>(p, t);
+      for (int t = tile0; t < p.num_tiles && ok; t += tile_step) {
+        const TileWork w = decode_tile<kAMn, k2Cta>(p, t, cta_rank);
         for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
           const int ps = it % PS;
           const uint32_t pph = (it / PS) & 1;
@@ -906,12 +985,13 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint8_t* pk_b = pk_a + T::kPkABytes;
           // all loads of the stage first: they do not depend on the int8 stage being free
           // B items are handled in batches of at most 4 to bound the registers holding raw data
-          constexpr int kBItems = 1024 / UT;
+          constexpr int kBItems = (k2Cta ? 512 : 1024) / UT;  // one or two 128-wide blocks of B
           constexpr int kBBatch = kBItems < 4 ? kBItems : 4;
           uint4 xa[512 / UT];
           uint4 xb[kBBatch];  // K-major B: packed tile [256 rows][64 B], same item scheme as K-major A
           auto load_b = [&](int j) -> uint4 {
-            if constexpr (kBMn) return *reinterpret_cast<const uint4*>(pk_b + b_src0 + j * (kBRowsPerPass * 128));
+            if constexpr (kBMn && k2Cta) return *reinterpret_cast<const uint4*>(pk_b + m_src0 + j * (kMRowsPerPass * 128));
+            else if constexpr (kBMn) return *reinterpret_cast<const uint4*>(pk_b + b_src0 + j * (kBRowsPerPass * 128));
             else return *reinterpret_cast<const uint4*>(pk_b + a_src0 + j * (kARowsPerPass * 64));
           };
 #pragma unroll
@@ -955,6 +1035,16 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               if constexpr (!kBMn) {
                 *reinterpret_cast<uint4*>(b8 + a_dst_lo0 + j * (kARowsPerPass * 128)) = lo;
                 *reinterpret_cast<uint4*>(b8 + a_dst_hi0 + j * (kARowsPerPass * 128)) = hi;
+              } else if constexpr (k2Cta) {
+                // one block, same item scheme as an MN-major A: packed row m_p0 + kMRowsPerPass * j
+                if constexpr (kMaskK) {
+                  const int k_lo = kb * BK + 2 * (m_p0 + kMRowsPerPass * j);
+                  if (k_lo >= w.k_valid) lo = make_uint4(0, 0, 0, 0);
+                  if (k_lo + 1 >= w.k_valid) hi = make_uint4(0, 0, 0, 0);
+                }
+                const uint32_t d = m_dst0 + j * ((kMRowsPerPass / 16) * 32 * 128);
+                *reinterpret_cast<uint4*>(b8 + d) = lo;
+                *reinterpret_cast<uint4*>(b8 + d + 16 * 128) = hi;
               } else {
                 // packed row of this pass: b_p0 + kBRowsPerPass * j  (b_p0 < kBRowsPerPass <= 16)
                 constexpr int R = kBRowsPerPass;
@@ -984,10 +1074,12 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   // ------------------------------------------------------------------ teardown
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (k2Cta) cluster_sync_all();  // the peer no longer touches this CTA's shared memory or TMEM
+  else __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if constexpr (k2Cta) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 

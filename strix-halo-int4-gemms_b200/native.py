@@ -29,6 +29,7 @@ EPILOGUE_CODES = {Epilogue.NONE: 0, Epilogue.RELU2: 1, Epilogue.SWIGLU: 2}
 OUT_BF16, OUT_F32, OUT_S32 = 0, 1, 2
 PATH_AUTO, PATH_TCGEN05, PATH_SIMT = 0, 1, 2
 SCHEDULE_PERSISTENT, SCHEDULE_STANDARD = 0, 1
+CTA_GROUP_AUTO, CTA_GROUP_SINGLE, CTA_GROUP_PAIR = 0, 1, 2
 
 EXPORTED_SYMBOLS = (
     "b200_int4_gemms_dispatch_version",
@@ -60,7 +61,8 @@ class GemmVariant(ctypes.Structure):
         ("path", ctypes.c_int32),
         ("group_m", ctypes.c_int32),
         ("schedule", ctypes.c_int32),
-        ("reserved", ctypes.c_int32 * 6),
+        ("cta_group", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 5),
     ]
 
 
@@ -276,6 +278,7 @@ def make_variant(
     path: int = PATH_AUTO,
     group_m: int = 0,
     schedule: KernelSchedule = KernelSchedule.PERSISTENT,
+    cta_group: int = CTA_GROUP_AUTO,
 ) -> GemmVariant:
     variant = GemmVariant()
     variant.dtype = DTYPE_CODES[dtype]
@@ -288,6 +291,11 @@ def make_variant(
     variant.path = int(path)
     variant.group_m = int(group_m)
     variant.schedule = SCHEDULE_STANDARD if schedule is KernelSchedule.STANDARD else SCHEDULE_PERSISTENT
+    # B200_INT4_GEMMS_CTA_GROUP=1|2 overrides an AUTO choice (A/B measurements of the single-CTA and
+    # CTA-pair kernels without touching call sites); an explicit argument wins.
+    if int(cta_group) == CTA_GROUP_AUTO and os.environ.get("B200_INT4_GEMMS_CTA_GROUP", "") in ("1", "2"):
+        cta_group = int(os.environ["B200_INT4_GEMMS_CTA_GROUP"])
+    variant.cta_group = int(cta_group)
     return variant
 
 

@@ -74,7 +74,7 @@ def assert_close_rms(got: np.ndarray, want: np.ndarray, *, rtol=1e-2, atol_rms=1
 # ----------------------------------------------------------------------------------------------
 # GPU side: calls through the C ABI (ctypes) with arbitrary shapes
 # ----------------------------------------------------------------------------------------------
-def abi_dense(pkg, case, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue="none", out="bf16", path=0, schedule="persistent"):
+def abi_dense(pkg, case, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue="none", out="bf16", path=0, schedule="persistent", cta_group=0):
     """One dense launch through ``b200_int4_gemms_launch_dense``; returns the CUDA output tensor."""
     from strix_halo_int4_gemms_b200 import native
 
@@ -87,6 +87,7 @@ def abi_dense(pkg, case, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue=
         dtype=pkg.OperandDType(dtype), layout=getattr(pkg.GemmLayout, layout.upper()), scale=scale_spec(pkg, sub),
         epilogue=pkg.Epilogue(epilogue), out_dtype=code, path=path,
         schedule=pkg.KernelSchedule.STANDARD if schedule == "standard" else pkg.KernelSchedule.PERSISTENT,
+        cta_group=cta_group,
     )
     native.launch_dense(
         variant, device_index=0, stream_handle=torch.cuda.current_stream().cuda_stream,
@@ -99,11 +100,11 @@ def abi_dense(pkg, case, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue=
     return c
 
 
-def check_dense(pkg, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue="none", out="bf16", path=0, seed=0, exact=None, schedule="persistent"):
+def check_dense(pkg, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue="none", out="bf16", path=0, seed=0, exact=None, schedule="persistent", cta_group=0):
     """Run one dense case on the GPU and compare with the oracle.  ``exact`` defaults to bit
     equality for everything except SwiGLU (whose exp() is implementation-defined to an ulp)."""
     case = dense_case(pkg, m=m, n=n, k=k, dtype=dtype, layout=layout, sub=sub, epilogue=epilogue, seed=seed)
-    got = abi_dense(pkg, case, m=m, n=n, k=k, dtype=dtype, layout=layout, sub=sub, epilogue=epilogue, out=out, path=path, schedule=schedule)
+    got = abi_dense(pkg, case, m=m, n=n, k=k, dtype=dtype, layout=layout, sub=sub, epilogue=epilogue, out=out, path=path, schedule=schedule, cta_group=cta_group)
     if out == "s32":
         want = oracle.int32_accumulators(case["a"].numpy(), case["b"].numpy(), int4=dtype == "int4", layout=layout)
         np.testing.assert_array_equal(got.cpu().numpy(), want)

@@ -85,6 +85,45 @@ def test_standard_and_persistent_schedules_agree(pkg):
     assert torch.equal(a, b)
 
 
+SINGLE, PAIR = 1, 2  # b200_gemm_variant.cta_group
+
+
+@pytest.mark.parametrize("dtype", ["int4", "int8"])
+@pytest.mark.parametrize("shape", [(256, 256, 128), (512, 768, 1024), (390, 528, 416)])
+def test_cta_pair_accumulators_bit_exact(pkg, dtype, shape):
+    """256-row tiles over two SMs (tcgen05 cta_group::2), incl. an M whose last pair is half empty."""
+    m, n, k = shape
+    check_dense(pkg, m=m, n=n, k=k, dtype=dtype, out="s32", path=TCGEN05, cta_group=PAIR)
+
+
+@pytest.mark.parametrize("dtype,layout,sub,epilogue,out", [
+    ("int4", "nn", 0, "none", "bf16"), ("int4", "nn", 0, "relu2", "bf16"), ("int4", "nn", 0, "swiglu", "bf16"),
+    ("int4", "nn", 0, "none", "f32"), ("int4", "nn", 256, "none", "bf16"), ("int4", "nn", 128, "swiglu", "bf16"),
+    ("int4", "nt", 0, "none", "bf16"), ("int8", "nn", 0, "none", "bf16"), ("int8", "nn", 0, "relu2", "bf16"),
+    ("int8", "nn", 0, "swiglu", "bf16"),
+])
+def test_cta_pair_kernels_match_the_oracle(pkg, dtype, layout, sub, epilogue, out):
+    check_dense(pkg, m=640, n=384, k=1024, dtype=dtype, layout=layout, sub=sub, epilogue=epilogue, out=out,
+                path=TCGEN05, cta_group=PAIR, seed=21)
+    check_dense(pkg, m=200, n=272, k=160, dtype=dtype, layout=layout, sub=sub, epilogue=epilogue, out=out,
+                path=TCGEN05, cta_group=PAIR, seed=22)
+
+
+def test_cta_pair_and_single_agree_bit_for_bit(pkg):
+    """Many tiles per cluster (persistent loop, both accumulator buffers, all pipeline phases)."""
+    for dtype, sub, epilogue in (("int4", 0, "none"), ("int8", 0, "relu2"), ("int4", 256, "swiglu")):
+        case = dense_case(pkg, m=2048, n=4608, k=1280, dtype=dtype, sub=sub, epilogue=epilogue, seed=23)
+        kw = dict(m=2048, n=4608, k=1280, dtype=dtype, sub=sub, epilogue=epilogue, path=TCGEN05)
+        one = abi_dense(pkg, case, cta_group=SINGLE, **kw)
+        two = abi_dense(pkg, case, cta_group=PAIR, **kw)
+        assert torch.equal(one, two)
+
+
+def test_cta_pair_falls_back_when_no_paired_kernel_exists(pkg):
+    check_dense(pkg, m=256, n=256, k=256, sub=32, path=TCGEN05, cta_group=PAIR)      # K-groups of 32: single-CTA kernel
+    check_dense(pkg, m=256, n=256, k=256, layout="tn", path=TCGEN05, cta_group=PAIR)
+
+
 def test_reference_fixtures_on_the_gpu(pkg, golden):
     """The 54 dense cells the reference package produced on CPU, recomputed by the CUDA path."""
     for key in (str(n) for n in golden["dense/names"]):
