@@ -219,6 +219,14 @@ int ensure_device(int device_index, DeviceState** out) {
   }
     B200_FOR_EACH_TC_KERNEL(X)
 #undef X
+    // B200_INT4_GEMMS_MAX_SMS=<n>: use at most n SMs (scaling experiments; results do not change)
+    if (const char* cap = std::getenv("B200_INT4_GEMMS_MAX_SMS"); cap != nullptr) {
+      const int n = std::atoi(cap);
+      if (n >= 2 && n < st.sm_count) {
+        st.sm_count = n;
+        if (st.max_pair_clusters > n / 2) st.max_pair_clusters = n / 2;
+      }
+    }
     if (std::getenv("B200_INT4_GEMMS_VERBOSE") != nullptr)
       std::fprintf(stderr, "b200_int4_gemms: device %d: %d SMs, %d co-resident CTA pairs\n", device_index,
                    st.sm_count, st.max_pair_clusters);

@@ -197,10 +197,10 @@ struct KernelTraits {
 #define B200_INT8_STAGES 4
 #endif
 #ifndef B200_PAIR_INT4_STAGES
-#define B200_PAIR_INT4_STAGES 5
+#define B200_PAIR_INT4_STAGES 4
 #endif
 #ifndef B200_PAIR_INT4_PK_STAGES
-#define B200_PAIR_INT4_PK_STAGES 2
+#define B200_PAIR_INT4_PK_STAGES 4
 #endif
 #ifndef B200_PAIR_INT8_STAGES
 #define B200_PAIR_INT8_STAGES 6

@@ -12,6 +12,7 @@ a CUDA device, the launchers raise.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from dataclasses import dataclass
 from pathlib import Path
