@@ -152,6 +152,7 @@ cudaError_t set_smem(Kernel kernel, int bytes) {
   X(true, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, true)            \
   X(true, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, true)           \
   X(true, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, true)         \
+  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, false, true)            \
   X(true, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, true)          \
   X(false, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true)          \
   X(false, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, true)         \
@@ -534,7 +535,7 @@ extern "C" int b200_int4_gemms_launch_ragged_fwd(
     return fail("ragged forward kernel pointers must be non-null");
   if (m <= 0 || n <= 0 || k_packed <= 0 || groups <= 0) return fail("m, n, k_packed and groups must be positive");
   if (num_tasks < 0) return fail("num_tasks must be non-negative");
-  if (block_rows <= 0 || block_rows > BM) return fail("block_rows must be in [1, 128]");
+  if (block_rows <= 0 || block_rows > 2 * BM) return fail("block_rows must be in [1, 256]");
   if (k_packed >= 65536) return fail("int4 path supports k < 131072");
   if (num_tasks == 0) return 0;
   DeviceState* dev = nullptr;
@@ -548,11 +549,15 @@ extern "C" int b200_int4_gemms_launch_ragged_fwd(
   if (sc_mode == SCALE_SC && scale_cols != (k + v->subchannel - 1) / v->subchannel)
     return fail("scale_cols does not match ceil(K / subchannel)");
 
+  // Tasks of more than 128 rows run on CTA pairs: rank 0 takes the first 128 rows of the block, rank 1 the rest.
   TcLaunch tl{true, a_t, true, false, sc_mode, EPI_NONE, v->out_dtype};
-  bool tc_ok = !b_t && !a_t && tc_has(tl) && aligned16(lhs) && aligned16(rhs) && (k_packed % 16 == 0) && (n % 16 == 0);
+  tl.pair = block_rows > BM;
+  const bool pair_ok = !tl.pair || sc_mode == SCALE_PC || v->subchannel >= BK;
+  bool tc_ok = !b_t && !a_t && pair_ok && tc_has(tl) && aligned16(lhs) && aligned16(rhs) && (k_packed % 16 == 0) && (n % 16 == 0);
   if (v->path == B200_PATH_SIMT) tc_ok = false;
   if (v->path == B200_PATH_TCGEN05 && !tc_ok)
-    return fail("the tcgen05 ragged forward kernel needs layout NN, 16-byte aligned operands and k_packed, n multiples of 16");
+    return fail("the tcgen05 ragged forward kernel needs layout NN, 16-byte aligned operands, k_packed and n multiples of 16, "
+                "and (for block_rows > 128) per-channel scales or K-groups of at least 128");
 
   if (!tc_ok) {
     SimtParams sp{};
@@ -614,7 +619,9 @@ extern "C" int b200_int4_gemms_launch_ragged_fwd(
   p.status = dev->status_dev;
   CUtensorMap tc;
   if (int rc = make_output_map(&tc, out, v->out_dtype, m, n, &p.tma_store); rc != 0) return rc;
-  const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
+  const int cta_per_tile = tl.pair ? 2 : 1;
+  const int max_units = tl.pair ? dev->max_pair_clusters : dev->sm_count;
+  const int grid = (p.num_tiles < max_units ? p.num_tiles : max_units) * cta_per_tile;
   int rc = launch_tc(tl, ta, tb, tc, p, grid, stream);
   if (rc < 0) return fail("internal: no tcgen05 instantiation for this variant");
   return rc;

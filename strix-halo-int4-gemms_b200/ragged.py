@@ -13,16 +13,20 @@ library, whose scheduler walks (row-block task x column tile) pairs for the forw
 
 Tile defaults are the kernel's real ones (128-row tasks, 256 columns, 128-deep K stages).  The
 kernel masks rows outside ``[actual_start, actual_end)`` of a task itself, so any task height
-up to 128 that is a multiple of ``align_tile`` works.
+up to 256 that is a multiple of ``align_tile`` works.  Tasks of more than 128 rows run on pairs
+of SMs (one 256 x 256 tile per pair); ``RaggedDotConfig.pair_tasks`` says when the default
+128-row tasks are widened to 256 rows.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
 from typing import Any
 
 from .metadata import GemmLayout, ScaleMode, ScaleSpec
 
-MAX_TASK_ROWS = 128
+MAX_TASK_ROWS = 256
+PAIR_TASK_ROWS = 256          # task height of the CTA-pair kernel
+PAIR_MIN_MEAN_GROUP_ROWS = 256  # widen tasks automatically when groups average at least this many rows
 
 RAGGED_FAMILY = "ragged_dot_int4"
 RAGGED_FWD = "fwd"
@@ -43,6 +47,10 @@ class RaggedDotConfig:
     enable_even_k_fast_path: bool = True
     num_warps: int = 10
     num_stages: int = 3
+    # None: 128-row tasks are widened to 256 rows (CTA pairs) when the groups are large enough and
+    # the kernel supports it for the call; False: never; True: whenever the kernel supports it.
+    # Only looked at when ``block_m`` is 128 and no prebuilt ``group_info`` is passed.
+    pair_tasks: bool | None = None
 
     def __post_init__(self) -> None:
         if min(self.block_m, self.block_n, self.block_k) <= 0:
@@ -433,6 +441,14 @@ def ragged_dot_int4(
         raise ValueError(f"config.block_m must be at most {MAX_TASK_ROWS}; got {config.block_m}")
 
     rows, cols, k_packed, groups = _forward_logical_shape(lhs, rhs, layout)
+    pair_capable = layout is GemmLayout.NN and (
+        scale.mode is ScaleMode.PER_CHANNEL or (scale.subchannel_size or 0) >= 128)
+    if config.block_m > 128 and not pair_capable:
+        raise ValueError("tasks of more than 128 rows need layout NN and per-channel scales or K-groups of at least 128")
+    if group_info is None and config.block_m == 128 and pair_capable and config.pair_tasks is not False:
+        if config.pair_tasks is True or rows >= PAIR_MIN_MEAN_GROUP_ROWS * groups:
+            if PAIR_TASK_ROWS % config.align_tile == 0:
+                config = replace(config, block_m=PAIR_TASK_ROWS)
     if group_info is None:
         _validate_group_sizes(torch, group_sizes, groups=groups, rows=rows)
         if group_sizes.device != lhs.device:

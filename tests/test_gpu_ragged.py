@@ -59,6 +59,27 @@ def test_forward_task_heights(pkg, block_m, align):
     np.testing.assert_array_equal(as_f32(out), want)
 
 
+@pytest.mark.parametrize("sub,out_dtype", [(0, None), (0, torch.float32), (128, None), (256, torch.float32)])
+def test_forward_256_row_tasks_on_cta_pairs(pkg, sub, out_dtype):
+    """Tasks of 256 rows: one 256 x 256 tile per pair of SMs, rank 1 takes rows 128..255 of the block."""
+    cfg = pkg.RaggedDotConfig(block_m=256)
+    sizes = [300, 0, 256, 7, 129, 512, 1, 255]
+    out, want = _fwd(pkg, sizes, 512, 1408, sub=sub, config=cfg, out_dtype=out_dtype, seed=11)
+    np.testing.assert_array_equal(as_f32(out), want)
+
+
+def test_forward_widens_tasks_for_large_groups(pkg):
+    """Default config: groups averaging >= 256 rows are cut into 256-row tasks; the result is the same
+    as with 128-row tasks pinned."""
+    sizes = [512, 300, 700, 256]
+    auto, want = _fwd(pkg, sizes, 1024, 768, seed=12)
+    pinned, _ = _fwd(pkg, sizes, 1024, 768, seed=12, config=pkg.RaggedDotConfig(pair_tasks=False))
+    np.testing.assert_array_equal(as_f32(auto), want)
+    assert torch.equal(auto, pinned)
+    with pytest.raises(ValueError, match="more than 128 rows"):
+        _fwd(pkg, sizes, 1024, 768, sub=32, config=pkg.RaggedDotConfig(block_m=256), seed=12)
+
+
 @pytest.mark.parametrize("layout", ["nn", "nt", "tn", "tt"])
 @pytest.mark.parametrize("sub", [0, 32])
 def test_forward_layouts_and_odd_k(pkg, layout, sub):

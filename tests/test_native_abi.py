@@ -87,8 +87,8 @@ def test_ragged_entry_points_check_arguments(pkg, native_lib):
     v4 = native.make_variant(dtype=pkg.OperandDType.INT4, layout=pkg.GemmLayout.NN, scale=pc, epilogue=pkg.Epilogue.NONE, out_dtype=native.OUT_BF16)
     rc = lib.b200_int4_gemms_launch_ragged_fwd(ctypes.byref(v4), 0, 0, *([ctypes.c_void_p(0)] * 9), 128, 256, 32, 1, 1, 1, 128)
     assert rc == 1 and "pointers must be non-null" in lib.b200_int4_gemms_last_error().decode()
-    rc = lib.b200_int4_gemms_launch_ragged_fwd(ctypes.byref(v4), 0, 0, *nine, 128, 256, 32, 1, 1, 1, 256)
-    assert rc == 1 and lib.b200_int4_gemms_last_error().decode() == "block_rows must be in [1, 128]"
+    rc = lib.b200_int4_gemms_launch_ragged_fwd(ctypes.byref(v4), 0, 0, *nine, 128, 256, 32, 1, 1, 1, 264)
+    assert rc == 1 and lib.b200_int4_gemms_last_error().decode() == "block_rows must be in [1, 256]"
     rc = lib.b200_int4_gemms_launch_ragged_bwd(ctypes.byref(v4), 0, 0, *([ctypes.c_void_p(16)] * 6), 128, 256, 32, 1, 2)
     assert rc == 1 and lib.b200_int4_gemms_last_error().decode() == "ragged backward stores float32"
 
