@@ -237,7 +237,10 @@ def make_runner(torch, pkg, w, problems):
                 native.launch_dense(variant, device_index=device_index, stream_handle=stream, m=w["m"], n=w["n"], k=w["k"], **ptrs)
         return step, len(problems)
     if w["kind"] == "ragged_fwd":
-        cfg = RaggedDotConfig()
+        # the task height ragged_dot_int4 itself picks for groups this large: 256-row tasks on pairs of SMs
+        from strix_halo_int4_gemms_b200.ragged import PAIR_MIN_MEAN_GROUP_ROWS, PAIR_TASK_ROWS
+        rows, groups = problems[0]["lhs"].shape[0], len(problems[0]["group_sizes"])
+        cfg = RaggedDotConfig(block_m=PAIR_TASK_ROWS if rows >= PAIR_MIN_MEAN_GROUP_ROWS * groups else 128)
         infos = [pkg.calculate_group_info(p["group_sizes"], cfg.block_m, align_tile=cfg.align_tile) for p in problems]
 
         def step():
