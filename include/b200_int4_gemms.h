@@ -157,6 +157,70 @@ int b200_int4_gemms_launch_ragged_bwd(const b200_gemm_variant* variant, int devi
 int b200_int4_gemms_unpack_int4(int device_index, uintptr_t stream_handle, const void* packed,
                                 void* out_int8, int64_t rows, int64_t cols_packed);
 
+/* ---- Callers and data formats either side of the GEMM path ------------------------------------ */
+
+/* Row-block tasks of the grouped forward pass, built on the device: the CUDA counterpart of the
+ * reference's task builder (ragged.py:127-185 Triton kernel, :201-323 calculate_group_info).
+ * For group g with rows [s, e): aligned = floor(s / align) * align; task b of the group has
+ * block_start = aligned + b * tile, actual_start = max(block_start, s), actual_end = min(block_start +
+ * tile, e); empty groups make no task; tasks are written in group order.
+ *   group_sizes   int64 [groups] on the device
+ *   task_*        int64 [max_tasks] outputs; entries past the task count are empty tasks (all zero)
+ *   num_tasks_dev int32 [1] output: min(task count, max_tasks)
+ *   overflow_dev  int32 [1] output: 1 when the tasks did not fit in max_tasks (then the arrays hold the
+ *                 first max_tasks tasks), else 0.  rows / tile + 2 * groups tasks always fit.
+ * Nothing returns to the host: pair it with b200_int4_gemms_launch_ragged_fwd_device_tasks. */
+int b200_int4_gemms_group_info(int device_index, uintptr_t stream_handle, const int64_t* group_sizes,
+                               int32_t groups, int32_t tile, int32_t align, int64_t* task_group_ids,
+                               int64_t* task_block_starts, int64_t* task_actual_starts,
+                               int64_t* task_actual_ends, int32_t max_tasks, int32_t* num_tasks_dev,
+                               int32_t* overflow_dev);
+
+/* b200_int4_gemms_launch_ragged_fwd with the task count left on the device (num_tasks_dev, as written
+ * by b200_int4_gemms_group_info); max_tasks is the capacity of the task arrays.  No reference
+ * counterpart: the reference reads the task count back to the host (ragged.py:275). */
+int b200_int4_gemms_launch_ragged_fwd_device_tasks(
+    const b200_gemm_variant* variant, int device_index, uintptr_t stream_handle, const void* lhs,
+    const void* rhs, const void* lhs_scale, const void* rhs_scale, const int64_t* task_group_ids,
+    const int64_t* task_block_starts, const int64_t* task_actual_starts,
+    const int64_t* task_actual_ends, const int32_t* num_tasks_dev, void* out, int32_t m, int32_t n,
+    int32_t k_packed, int32_t scale_cols, int32_t max_tasks, int32_t groups, int32_t block_rows);
+
+/* Grouped backward over FLAT operands: all tokens back to back, no per-group padding.
+ *   out[g] = (lhs[tokens of g, :]^T @ rhs[tokens of g, :]) * a_scale[g] * b_scale[g]
+ * No reference counterpart: the reference API only takes operands stacked per group and padded to a
+ * common capacity (ragged.py:1232-1402); this entry removes that repack.
+ *   variant     int4, layout TN, per-channel scales, no epilogue, f32 output
+ *   lhs         int4 [ceil(tokens/2), m]: byte (p, i) holds tokens 2p (low nibble) and 2p+1 of feature i
+ *   rhs         int4 [ceil(tokens/2), n], same packing (b200_int4_gemms_repack_tokens makes both)
+ *   lhs_scale   bf16 [groups, m]; rhs_scale bf16 [groups, n]
+ *   group_sizes int64 [groups], summing to tokens; groups may start on odd tokens
+ *   out         f32 [groups, m, n]
+ *   workspace   device scratch, 8-byte aligned, b200_int4_gemms_ragged_bwd_flat_workspace_bytes(groups)
+ *               bytes: the first token of every group, written by a small scan kernel launched first
+ *               on the same stream.  Calls that share a workspace must not overlap.
+ * A single group must stay below 131072 tokens (accumulator headroom of the int4 encoding). */
+size_t b200_int4_gemms_ragged_bwd_flat_workspace_bytes(int32_t groups);
+int b200_int4_gemms_launch_ragged_bwd_flat(const b200_gemm_variant* variant, int device_index,
+                                           uintptr_t stream_handle, const void* lhs, const void* rhs,
+                                           const void* lhs_scale, const void* rhs_scale,
+                                           const int64_t* group_sizes, void* out, void* workspace,
+                                           size_t workspace_bytes, int32_t m, int32_t n, int64_t tokens,
+                                           int32_t groups);
+
+/* bf16 [rows, cols] -> quantisation codes clamp(round_half_even(float(x) / scale), qmin, qmax):
+ * bits = 4: packed two per byte along the last axis (even index in the low nibble, an odd cols pads
+ * with a zero code), dst u8 [rows, ceil(cols/2)]; bits = 8: dst int8 [rows, cols].
+ * GPU form of fake_quant_int followed by pack_int4_k_major (quant.py:14-38), bit-identical to them. */
+int b200_int4_gemms_quantize(int device_index, uintptr_t stream_handle, const void* src_bf16, void* dst,
+                             int64_t rows, int64_t cols, int32_t bits, float scale);
+
+/* int4 packed along features, src u8 [rows, cols/2] (the forward operand format) -> packed along
+ * tokens, dst u8 [ceil(rows/2), cols] (the flat backward operand format); cols even.  No reference
+ * counterpart (the reference repacks on the host, tests/test_ragged_dot.py:55-81). */
+int b200_int4_gemms_repack_tokens(int device_index, uintptr_t stream_handle, const void* src, void* dst,
+                                  int64_t rows, int64_t cols);
+
 #ifdef __cplusplus
 }
 #endif

@@ -317,6 +317,42 @@ def ragged_dot_bwd(
 
 
 # ----------------------------------------------------------------------------------------------
+# formats either side of the path that the reference only handles on the host
+# ----------------------------------------------------------------------------------------------
+def repack_tokens(packed: np.ndarray) -> np.ndarray:
+    """Packed int4 ``[T, F/2]`` (features paired) -> ``[ceil(T/2), F]`` (tokens paired).
+
+    What the reference's test helper does per group with ``pack_int4_k_major(x.T).T``
+    (tests/test_ragged_dot.py:67-81), here for one flat token axis.
+    """
+    codes = unpack_int4_k_major(packed)                     # [T, F]
+    return np.ascontiguousarray(pack_int4_k_major(np.ascontiguousarray(codes.T)).T)
+
+
+def ragged_dot_bwd_flat(
+    lhs_tokens: np.ndarray,
+    rhs_tokens: np.ndarray,
+    group_sizes,
+    a_scale_bits: np.ndarray,
+    b_scale_bits: np.ndarray,
+) -> np.ndarray:
+    """Grouped backward dot over flat token-packed operands: the math of test_ragged_dot.py:84-97 with the
+    groups taken as consecutive token ranges of ``lhs [ceil(T/2), M]`` / ``rhs [ceil(T/2), N]``."""
+    x = unpack_int4_k_major(np.ascontiguousarray(lhs_tokens.T)).T    # [T', M] codes, T' = 2 * ceil(T/2)
+    dy = unpack_int4_k_major(np.ascontiguousarray(rhs_tokens.T)).T   # [T', N]
+    sa = bf16_bits_to_f32(a_scale_bits)
+    sb = bf16_bits_to_f32(b_scale_bits)
+    sizes = [int(s) for s in group_sizes]
+    out = np.zeros((len(sizes), x.shape[1], dy.shape[1]), dtype=np.float32)
+    start = 0
+    for g, size in enumerate(sizes):
+        if size:
+            out[g] = scaled_matmul(np.ascontiguousarray(x[start:start + size].T), dy[start:start + size], sa[g], sb[g])
+        start += size
+    return out
+
+
+# ----------------------------------------------------------------------------------------------
 # metric (reference benchmarking.py:104-111)
 # ----------------------------------------------------------------------------------------------
 def tops_for_runtime(m: int, n: int, k: int, runtime_ms: float) -> float:

@@ -54,6 +54,8 @@ from .quant import (
     pack_int4_k_major,
     pack_ragged_rhs_subchannel_scales,
     pack_rhs_subchannel_scales,
+    quantize_int_cuda,
+    repack_int4_tokens,
     unpack_int4_k_major,
 )
 from .ragged import (
@@ -61,13 +63,19 @@ from .ragged import (
     RaggedDotConfig,
     RaggedGroupInfo,
     calculate_group_info,
+    calculate_group_info_on_device,
     ragged_dot_int4,
     ragged_dot_int4_bwd,
+    ragged_dot_int4_bwd_flat,
 )
 from .registry import KernelRegistry, default_registry
 from .torch_ops import TORCH_GEMM_OP, TORCH_OP_NAMESPACE, register_torch_ops, torch_gemm
 
 __all__ = [
+    "calculate_group_info_on_device",
+    "quantize_int_cuda",
+    "ragged_dot_int4_bwd_flat",
+    "repack_int4_tokens",
     "ACC_DTYPE",
     "ARCH",
     "AutotuneResult",

@@ -14,6 +14,7 @@
 #include "../../include/b200_int4_gemms.h"
 #include "gemm_kernel.cuh"
 #include "simt_kernel.cuh"
+#include "prep_kernels.cuh"
 
 namespace {
 
@@ -518,13 +519,16 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
   return rc;
 }
 
-extern "C" int b200_int4_gemms_launch_ragged_fwd(
+namespace {
+
+// Grouped forward launch.  num_tasks_dev == nullptr: the host knows the task count (num_tasks).  Otherwise
+// the task arrays hold num_tasks entries of capacity and the device-side count says how many are real.
+int launch_ragged_fwd_impl(
     const b200_gemm_variant* v, int device_index, uintptr_t stream_handle, const void* lhs,
     const void* rhs, const void* lhs_scale, const void* rhs_scale, const int64_t* task_group_ids,
     const int64_t* task_block_starts, const int64_t* task_actual_starts,
-    const int64_t* task_actual_ends, void* out, int32_t m, int32_t n, int32_t k_packed,
-    int32_t scale_cols, int32_t num_tasks, int32_t groups, int32_t block_rows) {
-  g_last_error.clear();
+    const int64_t* task_actual_ends, const int32_t* num_tasks_dev, void* out, int32_t m, int32_t n,
+    int32_t k_packed, int32_t scale_cols, int32_t num_tasks, int32_t groups, int32_t block_rows) {
   if (int rc = check_variant(v); rc != 0) return rc;
   if (v->dtype != B200_DTYPE_INT4) return fail("ragged kernels take packed int4 operands");
   if (v->epilogue != B200_EPILOGUE_NONE) return fail("ragged kernels have no fused activation");
@@ -585,6 +589,7 @@ extern "C" int b200_int4_gemms_launch_ragged_fwd(
     sp.task_actual_starts = reinterpret_cast<const long long*>(task_actual_starts);
     sp.task_actual_ends = reinterpret_cast<const long long*>(task_actual_ends);
     sp.out = out;
+    // with a device-side count the padding entries are empty tasks (actual_start == actual_end): no rows
     return launch_simt(sp, block_rows, num_tasks, stream);
   }
 
@@ -613,6 +618,7 @@ extern "C" int b200_int4_gemms_launch_ragged_fwd(
   p.task_block_starts = reinterpret_cast<const long long*>(task_block_starts);
   p.task_actual_starts = reinterpret_cast<const long long*>(task_actual_starts);
   p.task_actual_ends = reinterpret_cast<const long long*>(task_actual_ends);
+  p.num_tasks_dev = num_tasks_dev;
   p.a_scale = static_cast<const __nv_bfloat16*>(lhs_scale);
   p.b_scale = static_cast<const __nv_bfloat16*>(rhs_scale);
   p.out = out;
@@ -627,13 +633,105 @@ extern "C" int b200_int4_gemms_launch_ragged_fwd(
   return rc;
 }
 
-extern "C" int b200_int4_gemms_launch_ragged_bwd(const b200_gemm_variant* v, int device_index,
-                                                 uintptr_t stream_handle, const void* lhs,
-                                                 const void* rhs, const void* lhs_scale,
-                                                 const void* rhs_scale, const int64_t* group_sizes,
-                                                 void* out, int32_t m, int32_t n, int32_t k_packed,
-                                                 int32_t scale_cols, int32_t groups) {
+}  // namespace
+
+extern "C" int b200_int4_gemms_launch_ragged_fwd(
+    const b200_gemm_variant* v, int device_index, uintptr_t stream_handle, const void* lhs,
+    const void* rhs, const void* lhs_scale, const void* rhs_scale, const int64_t* task_group_ids,
+    const int64_t* task_block_starts, const int64_t* task_actual_starts,
+    const int64_t* task_actual_ends, void* out, int32_t m, int32_t n, int32_t k_packed,
+    int32_t scale_cols, int32_t num_tasks, int32_t groups, int32_t block_rows) {
   g_last_error.clear();
+  return launch_ragged_fwd_impl(v, device_index, stream_handle, lhs, rhs, lhs_scale, rhs_scale, task_group_ids,
+                                task_block_starts, task_actual_starts, task_actual_ends, nullptr, out, m, n,
+                                k_packed, scale_cols, num_tasks, groups, block_rows);
+}
+
+extern "C" int b200_int4_gemms_launch_ragged_fwd_device_tasks(
+    const b200_gemm_variant* v, int device_index, uintptr_t stream_handle, const void* lhs,
+    const void* rhs, const void* lhs_scale, const void* rhs_scale, const int64_t* task_group_ids,
+    const int64_t* task_block_starts, const int64_t* task_actual_starts,
+    const int64_t* task_actual_ends, const int32_t* num_tasks_dev, void* out, int32_t m, int32_t n,
+    int32_t k_packed, int32_t scale_cols, int32_t max_tasks, int32_t groups, int32_t block_rows) {
+  g_last_error.clear();
+  if (num_tasks_dev == nullptr) return fail("num_tasks_dev must be non-null");
+  return launch_ragged_fwd_impl(v, device_index, stream_handle, lhs, rhs, lhs_scale, rhs_scale, task_group_ids,
+                                task_block_starts, task_actual_starts, task_actual_ends, num_tasks_dev, out, m, n,
+                                k_packed, scale_cols, max_tasks, groups, block_rows);
+}
+
+extern "C" int b200_int4_gemms_group_info(int device_index, uintptr_t stream_handle, const int64_t* group_sizes,
+                                          int32_t groups, int32_t tile, int32_t align, int64_t* task_group_ids,
+                                          int64_t* task_block_starts, int64_t* task_actual_starts,
+                                          int64_t* task_actual_ends, int32_t max_tasks, int32_t* num_tasks_dev,
+                                          int32_t* overflow_dev) {
+  g_last_error.clear();
+  if (group_sizes == nullptr || task_group_ids == nullptr || task_block_starts == nullptr ||
+      task_actual_starts == nullptr || task_actual_ends == nullptr || num_tasks_dev == nullptr || overflow_dev == nullptr)
+    return fail("group-info pointers must be non-null");
+  if (groups <= 0 || max_tasks <= 0) return fail("groups and max_tasks must be positive");
+  if (tile <= 0 || align <= 0 || tile % align != 0) return fail("tile must be a positive multiple of align");
+  DeviceState* dev = nullptr;
+  if (int rc = ensure_device(device_index, &dev); rc != 0) return rc;
+  group_info_kernel<<<1, 1024, 0, reinterpret_cast<cudaStream_t>(stream_handle)>>>(
+      reinterpret_cast<const long long*>(group_sizes), groups, tile, align, reinterpret_cast<long long*>(task_group_ids),
+      reinterpret_cast<long long*>(task_block_starts), reinterpret_cast<long long*>(task_actual_starts),
+      reinterpret_cast<long long*>(task_actual_ends), max_tasks, num_tasks_dev, overflow_dev);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda("group-info kernel launch", err);
+  return 0;
+}
+
+extern "C" int b200_int4_gemms_quantize(int device_index, uintptr_t stream_handle, const void* src_bf16, void* dst,
+                                        int64_t rows, int64_t cols, int32_t bits, float scale) {
+  g_last_error.clear();
+  if (src_bf16 == nullptr || dst == nullptr) return fail("src and dst pointers must be non-null");
+  if (rows < 0 || cols < 0) return fail("rows and cols must be non-negative");
+  if (bits != 4 && bits != 8) return fail("bits must be 4 or 8");
+  if (!(scale > 0.f)) return fail("scale must be positive");
+  DeviceState* dev = nullptr;
+  if (int rc = ensure_device(device_index, &dev); rc != 0) return rc;
+  const long long total = rows * ((cols + 7) / 8);
+  if (total == 0) return 0;
+  long long blocks = (total + 255) / 256;
+  const long long cap = static_cast<long long>(dev->sm_count) * 16;
+  if (blocks > cap) blocks = cap;
+  quantize_kernel<<<static_cast<unsigned>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream_handle)>>>(
+      static_cast<const __nv_bfloat16*>(src_bf16), static_cast<uint8_t*>(dst), rows, cols, bits, scale);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda("quantize kernel launch", err);
+  return 0;
+}
+
+extern "C" int b200_int4_gemms_repack_tokens(int device_index, uintptr_t stream_handle, const void* src, void* dst,
+                                             int64_t rows, int64_t cols) {
+  g_last_error.clear();
+  if (src == nullptr || dst == nullptr) return fail("src and dst pointers must be non-null");
+  if (rows < 0 || cols < 0 || cols % 2 != 0) return fail("rows must be non-negative and cols a non-negative even number");
+  DeviceState* dev = nullptr;
+  if (int rc = ensure_device(device_index, &dev); rc != 0) return rc;
+  const long long total = ((rows + 1) / 2) * ((cols + 7) / 8);
+  if (total == 0) return 0;
+  long long blocks = (total + 255) / 256;
+  const long long cap = static_cast<long long>(dev->sm_count) * 16;
+  if (blocks > cap) blocks = cap;
+  repack_tokens_kernel<<<static_cast<unsigned>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream_handle)>>>(
+      static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), rows, cols);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda("token repack kernel launch", err);
+  return 0;
+}
+
+namespace {
+
+// Grouped backward launch.  group_starts == nullptr: operands stacked per group ([G, k_packed, M] /
+// [G, k_packed, N], or [G, M, k_packed] for a K-major lhs).  Otherwise: flat token-packed operands
+// ([k_packed, M] / [k_packed, N] over all tokens) and group_starts[g] = first token of group g.
+int launch_ragged_bwd_impl(const b200_gemm_variant* v, int device_index, uintptr_t stream_handle,
+                           const void* lhs, const void* rhs, const void* lhs_scale, const void* rhs_scale,
+                           const int64_t* group_sizes, const long long* group_starts, void* out, int32_t m,
+                           int32_t n, int32_t k_packed, int32_t scale_cols, int32_t groups) {
+  const bool flat = group_starts != nullptr;
   if (int rc = check_variant(v); rc != 0) return rc;
   if (v->dtype != B200_DTYPE_INT4) return fail("ragged kernels take packed int4 operands");
   if (v->epilogue != B200_EPILOGUE_NONE) return fail("ragged kernels have no fused activation");
@@ -642,7 +740,9 @@ extern "C" int b200_int4_gemms_launch_ragged_bwd(const b200_gemm_variant* v, int
       group_sizes == nullptr || out == nullptr)
     return fail("ragged backward kernel pointers must be non-null");
   if (m <= 0 || n <= 0 || k_packed <= 0 || groups <= 0) return fail("m, n, k_packed and groups must be positive");
-  if (k_packed >= 65536) return fail("int4 path supports k < 131072");
+  // stacked operands: k_packed bounds one group's reduction; flat operands: it is the whole token axis,
+  // and a single group longer than the accumulator headroom is the caller's to avoid
+  if (!flat && k_packed >= 65536) return fail("int4 path supports k < 131072");
   DeviceState* dev = nullptr;
   if (int rc = ensure_device(device_index, &dev); rc != 0) return rc;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_handle);
@@ -651,6 +751,8 @@ extern "C" int b200_int4_gemms_launch_ragged_bwd(const b200_gemm_variant* v, int
   const bool b_t = (v->layout == B200_LAYOUT_NT || v->layout == B200_LAYOUT_TT);
   const int sc_mode = (v->scale_mode == B200_SCALE_SUBCHANNEL) ? SCALE_SC : SCALE_PC;
   const int k = 2 * k_packed;
+  if (flat && (!a_t || b_t)) return fail("flat backward operands are token-major: layout TN");
+  if (flat && sc_mode != SCALE_PC) return fail("flat backward operands support per-channel scales");
   if (sc_mode == SCALE_SC && scale_cols != (k + v->subchannel - 1) / v->subchannel)
     return fail("scale_cols does not match ceil(K / subchannel)");
 
@@ -682,22 +784,25 @@ extern "C" int b200_int4_gemms_launch_ragged_bwd(const b200_gemm_variant* v, int
     sp.a_scale = static_cast<const __nv_bfloat16*>(lhs_scale);
     sp.b_scale = static_cast<const __nv_bfloat16*>(rhs_scale);
     sp.group_sizes = reinterpret_cast<const long long*>(group_sizes);
+    sp.group_starts = group_starts;
     sp.out = out;
     return launch_simt(sp, m, groups, stream);
   }
 
+  const uint64_t k_rows = flat ? static_cast<uint64_t>(k_packed) : static_cast<uint64_t>(groups) * k_packed;
   CUtensorMap ta, tb;
   if (a_t) {
-    if (int rc = make_map_2d(&ta, lhs, m, static_cast<uint64_t>(groups) * k_packed, m, NBLK, BK / 2, 0, "lhs"); rc != 0)
+    if (int rc = make_map_2d(&ta, lhs, m, k_rows, m, NBLK, BK / 2, 0, "lhs"); rc != 0)
       return rc;
   } else {
     if (int rc = make_map_2d(&ta, lhs, k_packed, static_cast<uint64_t>(groups) * m, k_packed, BK / 2, BM, 0, "lhs"); rc != 0)
       return rc;
   }
-  if (int rc = make_map_2d(&tb, rhs, n, static_cast<uint64_t>(groups) * k_packed, n, NBLK, BK / 2, 0, "rhs"); rc != 0)
+  if (int rc = make_map_2d(&tb, rhs, n, k_rows, n, NBLK, BK / 2, 0, "rhs"); rc != 0)
     return rc;
   GemmParams p{};
   p.mode = MODE_RAGGED_BWD;
+  p.group_starts = group_starts;
   p.M = m;
   p.N = n;
   p.K = k;
@@ -725,6 +830,51 @@ extern "C" int b200_int4_gemms_launch_ragged_bwd(const b200_gemm_variant* v, int
   int rc = launch_tc(tl, ta, tb, tc, p, grid, stream);
   if (rc < 0) return fail("internal: no tcgen05 instantiation for this variant");
   return rc;
+}
+
+int launch_group_starts(const int64_t* group_sizes, long long* starts, int groups, cudaStream_t stream) {
+  group_starts_kernel<<<1, 1024, 0, stream>>>(reinterpret_cast<const long long*>(group_sizes), starts, groups);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda("group-start scan launch", err);
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int b200_int4_gemms_launch_ragged_bwd(const b200_gemm_variant* v, int device_index,
+                                                 uintptr_t stream_handle, const void* lhs,
+                                                 const void* rhs, const void* lhs_scale,
+                                                 const void* rhs_scale, const int64_t* group_sizes,
+                                                 void* out, int32_t m, int32_t n, int32_t k_packed,
+                                                 int32_t scale_cols, int32_t groups) {
+  g_last_error.clear();
+  return launch_ragged_bwd_impl(v, device_index, stream_handle, lhs, rhs, lhs_scale, rhs_scale, group_sizes,
+                                nullptr, out, m, n, k_packed, scale_cols, groups);
+}
+
+extern "C" size_t b200_int4_gemms_ragged_bwd_flat_workspace_bytes(int32_t groups) {
+  return groups > 0 ? (static_cast<size_t>(groups) + 1) * sizeof(long long) : 0;
+}
+
+extern "C" int b200_int4_gemms_launch_ragged_bwd_flat(const b200_gemm_variant* v, int device_index,
+                                                      uintptr_t stream_handle, const void* lhs,
+                                                      const void* rhs, const void* lhs_scale,
+                                                      const void* rhs_scale, const int64_t* group_sizes,
+                                                      void* out, void* workspace, size_t workspace_bytes,
+                                                      int32_t m, int32_t n, int64_t tokens, int32_t groups) {
+  g_last_error.clear();
+  if (tokens <= 0 || groups <= 0) return fail("tokens and groups must be positive");
+  if ((tokens + 1) / 2 > 0x7FFFFFFF) return fail("too many tokens for one launch");
+  if (group_sizes == nullptr) return fail("ragged backward kernel pointers must be non-null");
+  if (workspace == nullptr || workspace_bytes < b200_int4_gemms_ragged_bwd_flat_workspace_bytes(groups) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 7u) != 0)
+    return fail("workspace must be 8-byte aligned and hold b200_int4_gemms_ragged_bwd_flat_workspace_bytes(groups) bytes");
+  DeviceState* dev = nullptr;
+  if (int rc = ensure_device(device_index, &dev); rc != 0) return rc;
+  long long* starts = static_cast<long long*>(workspace);
+  if (int rc = launch_group_starts(group_sizes, starts, groups, reinterpret_cast<cudaStream_t>(stream_handle)); rc != 0) return rc;
+  return launch_ragged_bwd_impl(v, device_index, stream_handle, lhs, rhs, lhs_scale, rhs_scale, group_sizes, starts,
+                                out, m, n, static_cast<int32_t>((tokens + 1) / 2), 1, groups);
 }
 
 extern "C" int b200_int4_gemms_unpack_int4(int device_index, uintptr_t stream_handle,

@@ -69,6 +69,11 @@ struct GemmParams {
   const long long* task_actual_starts;
   const long long* task_actual_ends;
   const long long* group_sizes;  // bwd: valid K per group
+  // bwd, flat operands: lhs [ceil(rows/2), M] and rhs [ceil(rows/2), N] hold all tokens back to back,
+  // packed in pairs along the token axis; group g reduces over tokens [group_starts[g], +group_sizes[g]).
+  // nullptr: operands are stacked per group and padded to a common capacity.
+  const long long* group_starts;
+  const int* num_tasks_dev;      // fwd: task count left on the device by the task builder (nullptr: tiles_m)
   const __nv_bfloat16* a_scale;
   const __nv_bfloat16* b_scale;
   void* out;
@@ -82,6 +87,7 @@ struct TileWork {
   int num_kb;        // K blocks to run
   int k_len;         // reduction length of this tile (bwd: group_sizes[g])
   int k_valid;       // number of valid k (masking, bwd); INT_MAX otherwise
+  int k_first;       // first valid k (1 when a flat group starts on the odd token of a byte, else 0)
   int out_row0;      // output row of tile row 0
   int row_lo, row_hi;// valid output rows [lo, hi)
   long long out_off; // element offset added to out (bwd: g*M*N)
@@ -98,6 +104,7 @@ __device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t, int 
   const int rank_rows = k2Cta ? rank * BM : 0;
   TileWork w;
   w.k_valid = 0x7FFFFFFF;
+  w.k_first = 0;
   w.out_off = 0;
   w.out_row_base = 0;
   w.sa_off = 0;
@@ -143,10 +150,20 @@ __device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t, int 
     const int local = t - g * per_g;
     const int mt = local / p.tiles_n;
     const int nt = local - mt * p.tiles_n;
-    const int kg = static_cast<int>(p.group_sizes[g]);
+    int kg = static_cast<int>(p.group_sizes[g]);
     w.a_x = kAMn ? mt * RM + rank_rows : 0;
-    w.a_y = kAMn ? g * p.rows_per_group_a : g * p.rows_per_group_a + mt * RM + rank_rows;
-    w.b_y = g * p.rows_per_group_b;
+    if (p.group_starts != nullptr) {
+      // flat operands (token-major lhs only): the group's first byte row, and one leading nibble to
+      // skip when the group starts on an odd token; an empty group stays empty
+      const long long start = p.group_starts[g];
+      w.k_first = kg > 0 ? static_cast<int>(start & 1) : 0;
+      kg += w.k_first;
+      w.a_y = static_cast<int>(start >> 1);
+      w.b_y = w.a_y;
+    } else {
+      w.a_y = kAMn ? g * p.rows_per_group_a : g * p.rows_per_group_a + mt * RM + rank_rows;
+      w.b_y = g * p.rows_per_group_b;
+    }
     w.n0 = nt * BN;
     w.n1 = w.n0 + NBLK;
     w.k_valid = kg;
@@ -264,6 +281,8 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int cta_rank = k2Cta ? static_cast<int>(cluster_ctarank()) : 0;
   const int tile0 = k2Cta ? static_cast<int>(cluster_id_x()) : static_cast<int>(blockIdx.x);
   const int tile_step = k2Cta ? static_cast<int>(cluster_count_x()) : static_cast<int>(gridDim.x);
+  // grouped forward with tasks built on the device: the task count is read here, not passed by the host
+  const int num_tiles = p.num_tasks_dev != nullptr ? min(*p.num_tasks_dev, p.tiles_m) * p.tiles_n : p.num_tiles;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -320,7 +339,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (lane == 0) {
       int it = 0;
       bool ok = true;
-      for (int t = tile0; t < p.num_tiles && ok; t += tile_step) {
+      for (int t = tile0; t < num_tiles && ok; t += tile_step) {
         const TileWork w = decode_tile<kAMn, k2Cta>(p, t, cta_rank);
         for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
           if constexpr (kInt4) {
@@ -409,7 +428,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // Peer CTA of a pair: no MMAs are issued here.  Forward "my stage s is full" to the leader.
       int it = 0;
       bool ok = true;
-      for (int t = tile0; t < p.num_tiles && ok; t += tile_step) {
+      for (int t = tile0; t < num_tiles && ok; t += tile_step) {
         const TileWork w = decode_tile<kAMn, k2Cta>(p, t, cta_rank);
         for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
           const int s = it % S;
@@ -437,7 +456,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int it = 0;
     int grp = 0;  // accumulator hand-over counter (one per K-group)
     bool ok = true;
-    for (int t = tile0; t < p.num_tiles && ok; t += tile_step) {
+    for (int t = tile0; t < num_tiles && ok; t += tile_step) {
       const TileWork w = decode_tile<kAMn, k2Cta>(p, t, cta_rank);
       const int total_mma = (w.k_len + 31) / 32;  // K=32 steps that hold real data
       if constexpr (kScale == SCALE_PC) {
@@ -552,7 +571,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     //   per-channel, 4 warps: all 256 (SwiGLU: up 0..127 with gate 128..255)
     //   subchannel, 8 warps : plain -> [128*half, +128); SwiGLU -> up [64*half,+64) with gate 128+[64*half,+64)
     constexpr int kOwnCols = (kScale == SCALE_SC) ? 128 : 256;
-    for (int t = tile0; t < p.num_tiles && ok; t += tile_step) {
+    for (int t = tile0; t < num_tiles && ok; t += tile_step) {
       const TileWork w = decode_tile<kAMn, k2Cta>(p, t, cta_rank);
       const int row = w.out_row0 + row_in_tile;
       const bool row_ok = (row >= w.row_lo) && (row < w.row_hi);
@@ -973,7 +992,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t b_dst0 = b_blk * (T::kB8Bytes / 2) + b_p0 * 128 + ((b_cn ^ (b_p0 & 7)) << 4);
       int it = 0;
       bool ok = true;
-      for (int t = tile0; t < p.num_tiles && ok; t += tile_step) {
+      for (int t = tile0; t < num_tiles && ok; t += tile_step) {
         const TileWork w = decode_tile<kAMn, k2Cta>(p, t, cta_rank);
         for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
           const int ps = it % PS;
@@ -1039,7 +1058,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 // one block, same item scheme as an MN-major A: packed row m_p0 + kMRowsPerPass * j
                 if constexpr (kMaskK) {
                   const int k_lo = kb * BK + 2 * (m_p0 + kMRowsPerPass * j);
-                  if (k_lo >= w.k_valid) lo = make_uint4(0, 0, 0, 0);
+                  if (k_lo >= w.k_valid || k_lo < w.k_first) lo = make_uint4(0, 0, 0, 0);
                   if (k_lo + 1 >= w.k_valid) hi = make_uint4(0, 0, 0, 0);
                 }
                 const uint32_t d = m_dst0 + j * ((kMRowsPerPass / 16) * 32 * 128);
@@ -1052,7 +1071,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 const int slot_adv = 32 * (row_adv >> 4) + (row_adv & 15);
                 if constexpr (kMaskK) {
                   const int k_lo = kb * BK + 2 * (b_p0 + row_adv);
-                  if (k_lo >= w.k_valid) lo = make_uint4(0, 0, 0, 0);
+                  if (k_lo >= w.k_valid || k_lo < w.k_first) lo = make_uint4(0, 0, 0, 0);
                   if (k_lo + 1 >= w.k_valid) hi = make_uint4(0, 0, 0, 0);
                 }
                 const uint32_t d = b_dst0 + slot_adv * 128;

@@ -35,6 +35,7 @@ struct SimtParams {
   const long long* task_actual_starts;
   const long long* task_actual_ends;
   const long long* group_sizes;
+  const long long* group_starts;  // bwd, flat token-packed operands (see GemmParams::group_starts); else nullptr
   void* out;
 };
 
@@ -53,6 +54,7 @@ __global__ void gemm_simt_kernel(const SimtParams p) {
 
   int g = 0;
   int k_len = p.K;
+  long long k_base = 0;  // flat backward operands: token index of the group's k = 0
   long long a_group_off = 0, b_group_off = 0, out_off = 0, sa_off = 0, sb_off = 0;
   const int sc = (p.scale_mode == SCALE_SC) ? p.scale_cols : 1;
   if (p.mode == MODE_RAGGED_FWD) {
@@ -68,8 +70,12 @@ __global__ void gemm_simt_kernel(const SimtParams p) {
     g = blockIdx.z;
     if (row >= p.M) return;
     k_len = static_cast<int>(p.group_sizes[g]);
-    a_group_off = static_cast<long long>(g) * p.kb * p.M;
-    b_group_off = static_cast<long long>(g) * p.kb * p.b_cols;
+    if (p.group_starts != nullptr) {
+      k_base = p.group_starts[g];
+    } else {
+      a_group_off = static_cast<long long>(g) * p.kb * p.M;
+      b_group_off = static_cast<long long>(g) * p.kb * p.b_cols;
+    }
     out_off = static_cast<long long>(g) * p.M * p.N;
     sa_off = static_cast<long long>(g) * p.M * sc;
     sb_off = static_cast<long long>(g) * sc * p.b_cols;
@@ -90,17 +96,17 @@ __global__ void gemm_simt_kernel(const SimtParams p) {
     acc_up = 0;
     acc_gate = 0;
     for (int k = k0; k < k1; ++k) {
-      const int kbyte = p.int4 ? (k >> 1) : k;
-      const long long ai = p.a_transposed ? (static_cast<long long>(kbyte) * p.M + row)
-                                          : (static_cast<long long>(row) * p.kb + kbyte);
-      const int av = load_q(a, ai, k, p.int4);
-      const long long bi = p.b_transposed ? (static_cast<long long>(col) * p.kb + kbyte)
-                                          : (static_cast<long long>(kbyte) * p.b_cols + col);
-      acc_up += av * load_q(b, bi, k, p.int4);
+      const long long kk = k_base + k;  // position along the stored K axis (differs from k for flat operands)
+      const long long kbyte = p.int4 ? (kk >> 1) : kk;
+      const int knib = static_cast<int>(kk & 1);
+      const long long ai = p.a_transposed ? (kbyte * p.M + row) : (static_cast<long long>(row) * p.kb + kbyte);
+      const int av = load_q(a, ai, knib, p.int4);
+      const long long bi = p.b_transposed ? (static_cast<long long>(col) * p.kb + kbyte) : (kbyte * p.b_cols + col);
+      acc_up += av * load_q(b, bi, knib, p.int4);
       if (swiglu) {
         const long long bg = p.b_transposed ? (static_cast<long long>(col + p.N) * p.kb + kbyte)
-                                            : (static_cast<long long>(kbyte) * p.b_cols + col + p.N);
-        acc_gate += av * load_q(b, bg, k, p.int4);
+                                            : (kbyte * p.b_cols + col + p.N);
+        acc_gate += av * load_q(b, bg, knib, p.int4);
       }
     }
     if (p.out_dtype == OUT_S32) break;

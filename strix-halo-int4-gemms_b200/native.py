@@ -45,6 +45,12 @@ EXPORTED_SYMBOLS = (
     "b200_int4_gemms_launch_ragged_fwd",
     "b200_int4_gemms_launch_ragged_bwd",
     "b200_int4_gemms_unpack_int4",
+    "b200_int4_gemms_group_info",
+    "b200_int4_gemms_launch_ragged_fwd_device_tasks",
+    "b200_int4_gemms_ragged_bwd_flat_workspace_bytes",
+    "b200_int4_gemms_launch_ragged_bwd_flat",
+    "b200_int4_gemms_quantize",
+    "b200_int4_gemms_repack_tokens",
 )
 
 
@@ -118,6 +124,18 @@ def _declare(library: ctypes.CDLL) -> None:
     library.b200_int4_gemms_launch_ragged_bwd.argtypes = [variant_p, ctypes.c_int, size_t] + [void_p] * 6 + [i32] * 5
     library.b200_int4_gemms_unpack_int4.restype = ctypes.c_int
     library.b200_int4_gemms_unpack_int4.argtypes = [ctypes.c_int, size_t, void_p, void_p, i64, i64]
+    library.b200_int4_gemms_group_info.restype = ctypes.c_int
+    library.b200_int4_gemms_group_info.argtypes = [ctypes.c_int, size_t, void_p, i32, i32, i32] + [void_p] * 4 + [i32, void_p, void_p]
+    library.b200_int4_gemms_launch_ragged_fwd_device_tasks.restype = ctypes.c_int
+    library.b200_int4_gemms_launch_ragged_fwd_device_tasks.argtypes = [variant_p, ctypes.c_int, size_t] + [void_p] * 10 + [i32] * 7
+    library.b200_int4_gemms_ragged_bwd_flat_workspace_bytes.restype = size_t
+    library.b200_int4_gemms_ragged_bwd_flat_workspace_bytes.argtypes = [i32]
+    library.b200_int4_gemms_launch_ragged_bwd_flat.restype = ctypes.c_int
+    library.b200_int4_gemms_launch_ragged_bwd_flat.argtypes = [variant_p, ctypes.c_int, size_t] + [void_p] * 7 + [size_t, i32, i32, i64, i32]
+    library.b200_int4_gemms_quantize.restype = ctypes.c_int
+    library.b200_int4_gemms_quantize.argtypes = [ctypes.c_int, size_t, void_p, void_p, i64, i64, i32, ctypes.c_float]
+    library.b200_int4_gemms_repack_tokens.restype = ctypes.c_int
+    library.b200_int4_gemms_repack_tokens.argtypes = [ctypes.c_int, size_t, void_p, void_p, i64, i64]
 
 
 def load_dispatch_library(path: str | Path | None = None) -> ctypes.CDLL:
@@ -477,16 +495,25 @@ def launch_ragged_fwd_kernel(
         out_dtype=OUT_F32 if out.dtype is torch.float32 else OUT_BF16, path=path,
     )
     groups = int(rhs.shape[0])
-    rc = library.b200_int4_gemms_launch_ragged_fwd(
-        ctypes.byref(record), _device_index(lhs), _stream_handle(torch, lhs, stream),
-        ctypes.c_void_p(lhs.data_ptr()), ctypes.c_void_p(rhs.data_ptr()),
-        ctypes.c_void_p(a_scale.data_ptr()), ctypes.c_void_p(b_scale.data_ptr()),
+    task_arrays = (
         ctypes.c_void_p(group_info.group_id.data_ptr()), ctypes.c_void_p(group_info.block_start.data_ptr()),
         ctypes.c_void_p(group_info.actual_start.data_ptr()), ctypes.c_void_p(group_info.actual_end.data_ptr()),
-        ctypes.c_void_p(out.data_ptr()),
-        int(rows), int(cols), int(k_packed), int(scale_cols), int(group_info.num_tasks), groups,
-        int(config.block_m),
     )
+    operands = (
+        ctypes.c_void_p(lhs.data_ptr()), ctypes.c_void_p(rhs.data_ptr()),
+        ctypes.c_void_p(a_scale.data_ptr()), ctypes.c_void_p(b_scale.data_ptr()),
+    )
+    sizes = (int(rows), int(cols), int(k_packed), int(scale_cols), int(group_info.num_tasks), groups, int(config.block_m))
+    device_count = getattr(group_info, "device_num_tasks", None)
+    if device_count is not None:
+        # tasks built on the device: num_tasks is the capacity of the arrays, the real count stays on the GPU
+        rc = library.b200_int4_gemms_launch_ragged_fwd_device_tasks(
+            ctypes.byref(record), _device_index(lhs), _stream_handle(torch, lhs, stream), *operands, *task_arrays,
+            ctypes.c_void_p(device_count.data_ptr()), ctypes.c_void_p(out.data_ptr()), *sizes)
+    else:
+        rc = library.b200_int4_gemms_launch_ragged_fwd(
+            ctypes.byref(record), _device_index(lhs), _stream_handle(torch, lhs, stream), *operands, *task_arrays,
+            ctypes.c_void_p(out.data_ptr()), *sizes)
     if rc != 0:
         raise RuntimeError(_library_last_error(library))
     return out
@@ -556,6 +583,113 @@ def unpack_int4_on_device(packed: Any, *, library_path: str | Path | None = None
         _device_index(packed), _stream_handle(torch, packed, stream),
         ctypes.c_void_p(packed.data_ptr()), ctypes.c_void_p(out.data_ptr()), rows, int(packed.shape[-1]),
     )
+    if rc != 0:
+        raise RuntimeError(_library_last_error(library))
+    return out
+
+
+# device scratch kept per (device, stream, purpose); a buffer that was outgrown stays alive because a
+# kernel launched earlier may still be using it
+_WORKSPACES: dict[tuple[int, int, str], Any] = {}
+_RETIRED_WORKSPACES: list[Any] = []
+_WORKSPACES_LOCK = threading.Lock()
+
+
+def group_info_on_device(
+    group_sizes: Any, tile: int, *, align_tile: int = 8, max_tasks: int,
+    library_path: str | Path | None = None, stream: Any | None = None,
+) -> tuple[Any, Any, Any, Any, Any, Any]:
+    """Task arrays of the grouped forward pass built by ``b200_int4_gemms_group_info``.
+
+    Returns ``(group_id, block_start, actual_start, actual_end, num_tasks, overflow)``: four int64
+    tensors of ``max_tasks`` entries and two int32 one-element tensors, all on the device of
+    ``group_sizes``.  Nothing is copied to the host.
+    """
+    torch = _torch()
+    if not getattr(group_sizes, "is_cuda", False):
+        raise RuntimeError("group_info_on_device requires a CUDA group_sizes tensor")
+    library = load_dispatch_library(library_path)
+    sizes = group_sizes.to(torch.int64).contiguous()
+    arrays = [torch.empty(int(max_tasks), device=sizes.device, dtype=torch.int64) for _ in range(4)]
+    counters = torch.empty(2, device=sizes.device, dtype=torch.int32)
+    rc = library.b200_int4_gemms_group_info(
+        _device_index(sizes), _stream_handle(torch, sizes, stream), ctypes.c_void_p(sizes.data_ptr()),
+        int(sizes.numel()), int(tile), int(align_tile), *[ctypes.c_void_p(t.data_ptr()) for t in arrays],
+        int(max_tasks), ctypes.c_void_p(counters[0:1].data_ptr()), ctypes.c_void_p(counters[1:2].data_ptr()))
+    if rc != 0:
+        raise RuntimeError(_library_last_error(library))
+    return arrays[0], arrays[1], arrays[2], arrays[3], counters[0:1], counters[1:2]
+
+
+def launch_ragged_bwd_flat_kernel(
+    lhs: Any, rhs: Any, group_sizes: Any, *, a_scale: Any, b_scale: Any, out: Any, tokens: int,
+    library_path: str | Path | None = None, stream: Any | None = None, path: int = PATH_AUTO,
+) -> Any:
+    """Grouped backward launch over flat token-packed operands (``b200_int4_gemms_launch_ragged_bwd_flat``)."""
+    torch = _torch()
+    if not torch.cuda.is_available() or not getattr(lhs, "is_cuda", False):
+        raise RuntimeError("native ragged kernels require CUDA tensors")
+    a_scale = _require_bfloat16_scale(torch, "a_scale", _require_contiguous("a_scale", a_scale))
+    b_scale = _require_bfloat16_scale(torch, "b_scale", _require_contiguous("b_scale", b_scale))
+    library = load_dispatch_library(library_path)
+    record = make_variant(dtype=OperandDType.INT4, layout=GemmLayout.TN, scale=ScaleSpec(ScaleMode.PER_CHANNEL),
+                          epilogue=Epilogue.NONE, out_dtype=OUT_F32, path=path)
+    groups = int(group_sizes.numel())
+    device_index, stream_handle = _device_index(lhs), _stream_handle(torch, lhs, stream)
+    need = int(library.b200_int4_gemms_ragged_bwd_flat_workspace_bytes(groups))
+    key = (device_index, stream_handle, "bwd_flat")
+    with _WORKSPACES_LOCK:  # one scratch buffer per (device, stream): calls that share one must not overlap
+        scratch = _WORKSPACES.get(key)
+        if scratch is None or scratch.numel() < need:
+            if scratch is not None:
+                _RETIRED_WORKSPACES.append(scratch)
+            scratch = torch.empty(max(need, 4096), dtype=torch.uint8, device=lhs.device)
+            _WORKSPACES[key] = scratch
+    sizes = group_sizes.to(torch.int64).contiguous()
+    rc = library.b200_int4_gemms_launch_ragged_bwd_flat(
+        ctypes.byref(record), device_index, stream_handle,
+        ctypes.c_void_p(lhs.data_ptr()), ctypes.c_void_p(rhs.data_ptr()),
+        ctypes.c_void_p(a_scale.data_ptr()), ctypes.c_void_p(b_scale.data_ptr()),
+        ctypes.c_void_p(sizes.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+        ctypes.c_void_p(scratch.data_ptr()), int(scratch.numel()),
+        int(lhs.shape[1]), int(rhs.shape[1]), int(tokens), groups)
+    if rc != 0:
+        raise RuntimeError(_library_last_error(library))
+    return out
+
+
+def quantize_on_device(x: Any, *, bits: int, scale: float, library_path: str | Path | None = None,
+                       stream: Any | None = None) -> Any:
+    """bf16 ``[..., cols]`` -> packed int4 ``[..., ceil(cols/2)]`` uint8 (bits=4) or int8 codes (bits=8)."""
+    torch = _torch()
+    if not getattr(x, "is_cuda", False) or x.dtype is not torch.bfloat16:
+        raise RuntimeError("quantize_on_device requires a CUDA bfloat16 tensor")
+    x = _require_contiguous("x", x)
+    cols = int(x.shape[-1])
+    rows = int(x.numel() // cols) if cols else 0
+    if bits == 4:
+        out = torch.empty((*x.shape[:-1], (cols + 1) // 2), device=x.device, dtype=torch.uint8)
+    else:
+        out = torch.empty(x.shape, device=x.device, dtype=torch.int8)
+    library = load_dispatch_library(library_path)
+    rc = library.b200_int4_gemms_quantize(_device_index(x), _stream_handle(torch, x, stream), ctypes.c_void_p(x.data_ptr()),
+                                          ctypes.c_void_p(out.data_ptr()), rows, cols, int(bits), float(scale))
+    if rc != 0:
+        raise RuntimeError(_library_last_error(library))
+    return out
+
+
+def repack_tokens_on_device(packed: Any, *, library_path: str | Path | None = None, stream: Any | None = None) -> Any:
+    """int4 packed along features ``[rows, cols/2]`` -> packed along tokens ``[ceil(rows/2), cols]``."""
+    torch = _torch()
+    if not getattr(packed, "is_cuda", False) or packed.dtype is not torch.uint8 or packed.ndim != 2:
+        raise RuntimeError("repack_tokens_on_device requires a 2-D CUDA uint8 tensor")
+    packed = _require_contiguous("packed", packed)
+    rows, cols = int(packed.shape[0]), 2 * int(packed.shape[1])
+    out = torch.empty(((rows + 1) // 2, cols), device=packed.device, dtype=torch.uint8)
+    library = load_dispatch_library(library_path)
+    rc = library.b200_int4_gemms_repack_tokens(_device_index(packed), _stream_handle(torch, packed, stream),
+                                               ctypes.c_void_p(packed.data_ptr()), ctypes.c_void_p(out.data_ptr()), rows, cols)
     if rc != 0:
         raise RuntimeError(_library_last_error(library))
     return out

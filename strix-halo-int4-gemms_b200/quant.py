@@ -78,3 +78,35 @@ def apply_scales(result: Any, a_scale: Any | None, b_scale: Any | None) -> Any:
     if b_scale is not None:
         result = result * b_scale[..., None, :]
     return result
+
+
+def quantize_int_cuda(x: Any, *, bits: int, scale: float) -> Any:
+    """``fake_quant_int`` (+ ``pack_int4_k_major`` for ``bits=4``) as one CUDA kernel of the native library.
+
+    ``x``: CUDA bfloat16 ``[..., K]``.  Returns packed uint8 ``[..., ceil(K/2)]`` for ``bits=4`` and int8
+    codes ``[..., K]`` for ``bits=8``, bit-identical to the host helpers above.
+    """
+    if bits not in (4, 8):
+        raise ValueError("bits must be 4 or 8")
+    if isinstance(scale, bool) or not isinstance(scale, (int, float)):
+        raise TypeError("scale must be a positive Python int or float scalar")
+    if scale <= 0:
+        raise ValueError("scale must be positive")
+    from .native import quantize_on_device
+
+    return quantize_on_device(x, bits=bits, scale=float(scale))
+
+
+def repack_int4_tokens(x_packed: Any) -> Any:
+    """Packed int4 ``[T, F/2]`` (pairs of features per byte) -> ``[ceil(T/2), F]`` (pairs of tokens per byte).
+
+    The operand format of ``ragged_dot_int4_bwd_flat``; CUDA tensors go through the native kernel,
+    host tensors through the equivalent torch expression.
+    """
+    torch = _torch()
+    if getattr(x_packed, "is_cuda", False):
+        from .native import repack_tokens_on_device
+
+        return repack_tokens_on_device(x_packed)
+    codes = unpack_int4_k_major(x_packed)          # [T, F]
+    return pack_int4_k_major(codes.t().contiguous()).t().contiguous()  # pack along tokens, back to [T/2, F]

@@ -105,6 +105,10 @@ class RaggedGroupInfo:
     start_within_block: Any
     actual_size: Any
     num_tasks: int
+    # set by calculate_group_info_on_device: the task count as a one-element int32 device tensor
+    # (``num_tasks`` is then the capacity of the arrays) and a flag that is 1 when the capacity was too small
+    device_num_tasks: Any | None = None
+    device_overflow: Any | None = None
 
 
 def _torch() -> Any:
@@ -641,3 +645,91 @@ def ragged_dot_int4_bwd(
         root=native_root,
         library_path=native_library_path,
     )
+
+
+def calculate_group_info_on_device(
+    group_sizes: Any,
+    tile: int,
+    *,
+    total_rows: int,
+    align_tile: int = 8,
+    max_tasks: int | None = None,
+) -> RaggedGroupInfo:
+    """``calculate_group_info`` without a host round trip (CUDA kernel of the native library).
+
+    The reference reads the task count back to the host to size its launch (ragged.py:275); here the
+    arrays are sized by an upper bound (``total_rows // tile + 2 * groups`` tasks always fit) and the
+    count stays on the GPU in ``device_num_tasks``; the forward kernel reads it there.  Entries past
+    the count are empty tasks.  ``total_rows`` must be the sum of ``group_sizes`` (it only sizes the
+    arrays; nothing checks it).  Same task arrays, element for element, as ``calculate_group_info``.
+    """
+    torch = _torch()
+    if tile <= 0:
+        raise ValueError("tile must be positive")
+    if align_tile <= 0:
+        raise ValueError("align_tile must be positive")
+    if tile % align_tile:
+        raise ValueError("tile must be a multiple of align_tile")
+    if group_sizes.ndim != 1:
+        raise ValueError("group_sizes must be a 1-D tensor")
+    groups = int(group_sizes.numel())
+    if groups == 0:
+        raise ValueError("group_sizes must not be empty")
+    capacity = int(max_tasks) if max_tasks is not None else int(total_rows) // tile + 2 * groups
+    from .native import group_info_on_device
+
+    gid, bstart, astart, aend, count, overflow = group_info_on_device(
+        group_sizes, tile, align_tile=align_tile, max_tasks=max(capacity, 1))
+    return RaggedGroupInfo(
+        group_id=gid, block_start=bstart, actual_start=astart, actual_end=aend,
+        start_within_block=astart - bstart, actual_size=aend - astart, num_tasks=max(capacity, 1),
+        device_num_tasks=count, device_overflow=overflow,
+    )
+
+
+def ragged_dot_int4_bwd_flat(
+    lhs: Any,
+    rhs: Any,
+    group_sizes: Any,
+    *,
+    a_scale: Any,
+    b_scale: Any,
+    out: Any | None = None,
+    native_library_path: str | None = None,
+) -> Any:
+    """Backward grouped int4 dot over flat token-packed operands (not in the reference).
+
+    ``out[g] = (lhs[tokens of g]^T @ rhs[tokens of g]) * a_scale[g][:, None] * b_scale[g][None, :]``.
+    ``lhs [ceil(T/2), M]`` and ``rhs [ceil(T/2), N]`` hold the ``T`` tokens back to back, two per byte along
+    the token axis (``repack_int4_tokens`` builds this form from the forward operand format), so
+    there is no per-group padding to a common capacity as ``ragged_dot_int4_bwd`` needs.  Groups may
+    start on odd tokens.  Per-channel scales ``a_scale [G, M]``, ``b_scale [G, N]`` (bf16); output
+    ``[G, M, N]`` float32.  ``group_sizes`` must sum to the number of real tokens (``2 * lhs.shape[0]``, or one less when the
+    last byte row holds a single token); it is not read on the host.
+    """
+    torch = _torch()
+    _require_cuda_tensor(torch, "lhs", lhs)
+    _require_cuda_tensor(torch, "rhs", rhs)
+    if lhs.dtype != torch.uint8 or rhs.dtype != torch.uint8:
+        raise ValueError("lhs and rhs must be packed int4 torch.uint8")
+    if lhs.ndim != 2 or rhs.ndim != 2 or lhs.shape[0] != rhs.shape[0]:
+        raise ValueError(f"lhs and rhs must have shapes (T/2, M) and (T/2, N); got {tuple(lhs.shape)} and {tuple(rhs.shape)}")
+    if not lhs.is_contiguous() or not rhs.is_contiguous():
+        raise ValueError("lhs and rhs must be contiguous")
+    if group_sizes.ndim != 1 or group_sizes.numel() == 0:
+        raise ValueError("group_sizes must be a non-empty 1-D tensor")
+    _require_cuda_tensor(torch, "a_scale", a_scale)
+    _require_cuda_tensor(torch, "b_scale", b_scale)
+    groups, m, n = int(group_sizes.numel()), int(lhs.shape[1]), int(rhs.shape[1])
+    if tuple(a_scale.shape) != (groups, m) or tuple(b_scale.shape) != (groups, n):
+        raise ValueError(f"a_scale must have shape ({groups}, {m}) and b_scale ({groups}, {n})")
+    if group_sizes.device != lhs.device:
+        group_sizes = group_sizes.to(device=lhs.device)
+    if out is None:
+        out = torch.empty((groups, m, n), device=lhs.device, dtype=torch.float32)
+    elif tuple(out.shape) != (groups, m, n) or out.dtype != torch.float32 or not out.is_contiguous():
+        raise ValueError(f"out must be a contiguous float32 tensor of shape ({groups}, {m}, {n})")
+    from .native import launch_ragged_bwd_flat_kernel
+
+    return launch_ragged_bwd_flat_kernel(lhs, rhs, group_sizes, a_scale=a_scale, b_scale=b_scale, out=out,
+                                         tokens=2 * int(lhs.shape[0]), library_path=native_library_path)
