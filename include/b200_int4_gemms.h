@@ -208,6 +208,30 @@ int b200_int4_gemms_launch_ragged_bwd_flat(const b200_gemm_variant* variant, int
                                            size_t workspace_bytes, int32_t m, int32_t n, int64_t tokens,
                                            int32_t groups);
 
+/* b200_int4_gemms_launch_ragged_bwd_flat for callers that can neither hand over device scratch nor
+ * let the library allocate: code running inside someone else's memory plan (a framework whose pool
+ * is fully reserved, a plugin that is told not to touch the allocator because allocation would
+ * synchronise the device or move what the host application has placed).  No reference counterpart.
+ * Same arguments minus the workspace.  The group starts go to an array that is part of the library
+ * image (B200_STATIC_SCRATCH_MAX_GROUPS + 1 int64 entries, 32 KB + 8 bytes per device); nothing is
+ * allocated on any call, the first included.
+ *   - more than B200_STATIC_SCRATCH_MAX_GROUPS groups: refused (rc 1, message names the limit);
+ *   - the first call on a device also looks the array's address up and sets the GEMM kernel's
+ *     shared-memory attribute: make one call before starting a stream capture, since that set-up
+ *     is host-side work that does not belong inside one;
+ *   - the array is shared by all calls on a device and keeps what the last call wrote.  Each call
+ *     rewrites the entries it reads, so nothing needs clearing, but two calls that can overlap in
+ *     time (two streams, two threads) race on it: serialise them, or use the workspace form;
+ *   - a bounded device wait that runs out is reported through b200_int4_gemms_device_status only
+ *     when another entry point has already set the device up (that set-up owns the status word). */
+#define B200_STATIC_SCRATCH_MAX_GROUPS 4096
+int b200_int4_gemms_launch_ragged_bwd_flat_static(const b200_gemm_variant* variant, int device_index,
+                                                  uintptr_t stream_handle, const void* lhs,
+                                                  const void* rhs, const void* lhs_scale,
+                                                  const void* rhs_scale, const int64_t* group_sizes,
+                                                  void* out, int32_t m, int32_t n, int64_t tokens,
+                                                  int32_t groups);
+
 /* bf16 [rows, cols] -> quantisation codes clamp(round_half_even(float(x) / scale), qmin, qmax):
  * bits = 4: packed two per byte along the last axis (even index in the low nibble, an odd cols pads
  * with a zero code), dst u8 [rows, ceil(cols/2)]; bits = 8: dst int8 [rows, cols].

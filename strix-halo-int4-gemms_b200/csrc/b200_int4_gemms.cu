@@ -730,7 +730,8 @@ namespace {
 int launch_ragged_bwd_impl(const b200_gemm_variant* v, int device_index, uintptr_t stream_handle,
                            const void* lhs, const void* rhs, const void* lhs_scale, const void* rhs_scale,
                            const int64_t* group_sizes, const long long* group_starts, void* out, int32_t m,
-                           int32_t n, int32_t k_packed, int32_t scale_cols, int32_t groups) {
+                           int32_t n, int32_t k_packed, int32_t scale_cols, int32_t groups,
+                           DeviceState* prepared = nullptr) {
   const bool flat = group_starts != nullptr;
   if (int rc = check_variant(v); rc != 0) return rc;
   if (v->dtype != B200_DTYPE_INT4) return fail("ragged kernels take packed int4 operands");
@@ -743,8 +744,10 @@ int launch_ragged_bwd_impl(const b200_gemm_variant* v, int device_index, uintptr
   // stacked operands: k_packed bounds one group's reduction; flat operands: it is the whole token axis,
   // and a single group longer than the accumulator headroom is the caller's to avoid
   if (!flat && k_packed >= 65536) return fail("int4 path supports k < 131072");
-  DeviceState* dev = nullptr;
-  if (int rc = ensure_device(device_index, &dev); rc != 0) return rc;
+  DeviceState* dev = prepared;  // a caller that has done its own device set-up passes it in
+  if (dev == nullptr) {
+    if (int rc = ensure_device(device_index, &dev); rc != 0) return rc;
+  }
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_handle);
 
   const bool a_t = (v->layout == B200_LAYOUT_TN || v->layout == B200_LAYOUT_TT);
@@ -875,6 +878,86 @@ extern "C" int b200_int4_gemms_launch_ragged_bwd_flat(const b200_gemm_variant* v
   if (int rc = launch_group_starts(group_sizes, starts, groups, reinterpret_cast<cudaStream_t>(stream_handle)); rc != 0) return rc;
   return launch_ragged_bwd_impl(v, device_index, stream_handle, lhs, rhs, lhs_scale, rhs_scale, group_sizes, starts,
                                 out, m, n, static_cast<int32_t>((tokens + 1) / 2), 1, groups);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Flat grouped backward without a caller-provided workspace and without any allocation.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+// The group-start scan's scratch, for callers that cannot bring device memory of their own.  One
+// array per loaded library image and device, shared by every call of the entry point below: calls
+// that may run at the same time (different streams, different host threads) would overwrite each
+// other's group starts.  Every call rewrites entries [0, groups] before its GEMM kernel reads them,
+// so nothing in it has to be zero and stale contents of an earlier call do no harm.
+static __device__ __align__(256) long long g_static_group_starts[B200_STATIC_SCRATCH_MAX_GROUPS + 1];
+
+struct StaticScratchState {
+  bool ready = false;
+  DeviceState view;             // SM count for the grid; status word borrowed when the device has one
+  long long* starts = nullptr;  // device address of g_static_group_starts on this device
+};
+StaticScratchState g_static_devices[kMaxDevices];
+std::mutex g_static_mutex;
+
+// First call per device: look the array's address up and give the one tensor-core kernel this entry
+// point launches its shared-memory size.  No allocation: unlike ensure_device, no status word is made.
+int ensure_static_scratch(int device_index, StaticScratchState** out) {
+  if (device_index < 0 || device_index >= kMaxDevices) return fail("device_index out of range");
+  cudaError_t err = cudaSetDevice(device_index);
+  if (err != cudaSuccess) return fail_cuda("cudaSetDevice", err);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  StaticScratchState& st = g_static_devices[device_index];
+  if (!st.ready) {
+    int major = 0, sms = 0;
+    err = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device_index);
+    if (err != cudaSuccess) return fail_cuda("cudaDeviceGetAttribute(compute capability)", err);
+    if (major != 10) return fail("this library holds sm_100a kernels only");
+    err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device_index);
+    if (err != cudaSuccess) return fail_cuda("cudaDeviceGetAttribute(SM count)", err);
+    void* address = nullptr;
+    err = cudaGetSymbolAddress(&address, g_static_group_starts);
+    if (err != cudaSuccess) return fail_cuda("cudaGetSymbolAddress(static group-start scratch)", err);
+    if (address == nullptr) return fail("static group-start scratch has no device address");
+    using Kernel = KernelTraits<true, true, true, SCALE_PC, EPI_NONE, OUT_F32, true, false>;
+    err = set_smem(gemm_i8_tcgen05_kernel<true, true, true, SCALE_PC, EPI_NONE, OUT_F32, true, false>, Kernel::kSmemBytes);
+    if (err != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(max dynamic shared memory)", err);
+    st.view.sm_count = sms;
+    st.view.cc_major = major;
+    st.view.max_pair_clusters = 0;  // this entry point never launches a CTA-pair kernel
+    st.starts = static_cast<long long*>(address);
+    st.ready = true;
+  }
+  // time-outs of bounded device waits are recorded only if another entry point has given the device a status word
+  {
+    std::lock_guard<std::mutex> dev_lock(g_device_mutex);
+    st.view.status_dev = g_devices[device_index].ready ? g_devices[device_index].status_dev : nullptr;
+  }
+  *out = &st;
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int b200_int4_gemms_launch_ragged_bwd_flat_static(const b200_gemm_variant* v, int device_index,
+                                                             uintptr_t stream_handle, const void* lhs,
+                                                             const void* rhs, const void* lhs_scale,
+                                                             const void* rhs_scale, const int64_t* group_sizes,
+                                                             void* out, int32_t m, int32_t n, int64_t tokens,
+                                                             int32_t groups) {
+  g_last_error.clear();
+  if (tokens <= 0 || groups <= 0) return fail("tokens and groups must be positive");
+  if (groups > B200_STATIC_SCRATCH_MAX_GROUPS)
+    return fail("the built-in scratch holds the starts of at most " + std::to_string(B200_STATIC_SCRATCH_MAX_GROUPS) +
+                " groups; got " + std::to_string(groups) +
+                " (use b200_int4_gemms_launch_ragged_bwd_flat with a workspace of your own)");
+  if ((tokens + 1) / 2 > 0x7FFFFFFF) return fail("too many tokens for one launch");
+  if (group_sizes == nullptr) return fail("ragged backward kernel pointers must be non-null");
+  StaticScratchState* st = nullptr;
+  if (int rc = ensure_static_scratch(device_index, &st); rc != 0) return rc;
+  if (int rc = launch_group_starts(group_sizes, st->starts, groups, reinterpret_cast<cudaStream_t>(stream_handle)); rc != 0) return rc;
+  return launch_ragged_bwd_impl(v, device_index, stream_handle, lhs, rhs, lhs_scale, rhs_scale, group_sizes, st->starts,
+                                out, m, n, static_cast<int32_t>((tokens + 1) / 2), 1, groups, &st->view);
 }
 
 extern "C" int b200_int4_gemms_unpack_int4(int device_index, uintptr_t stream_handle,

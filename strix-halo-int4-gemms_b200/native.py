@@ -49,6 +49,7 @@ EXPORTED_SYMBOLS = (
     "b200_int4_gemms_launch_ragged_fwd_device_tasks",
     "b200_int4_gemms_ragged_bwd_flat_workspace_bytes",
     "b200_int4_gemms_launch_ragged_bwd_flat",
+    "b200_int4_gemms_launch_ragged_bwd_flat_static",
     "b200_int4_gemms_quantize",
     "b200_int4_gemms_repack_tokens",
 )
@@ -132,6 +133,8 @@ def _declare(library: ctypes.CDLL) -> None:
     library.b200_int4_gemms_ragged_bwd_flat_workspace_bytes.argtypes = [i32]
     library.b200_int4_gemms_launch_ragged_bwd_flat.restype = ctypes.c_int
     library.b200_int4_gemms_launch_ragged_bwd_flat.argtypes = [variant_p, ctypes.c_int, size_t] + [void_p] * 7 + [size_t, i32, i32, i64, i32]
+    library.b200_int4_gemms_launch_ragged_bwd_flat_static.restype = ctypes.c_int
+    library.b200_int4_gemms_launch_ragged_bwd_flat_static.argtypes = [variant_p, ctypes.c_int, size_t] + [void_p] * 6 + [i32, i32, i64, i32]
     library.b200_int4_gemms_quantize.restype = ctypes.c_int
     library.b200_int4_gemms_quantize.argtypes = [ctypes.c_int, size_t, void_p, void_p, i64, i64, i32, ctypes.c_float]
     library.b200_int4_gemms_repack_tokens.restype = ctypes.c_int
@@ -621,11 +624,19 @@ def group_info_on_device(
     return arrays[0], arrays[1], arrays[2], arrays[3], counters[0:1], counters[1:2]
 
 
+STATIC_SCRATCH_MAX_GROUPS = 4096  # B200_STATIC_SCRATCH_MAX_GROUPS of the header
+
+
 def launch_ragged_bwd_flat_kernel(
     lhs: Any, rhs: Any, group_sizes: Any, *, a_scale: Any, b_scale: Any, out: Any, tokens: int,
     library_path: str | Path | None = None, stream: Any | None = None, path: int = PATH_AUTO,
+    static_scratch: bool = False,
 ) -> Any:
-    """Grouped backward launch over flat token-packed operands (``b200_int4_gemms_launch_ragged_bwd_flat``)."""
+    """Grouped backward launch over flat token-packed operands (``b200_int4_gemms_launch_ragged_bwd_flat``).
+
+    ``static_scratch=True`` goes through ``b200_int4_gemms_launch_ragged_bwd_flat_static``: no workspace
+    tensor is made here and the library allocates nothing; ``group_sizes`` must already be a contiguous
+    int64 CUDA tensor (converting it would allocate)."""
     torch = _torch()
     if not torch.cuda.is_available() or not getattr(lhs, "is_cuda", False):
         raise RuntimeError("native ragged kernels require CUDA tensors")
@@ -636,6 +647,18 @@ def launch_ragged_bwd_flat_kernel(
                           epilogue=Epilogue.NONE, out_dtype=OUT_F32, path=path)
     groups = int(group_sizes.numel())
     device_index, stream_handle = _device_index(lhs), _stream_handle(torch, lhs, stream)
+    if static_scratch:
+        if group_sizes.dtype is not torch.int64 or not group_sizes.is_contiguous() or not group_sizes.is_cuda:
+            raise ValueError("static_scratch=True requires group_sizes as a contiguous int64 CUDA tensor")
+        rc = library.b200_int4_gemms_launch_ragged_bwd_flat_static(
+            ctypes.byref(record), device_index, stream_handle,
+            ctypes.c_void_p(lhs.data_ptr()), ctypes.c_void_p(rhs.data_ptr()),
+            ctypes.c_void_p(a_scale.data_ptr()), ctypes.c_void_p(b_scale.data_ptr()),
+            ctypes.c_void_p(group_sizes.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+            int(lhs.shape[1]), int(rhs.shape[1]), int(tokens), groups)
+        if rc != 0:
+            raise RuntimeError(_library_last_error(library))
+        return out
     need = int(library.b200_int4_gemms_ragged_bwd_flat_workspace_bytes(groups))
     key = (device_index, stream_handle, "bwd_flat")
     with _WORKSPACES_LOCK:  # one scratch buffer per (device, stream): calls that share one must not overlap

@@ -696,6 +696,7 @@ def ragged_dot_int4_bwd_flat(
     b_scale: Any,
     out: Any | None = None,
     native_library_path: str | None = None,
+    static_scratch: bool = False,
 ) -> Any:
     """Backward grouped int4 dot over flat token-packed operands (not in the reference).
 
@@ -706,6 +707,10 @@ def ragged_dot_int4_bwd_flat(
     start on odd tokens.  Per-channel scales ``a_scale [G, M]``, ``b_scale [G, N]`` (bf16); output
     ``[G, M, N]`` float32.  ``group_sizes`` must sum to the number of real tokens (``2 * lhs.shape[0]``, or one less when the
     last byte row holds a single token); it is not read on the host.
+
+    ``static_scratch=True`` uses the library's built-in scratch instead of a workspace tensor (at most
+    4096 groups, one call at a time per device); with ``out`` given and ``group_sizes`` already an int64
+    CUDA tensor, such a call allocates nothing at all.
     """
     torch = _torch()
     _require_cuda_tensor(torch, "lhs", lhs)
@@ -724,6 +729,8 @@ def ragged_dot_int4_bwd_flat(
     if tuple(a_scale.shape) != (groups, m) or tuple(b_scale.shape) != (groups, n):
         raise ValueError(f"a_scale must have shape ({groups}, {m}) and b_scale ({groups}, {n})")
     if group_sizes.device != lhs.device:
+        if static_scratch:
+            raise ValueError("static_scratch=True requires group_sizes on the operands' device")
         group_sizes = group_sizes.to(device=lhs.device)
     if out is None:
         out = torch.empty((groups, m, n), device=lhs.device, dtype=torch.float32)
@@ -732,4 +739,5 @@ def ragged_dot_int4_bwd_flat(
     from .native import launch_ragged_bwd_flat_kernel
 
     return launch_ragged_bwd_flat_kernel(lhs, rhs, group_sizes, a_scale=a_scale, b_scale=b_scale, out=out,
-                                         tokens=2 * int(lhs.shape[0]), library_path=native_library_path)
+                                         tokens=2 * int(lhs.shape[0]), library_path=native_library_path,
+                                         static_scratch=static_scratch)
