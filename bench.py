@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the quantized-GEMM hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5fwd|c5bwd] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5fwd|c5bwd|c5bwd_flat] [--impl ours|reference]
 
 Prints ONE JSON line (rank 0).  Default workload is the headline one: int4 x int4 per-channel GEMM at
 M = N = K = 4096 (metric: TOPS = 2*M*N*K / t).  One *step* is one pass over a batch of ``--batch``
@@ -58,6 +58,10 @@ WORKLOADS = {
     "c5bwd": dict(kind="ragged_bwd", rows=32768, m=2048, n=1408, groups=64,
                   name="ragged_dot_int4_bwd, 64 groups, 32768 tokens, out [64,2048,1408] fp32 (BASELINE config 5)",
                   metric="ragged_dot_int4 bwd TOPS"),
+    # the same grouped backward over FLAT token-packed operands (no per-group padding; not in the reference API)
+    "c5bwd_flat": dict(kind="ragged_bwd", flat=True, rows=32768, m=2048, n=1408, groups=64,
+                       name="ragged_dot_int4_bwd_flat, 64 groups, 32768 tokens back to back, out [64,2048,1408] fp32 (BASELINE config 5, flat dy)",
+                       metric="ragged_dot_int4 bwd TOPS"),
 }
 
 
@@ -68,6 +72,15 @@ def config5_group_sizes(torch):
     probs[torch.randperm(64, generator=g)[:3]] = 0
     draws = torch.multinomial(probs / probs.sum(), 32768, replacement=True, generator=g)
     return torch.bincount(draws, minlength=64)
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the workload's GEMM kernel, from one `ncu --set full`
+# capture of the same command at 1 GPU (summaries under profiles/).  Smaller than the algorithmic bytes where the
+# result is still in the 126 MB L2 when the kernel ends.
+NCU_DRAM_TRAFFIC_BYTES = {
+    "c2": 17.08e6, "c3": 463.3e6, "c4": 212.9e6, "c5fwd": 175.2e6, "c5bwd": 746.1e6, "c5bwd_flat": 737.8e6,
+}
+VENDOR_INT8_GEMM_TOPS = 2973.1  # torch._int_mm (cuBLASLt) int8 8192^3 on this pool's B200: `bench.py --probe-int8-peak`
 
 
 def workload_ops(w, sizes=None) -> float:
@@ -205,6 +218,14 @@ def build_problem_set(torch, pkg, w, batch: int, seed: int, device):
                 a_scale=scales((int(sizes.sum()),)), b_scale=scales((len(sizes), w["n"])),
                 group_sizes=sizes.to(device), out=torch.empty((int(sizes.sum()), w["n"]), device=device, dtype=torch.bfloat16),
             ))
+        elif w.get("flat"):
+            sizes = w["sizes"]
+            pairs = (int(sizes.sum()) + 1) // 2
+            problems.append(dict(
+                lhs=codes((pairs, w["m"])), rhs=codes((pairs, w["n"])),
+                a_scale=scales((len(sizes), w["m"])), b_scale=scales((len(sizes), w["n"])),
+                group_sizes=sizes.to(device), out=torch.empty((len(sizes), w["m"], w["n"]), device=device, dtype=torch.float32),
+            ))
         else:
             sizes = w["sizes"]
             cap = int(sizes.max()) if len(sizes) else 2
@@ -250,6 +271,14 @@ def make_runner(torch, pkg, w, problems):
                                                 k_packed=w["k"] // 2, scale_cols=1)
         return step, len(problems)
     cfg = RaggedBwdDotConfig()
+    if w.get("flat"):
+        tokens = [int(p["group_sizes"].sum()) for p in problems]
+
+        def step():
+            for p, t in zip(problems, tokens):
+                native.launch_ragged_bwd_flat_kernel(p["lhs"], p["rhs"], p["group_sizes"], a_scale=p["a_scale"], b_scale=p["b_scale"],
+                                                     out=p["out"], tokens=t)
+        return step, 2 * len(problems)  # the group-start scan + the GEMM kernel per problem
 
     def step():
         for p in problems:
@@ -281,6 +310,8 @@ def make_e2e_runner(torch, pkg, w, problem):
                              dtype=pkg.OperandDType(w["dtype"]), epilogue=pkg.Epilogue(w["epilogue"]), schedule=pkg.KernelSchedule.PERSISTENT)
         elif w["kind"] == "ragged_fwd":
             out = pkg.ragged_dot_int4(dev["lhs"], dev["rhs"], dev["group_sizes"], a_scale=dev["a_scale"], b_scale=dev["b_scale"])
+        elif w.get("flat"):
+            out = pkg.ragged_dot_int4_bwd_flat(dev["lhs"], dev["rhs"], dev["group_sizes"], a_scale=dev["a_scale"], b_scale=dev["b_scale"])
         else:
             out = pkg.ragged_dot_int4_bwd(dev["lhs"], dev["rhs"], dev["group_sizes"], a_scale=dev["a_scale"], b_scale=dev["b_scale"],
                                           layout=pkg.GemmLayout.TN)
@@ -435,6 +466,9 @@ def main() -> None:
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=0, help="independent problems per step (0 = enough to exceed L2 twice over)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--probe-int8-peak", action="store_true",
+                    help="time the vendor library's int8 GEMM (torch._int_mm, 8192^3, best of 10) and print it: "
+                         "a measured int8 figure to set beside the nominal 4500 TOPS; not a bench line")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -463,6 +497,24 @@ def main() -> None:
     import strix_halo_int4_gemms_b200 as pkg
     from strix_halo_int4_gemms_b200 import distributed as shard
     from strix_halo_int4_gemms_b200 import native
+
+    if args.probe_int8_peak:
+        n = 8192
+        a = torch.randint(-127, 128, (n, n), device="cuda", dtype=torch.int8)
+        b = torch.randint(-127, 128, (n, n), device="cuda", dtype=torch.int8).t()   # column-major B, as cuBLASLt wants it
+        for _ in range(3):
+            torch._int_mm(a, b)
+        best = float("inf")
+        for _ in range(10):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            torch._int_mm(a, b)
+            stop.record()
+            stop.synchronize()
+            best = min(best, float(start.elapsed_time(stop)))
+        print(json.dumps({"probe": "torch._int_mm int8 8192^3 -> int32, best of 10", "ms": best,
+                          "tops": 2.0 * n ** 3 / (best * 1e-3) / 1e12}), flush=True)
+        return
 
     status = pkg.dispatch_runtime_status()
     if not status.has_linked_kernels:
@@ -503,7 +555,9 @@ def main() -> None:
         raise SystemExit(f"a kernel reported status {dev_status}")
     ms_per_step = ms / args.steps
     value = ops_per_step / (ms_per_step * 1e-3) / 1e12
-    kernel_us = ms_per_step * 1e3 / launches_per_step
+    # duration of the dominant (GEMM) kernel: one per problem; the flat backward's group-start scan (one tiny
+    # CTA per problem, counted in gpu_launches) rides along inside it
+    kernel_us = ms_per_step * 1e3 / batch
 
     e2e = None
     if not args.no_e2e:
@@ -522,18 +576,21 @@ def main() -> None:
     peaks, peak_source = load_peaks()
     timed_s = ms / 1e3
     bf16_peak = peaks["bf16_tflops_sustained"] if timed_s > 1.0 and "bf16_tflops_sustained" in peaks else peaks["bf16_tflops"]
-    hbm_bound = args.workload == "c5bwd"
+    hbm_bound = args.workload in ("c5bwd", "c5bwd_flat")
     per_gpu_tops = value / world
+    traffic = NCU_DRAM_TRAFFIC_BYTES.get(args.workload) if world == 1 else None
     if hbm_bound:
         achieved = per_problem_bytes / (kernel_us * 1e-6) / 1e9
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                    "traffic": None, "peak_source": f"{peak_source} STREAM-style copy"}
+                    "traffic": traffic, "peak_source": f"{peak_source} STREAM-style copy",
+                    "algorithmic_bytes_per_launch": per_problem_bytes, "kernel_us": kernel_us}
     else:
         peak = 2.0 * bf16_peak
-        roofline = {"bound": "tensor", "achieved": per_gpu_tops, "peak": peak, "unit": "TFLOP/s", "frac": per_gpu_tops / peak, "traffic": None,
+        roofline = {"bound": "tensor", "achieved": per_gpu_tops, "peak": peak, "unit": "TFLOP/s", "frac": per_gpu_tops / peak, "traffic": traffic,
                     "peak_source": f"2 x {peak_source} cuBLAS bf16 {'sustained' if bf16_peak != peaks['bf16_tflops'] else 'burst'} "
                                    f"({bf16_peak} TFLOP/s): kind::i8 runs at twice the bf16 rate",
                     "frac_of_nominal_int8_4500": per_gpu_tops / NOMINAL_INT8_TOPS,
+                    "frac_of_vendor_int8_gemm": per_gpu_tops / VENDOR_INT8_GEMM_TOPS,
                     "algorithmic_bytes_per_launch": per_problem_bytes, "kernel_us": kernel_us}
 
     line = {
