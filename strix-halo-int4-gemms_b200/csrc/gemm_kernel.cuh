@@ -225,8 +225,12 @@ struct KernelTraits {
   // A CTA of a pair holds one 128-wide block of B (the MMA reads the other one from the peer), so
   // its stages are a third smaller and more of them fit.
   static constexpr int kBBlocks = k2Cta ? 1 : 2;
-  static constexpr int kStages = kInt4 ? (k2Cta ? B200_PAIR_INT4_STAGES : B200_INT4_STAGES)
-                                       : (k2Cta ? B200_PAIR_INT8_STAGES : B200_INT8_STAGES);  // int8 UMMA stages
+  // K-masked kernels serve the grouped backward pass: short reductions (a group's tokens) and large fp32
+  // tiles, so they give one operand stage to the output staging.
+  static constexpr bool kShortK = kMaskK && kInt4 && !k2Cta;
+  static constexpr int kStages = kShortK ? 2
+                                 : kInt4 ? (k2Cta ? B200_PAIR_INT4_STAGES : B200_INT4_STAGES)
+                                         : (k2Cta ? B200_PAIR_INT8_STAGES : B200_INT8_STAGES);  // int8 UMMA stages
   static constexpr int kPkStages = kInt4 ? (k2Cta ? B200_PAIR_INT4_PK_STAGES : B200_INT4_PK_STAGES) : 0; // packed staging stages
   static constexpr int kA8Bytes = BM * BK;                  // 16 KB
   static constexpr int kB8Bytes = kBBlocks * NBLK * BK;     // 32 KB (pair: 16 KB)
@@ -238,13 +242,18 @@ struct KernelTraits {
   // results leave through shared memory + TMA stores (per-channel kernels; 2 KB per epilogue warp)
   static constexpr bool kTmaStore = (kScale == SCALE_PC) ? (kOut != OUT_S32) : (kOut == OUT_BF16);
   static constexpr int kStagingSlots = 2;
-  // per-channel: per warp 2 slots x 2 KB (bf16) or 1 x 4 KB (fp32); subchannel: 2 KB per warp
-  static constexpr int kStagingPerWarp = (kScale == SCALE_PC) ? kStagingSlots * 2048 : 2048;
+  // fp32 output of the backward kernels: four 4 KB slots per warp; two 32-column chunks are staged, fenced
+  // and handed to TMA together (one proxy fence per 64 columns), while the previous two are still being read
+  static constexpr int kF32Slots = kShortK ? 4 : 1;
+  // per-channel: per warp 2 slots x 2 KB (bf16) or kF32Slots x 4 KB (fp32); subchannel: 2 KB per warp
+  static constexpr int kStagingPerWarp =
+      (kScale == SCALE_PC) ? (kOut == OUT_F32 ? kF32Slots * 4096 : kStagingSlots * 2048) : 2048;
   static constexpr int kStagingBytes = kTmaStore ? kEpiWarps * kStagingPerWarp : 0;
   // column scales as fp32: per-channel 256 per warp; subchannel 2 x 128 per warp (double-buffered by K-group)
   static constexpr int kScaleStripBytes = kEpiWarps * 1024;
   static constexpr int kSmemBytes =
       1024 + kStages * kStageBytes + kPkStages * kPkStageBytes + kStagingBytes + kScaleStripBytes + kBarBytes;
+  static_assert(kSmemBytes <= 232448, "over the 227 KB of shared memory a CTA can have");
 };
 
 template <bool kInt4, bool kAMn, bool kBMn, int kScale, int kEpi, int kOut, bool kMaskK, bool k2Cta = false>
@@ -700,6 +709,34 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 if (lane == 0) {
                   tma_store_2d(&tmap_c, stage_out_u32 + slot * 2048, col0 * 2, w.out_row_base + wrow0);
                   bulk_commit_group();
+                }
+              } else if constexpr (T::kF32Slots >= 4) {
+                // chunks are staged in pairs: slots (0,1) and (2,3) alternate, one fence and one bulk group per pair
+                const int slot = store_count & 3;
+                ++store_count;
+                uint8_t* dst = stage_out + slot * 4096 + lane * 128;
+                const int sw = lane & 7;
+                if ((slot & 1) == 0) {
+                  if (lane == 0) bulk_wait_read_keep<1>();  // the pair that used these two slots has been read
+                  __syncwarp();
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  uint4 pk;
+                  pk.x = __float_as_uint(v[4 * i + 0]);
+                  pk.y = __float_as_uint(v[4 * i + 1]);
+                  pk.z = __float_as_uint(v[4 * i + 2]);
+                  pk.w = __float_as_uint(v[4 * i + 3]);
+                  *reinterpret_cast<uint4*>(dst + ((i ^ sw) << 4)) = pk;
+                }
+                if ((slot & 1) == 1) {
+                  fence_proxy_async_smem();
+                  __syncwarp();
+                  if (lane == 0) {
+                    tma_store_2d(&tmap_c, stage_out_u32 + (slot - 1) * 4096, (col0 - 32) * 4, w.out_row_base + wrow0);
+                    tma_store_2d(&tmap_c, stage_out_u32 + slot * 4096, col0 * 4, w.out_row_base + wrow0);
+                    bulk_commit_group();
+                  }
                 }
               } else {
                 uint8_t* dst = stage_out + lane * 128;
