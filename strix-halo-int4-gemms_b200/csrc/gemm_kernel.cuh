@@ -197,17 +197,22 @@ struct KernelTraits {
 #ifndef B200_INT4_PK_STAGES
 #define B200_INT4_PK_STAGES 2
 #endif
-  // Subchannel kernels re-balance registers between roles with setmaxnreg, which works on warpgroups
-  // (4 consecutive warps): warps 0..3 = TMA, MMA and two idle warps, 4..11 = epilogue, 12..15 = unpack.
-  static constexpr bool kRegBalance = (kScale == SCALE_SC);
-  static constexpr int kUnpackWarps = kInt4 ? (kRegBalance ? 4 : B200_UNPACK_WARPS) : 0;
-  static constexpr int kEpiWarps = (kScale == SCALE_SC) ? 8 : 4;
+  // K-masked kernels serve the grouped backward pass: short reductions (a group's tokens) and large fp32
+  // tiles.  Their epilogue is the long pole, so it gets eight warps (two per TMEM lane quarter, half of the
+  // columns each) and one of the operand stages as output staging.
+  static constexpr bool kShortK = kMaskK && kInt4 && !k2Cta;
+  // Kernels with eight epilogue warps re-balance registers between roles with setmaxnreg, which works on
+  // warpgroups (4 consecutive warps): warps 0..3 = TMA, MMA and two idle warps, 4..11 = epilogue, then unpack
+  // (4 warps next to the subchannel epilogue, whose running sums need 184 registers; 8 warps otherwise).
+  static constexpr bool kRegBalance = (kScale == SCALE_SC) || kShortK;
+  static constexpr int kUnpackWarps = kInt4 ? ((kScale == SCALE_SC) ? 4 : B200_UNPACK_WARPS) : 0;
+  static constexpr int kEpiWarps = kRegBalance ? 8 : 4;
   static constexpr int kEpiWarp0 = kRegBalance ? 4 : 2;
   static constexpr int kUnpackWarp0 = kEpiWarp0 + kEpiWarps;
   static constexpr int kThreads = (kUnpackWarp0 + kUnpackWarps) * 32;
   static constexpr int kRegsLight = 40;    // TMA / MMA warpgroup
-  static constexpr int kRegsUnpack = 96;
-  static constexpr int kRegsEpilogue = 184;
+  static constexpr int kRegsUnpack = (kScale == SCALE_SC) ? 96 : 80;
+  static constexpr int kRegsEpilogue = (kScale == SCALE_SC) ? 184 : 136;
   // registers the CTA needs after the re-balance; the host checks this against regs-per-thread x threads
   static constexpr int kRegPoolNeeded = kRegBalance ? (128 * kRegsLight + 256 * kRegsEpilogue + kUnpackWarps * 32 * kRegsUnpack) : 0;
 #ifndef B200_INT8_STAGES
@@ -225,9 +230,6 @@ struct KernelTraits {
   // A CTA of a pair holds one 128-wide block of B (the MMA reads the other one from the peer), so
   // its stages are a third smaller and more of them fit.
   static constexpr int kBBlocks = k2Cta ? 1 : 2;
-  // K-masked kernels serve the grouped backward pass: short reductions (a group's tokens) and large fp32
-  // tiles, so they give one operand stage to the output staging.
-  static constexpr bool kShortK = kMaskK && kInt4 && !k2Cta;
   static constexpr int kStages = kShortK ? 2
                                  : kInt4 ? (k2Cta ? B200_PAIR_INT4_STAGES : B200_INT4_STAGES)
                                          : (k2Cta ? B200_PAIR_INT8_STAGES : B200_INT8_STAGES);  // int8 UMMA stages
@@ -242,9 +244,9 @@ struct KernelTraits {
   // results leave through shared memory + TMA stores (per-channel kernels; 2 KB per epilogue warp)
   static constexpr bool kTmaStore = (kScale == SCALE_PC) ? (kOut != OUT_S32) : (kOut == OUT_BF16);
   static constexpr int kStagingSlots = 2;
-  // fp32 output of the backward kernels: four 4 KB slots per warp; two 32-column chunks are staged, fenced
-  // and handed to TMA together (one proxy fence per 64 columns), while the previous two are still being read
-  static constexpr int kF32Slots = kShortK ? 4 : 1;
+  // fp32 output of the backward kernels: two 4 KB slots per warp, so that a chunk is staged while TMA still
+  // reads the previous one
+  static constexpr int kF32Slots = kShortK ? 2 : 1;
   // per-channel: per warp 2 slots x 2 KB (bf16) or kF32Slots x 4 KB (fp32); subchannel: 2 KB per warp
   static constexpr int kStagingPerWarp =
       (kScale == SCALE_PC) ? (kOut == OUT_F32 ? kF32Slots * 4096 : kStagingSlots * 2048) : 2048;
@@ -710,16 +712,13 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   tma_store_2d(&tmap_c, stage_out_u32 + slot * 2048, col0 * 2, w.out_row_base + wrow0);
                   bulk_commit_group();
                 }
-              } else if constexpr (T::kF32Slots >= 4) {
-                // chunks are staged in pairs: slots (0,1) and (2,3) alternate, one fence and one bulk group per pair
-                const int slot = store_count & 3;
+              } else if constexpr (T::kF32Slots == 2) {
+                const int slot = store_count & 1;
                 ++store_count;
                 uint8_t* dst = stage_out + slot * 4096 + lane * 128;
                 const int sw = lane & 7;
-                if ((slot & 1) == 0) {
-                  if (lane == 0) bulk_wait_read_keep<1>();  // the pair that used these two slots has been read
-                  __syncwarp();
-                }
+                if (lane == 0) bulk_wait_read_keep<1>();
+                __syncwarp();
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                   uint4 pk;
@@ -729,14 +728,11 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   pk.w = __float_as_uint(v[4 * i + 3]);
                   *reinterpret_cast<uint4*>(dst + ((i ^ sw) << 4)) = pk;
                 }
-                if ((slot & 1) == 1) {
-                  fence_proxy_async_smem();
-                  __syncwarp();
-                  if (lane == 0) {
-                    tma_store_2d(&tmap_c, stage_out_u32 + (slot - 1) * 4096, (col0 - 32) * 4, w.out_row_base + wrow0);
-                    tma_store_2d(&tmap_c, stage_out_u32 + slot * 4096, col0 * 4, w.out_row_base + wrow0);
-                    bulk_commit_group();
-                  }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                  tma_store_2d(&tmap_c, stage_out_u32 + slot * 4096, col0 * 4, w.out_row_base + wrow0);
+                  bulk_commit_group();
                 }
               } else {
                 uint8_t* dst = stage_out + lane * 128;
@@ -799,17 +795,20 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         };
 
 #ifdef B200_DBG_SKIP_EPILOGUE
-        constexpr int kOutChunks = 0;
+        constexpr int kAllChunks = 0;
 #else
-        constexpr int kOutChunks = (kEpi == EPI_SWIGLU) ? 4 : 8;
+        constexpr int kAllChunks = (kEpi == EPI_SWIGLU) ? 4 : 8;
 #endif
+        // with eight epilogue warps, the two warps of a lane quarter split the chunks between them
+        constexpr int kOutChunks = kAllChunks / (T::kEpiWarps / 4);
+        const int c_first = half * kOutChunks;
         // two register sets: the TMEM read of the next chunk is in flight while this one is processed
         uint32_t ra[32], rb[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) { ra[i] = 0u; rb[i] = 0u; }
-        if (!zero_tile && kOutChunks > 0) tmem_ld_32x32b_x32(acc_addr, ra);
+        if (!zero_tile && kOutChunks > 0) tmem_ld_32x32b_x32(acc_addr + 32 * c_first, ra);
 #pragma unroll 1
-        for (int c = 0; c < kOutChunks; c += 2) {
+        for (int c = c_first; c < c_first + kOutChunks; c += 2) {
           if (!zero_tile) {
             tmem_ld_wait();
             tmem_ld_fence(ra);
@@ -819,7 +818,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (!zero_tile) {
             tmem_ld_wait();
             tmem_ld_fence(rb);
-            if (c + 2 < kOutChunks) tmem_ld_32x32b_x32(acc_addr + 32 * (c + 2), ra);
+            if (c + 2 < c_first + kOutChunks) tmem_ld_32x32b_x32(acc_addr + 32 * (c + 2), ra);
           }
           process(rb, c + 1);
         }
