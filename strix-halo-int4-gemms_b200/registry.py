@@ -47,10 +47,11 @@ DEVICE_KERNEL = "b200::gemm_i8_tcgen05_kernel"
 
 
 def cta_warps(dtype: OperandDType, scale: ScaleSpec) -> int:
-    """TMA + MMA warps, 4 (per-channel) or 8 (subchannel) epilogue warps, 4 unpack warps for int4."""
-    epilogue_warps = 8 if scale.mode is ScaleMode.SUBCHANNEL else 4
-    unpack_warps = 4 if dtype is OperandDType.INT4 else 0
-    return 2 + epilogue_warps + unpack_warps
+    """Warps of the kernel's CTA.  Per-channel: TMA + MMA warps, 4 epilogue warps, 8 unpack warps for int4.
+    Subchannel: a warpgroup of 4 for TMA / MMA (two of them idle), 8 epilogue warps, 4 unpack warps for int4."""
+    if scale.mode is ScaleMode.SUBCHANNEL:
+        return 4 + 8 + (4 if dtype is OperandDType.INT4 else 0)
+    return 2 + 4 + (8 if dtype is OperandDType.INT4 else 0)
 
 
 def pipeline_stages(dtype: OperandDType) -> int:

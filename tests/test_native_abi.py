@@ -100,7 +100,7 @@ def test_launcher_validation_before_any_device_work(pkg):
     k = pkg.default_registry.select(
         dtype=pkg.OperandDType.INT4, scale=pkg.ScaleSpec(pkg.ScaleMode.PER_CHANNEL), epilogue=pkg.Epilogue.NONE, m=4096, n=4096, k=4096
     )
-    assert block_size(k) == 320
+    assert block_size(k) == 448  # 2 + 4 + 8 warps: TMA, MMA, epilogue, unpack
     assert launch_grid(k, 4096, 4096) == (512, 1, 1)
     persistent = pkg.default_registry.select(
         dtype=pkg.OperandDType.INT4, scale=pkg.ScaleSpec(pkg.ScaleMode.PER_CHANNEL), epilogue=pkg.Epilogue.NONE,

@@ -55,7 +55,7 @@ def _select(pkg, **kw):
 def test_selection_prefers_largest_registered_multiples(pkg):
     k = _select(pkg, m=4096, n=4096, k=4096)
     assert (k.tile.block_m, k.tile.block_n, k.tile.split_k, k.tile.even_k) == (128, 256, 1, True)
-    assert k.kernel_id == "sm_100a_int4xint4_nn_pc_none_bm128_bn256_bk32_gm8_w10_s3_weu0_sk1_evenk"
+    assert k.kernel_id == "sm_100a_int4xint4_nn_pc_none_bm128_bn256_bk32_gm8_w14_s3_weu0_sk1_evenk"
     assert _select(pkg, m=128, n=1024, k=64).tile.block_m == 128          # the quick-start shape
     small = _select(pkg, m=48, n=384, k=96)
     assert (small.tile.block_m, small.tile.block_n) == (16, 128)
