@@ -431,10 +431,10 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     };
     auto wait_operands = [&](int s, uint32_t ph) -> bool {
       bool got = mbar_wait(full_bar(s), ph, ctx, 20);
-      if constexpr (k2Cta) got = got && mbar_wait<true>(peer_full_bar(s), ph, ctx, 22);
+      if constexpr (k2Cta) got = got && mbar_wait(peer_full_bar(s), ph, ctx, 22);
       return got;
     };
-    auto wait_acc_empty = [&](int b, uint32_t ph) -> bool { return mbar_wait<k2Cta>(acc_empty_bar(b), ph, ctx, 21); };
+    auto wait_acc_empty = [&](int b, uint32_t ph) -> bool { return mbar_wait(acc_empty_bar(b), ph, ctx, 21); };
     if (k2Cta && cta_rank != 0) {
       // Peer CTA of a pair: no MMAs are issued here.  Forward "my stage s is full" to the leader.
       int it = 0;
@@ -446,9 +446,6 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t ph = (it / S) & 1;
           if (!__all_sync(0xFFFFFFFFu, mbar_wait(full_bar(s), ph, ctx, 23))) { ok = false; break; }
           if (elect_one()) {
-#ifdef B200_FORWARD_FENCE
-            fence_proxy_async_smem();
-#endif
             mbar_arrive_cluster(map_to_cta(peer_full_bar(s), 0));
           }
           __syncwarp();

@@ -50,30 +50,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
-#ifdef B200_TRY_WAIT_HINT_NS
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#endif
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(ok)
-#ifdef B200_TRY_WAIT_HINT_NS
-      : "r"(bar), "r"(parity), "r"(static_cast<uint32_t>(B200_TRY_WAIT_HINT_NS))
-#else
-      : "r"(bar), "r"(parity)
-#endif
-      : "memory");
-  return ok != 0;
-}
-
-// Same, with acquire semantics at cluster scope: for barriers that threads of the peer CTA arrive on.
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t"
       "}\n"
       : "=r"(ok)
@@ -96,19 +73,13 @@ struct AbortCtx {
 
 // Bounded wait.  Returns false when the wait was abandoned (either this wait ran
 // out of time or another role in the CTA already raised the abort flag).
-template <bool kClusterScope = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtx& ctx,
                                           int site) {
-#ifdef B200_WAIT_ACQUIRE_CLUSTER
-  auto try_wait = [&]() { return kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity); };
-#else
-  auto try_wait = [&]() { return mbar_try_wait(bar, parity); };
-#endif
-  if (try_wait()) return true;
+  if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   uint32_t spins = 0;
   while (true) {
-    if (try_wait()) return true;
+    if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3FFu) == 0u) {
       if (*ctx.cta_flag) return false;
       if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
@@ -161,13 +132,13 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
   return r;
 }
-// Arrive (count 1) on an mbarrier of any CTA of the cluster.
+// Arrive (count 1) on an mbarrier of any CTA of the cluster.  Default semantics (release at CTA scope), as
+// for the waits: the data these barriers guard travels through the async proxy (TMA writes, tensor-core
+// reads, tcgen05.commit), which orders itself against the barrier.  The explicitly cluster-scoped forms
+// (arrive.release.cluster / try_wait.acquire.cluster) were measured: they made the pair kernels 2.4 times
+// slower, one remote arrive then taking about a microsecond.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-#ifdef B200_REMOTE_ARRIVE_RELEASE_CLUSTER
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-#else
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-#endif
 }
 // All threads of all CTAs of the cluster.
 __device__ __forceinline__ void cluster_sync_all() {
