@@ -289,33 +289,52 @@ def make_runner(torch, pkg, w, problems):
 
 
 def make_e2e_runner(torch, pkg, w, problem):
-    """One step through the PUBLIC API from pinned host buffers and back; returns (callable, h2d, d2h bytes)."""
+    """One step through the PUBLIC API from pinned host buffers and back; returns (callable, h2d, d2h bytes).
+
+    Every step uploads its operands, calls the API and downloads the result.  Steps alternate between two
+    streams with their own device and host buffers, the way a host pipeline would run them, so that one step's
+    upload overlaps the previous step's download (PCIe is full duplex); the work of each step is unchanged.
+    ``step.finish()`` joins both streams into the current one (called before the stop event is recorded)."""
+    lanes = 2
+    streams = [torch.cuda.Stream() for _ in range(lanes)]
     host = {k: v.cpu().pin_memory() for k, v in problem.items() if k != "out"}
-    out_host = torch.empty(problem["out"].shape, dtype=problem["out"].dtype).pin_memory()
-    dev = {k: torch.empty_like(v, device="cuda") for k, v in host.items()}
+    out_host = [torch.empty(problem["out"].shape, dtype=problem["out"].dtype).pin_memory() for _ in range(lanes)]
+    dev_sets = [{k: torch.empty_like(v, device="cuda") for k, v in host.items()} for _ in range(lanes)]
     h2d = sum(v.numel() * v.element_size() for v in host.values())
-    d2h = out_host.numel() * out_host.element_size()
+    d2h = out_host[0].numel() * out_host[0].element_size()
     pc = pkg.ScaleSpec(pkg.ScaleMode.PER_CHANNEL)
+    state = {"i": 0}
 
     def step():
-        for k, v in host.items():
-            dev[k].copy_(v, non_blocking=True)
-        if w["kind"] == "dense":
-            scale = pkg.ScaleSpec(pkg.ScaleMode.SUBCHANNEL, w["sub"]) if w["sub"] else pc
-            if w["epilogue"] == "swiglu":
-                out = pkg.fused_swiglu_up_gate(dev["a"], dev["b"], a_scale=dev["a_scale"], b_scale=dev["b_scale"], scale=scale,
-                                               dtype=pkg.OperandDType(w["dtype"]))
+        lane = state["i"] % lanes
+        state["i"] += 1
+        stream, dev = streams[lane], dev_sets[lane]
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            for k, v in host.items():
+                dev[k].copy_(v, non_blocking=True)
+            if w["kind"] == "dense":
+                scale = pkg.ScaleSpec(pkg.ScaleMode.SUBCHANNEL, w["sub"]) if w["sub"] else pc
+                if w["epilogue"] == "swiglu":
+                    out = pkg.fused_swiglu_up_gate(dev["a"], dev["b"], a_scale=dev["a_scale"], b_scale=dev["b_scale"], scale=scale,
+                                                   dtype=pkg.OperandDType(w["dtype"]))
+                else:
+                    out = pkg.mm(dev["a"], dev["b"], a_scale=dev["a_scale"], b_scale=dev["b_scale"], scale=scale,
+                                 dtype=pkg.OperandDType(w["dtype"]), epilogue=pkg.Epilogue(w["epilogue"]), schedule=pkg.KernelSchedule.PERSISTENT)
+            elif w["kind"] == "ragged_fwd":
+                out = pkg.ragged_dot_int4(dev["lhs"], dev["rhs"], dev["group_sizes"], a_scale=dev["a_scale"], b_scale=dev["b_scale"])
+            elif w.get("flat"):
+                out = pkg.ragged_dot_int4_bwd_flat(dev["lhs"], dev["rhs"], dev["group_sizes"], a_scale=dev["a_scale"], b_scale=dev["b_scale"])
             else:
-                out = pkg.mm(dev["a"], dev["b"], a_scale=dev["a_scale"], b_scale=dev["b_scale"], scale=scale,
-                             dtype=pkg.OperandDType(w["dtype"]), epilogue=pkg.Epilogue(w["epilogue"]), schedule=pkg.KernelSchedule.PERSISTENT)
-        elif w["kind"] == "ragged_fwd":
-            out = pkg.ragged_dot_int4(dev["lhs"], dev["rhs"], dev["group_sizes"], a_scale=dev["a_scale"], b_scale=dev["b_scale"])
-        elif w.get("flat"):
-            out = pkg.ragged_dot_int4_bwd_flat(dev["lhs"], dev["rhs"], dev["group_sizes"], a_scale=dev["a_scale"], b_scale=dev["b_scale"])
-        else:
-            out = pkg.ragged_dot_int4_bwd(dev["lhs"], dev["rhs"], dev["group_sizes"], a_scale=dev["a_scale"], b_scale=dev["b_scale"],
-                                          layout=pkg.GemmLayout.TN)
-        out_host.copy_(out, non_blocking=True)
+                out = pkg.ragged_dot_int4_bwd(dev["lhs"], dev["rhs"], dev["group_sizes"], a_scale=dev["a_scale"], b_scale=dev["b_scale"],
+                                              layout=pkg.GemmLayout.TN)
+            out_host[lane].copy_(out, non_blocking=True)
+
+    def finish():
+        for stream in streams:
+            torch.cuda.current_stream().wait_stream(stream)
+
+    step.finish = finish
     return step, h2d, d2h
 
 
@@ -332,6 +351,9 @@ def timed_region(torch, dist, world, step, steps: int, warmup: int, sampler=None
         start.record()
         for _ in range(steps):
             step()
+        finish = getattr(step, "finish", None)
+        if finish is not None:
+            finish()  # steps that run on side streams: the stop event must come after all of them
         stop.record()
         stop.synchronize()
     torch.cuda.synchronize()
@@ -566,7 +588,8 @@ def main() -> None:
         e2e_ms = timed_region(torch, dist, world, e2e_step, e2e_steps, 3) / e2e_steps
         e2e = {"value": (ops_per_step / batch) / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS", "h2d_bytes_per_step": int(h2d),
                "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms, "steps": e2e_steps,
-               "note": "one problem per step through the public API; pinned host operands in, result out, copies inside the timed region"}
+               "note": "one problem per step through the public API; pinned host operands in, result out, copies inside the timed region; "
+                       "steps alternate between two streams so that uploads overlap the previous step's download"}
 
     if rank != 0:
         if world > 1:
