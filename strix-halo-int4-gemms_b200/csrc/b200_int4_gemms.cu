@@ -158,7 +158,14 @@ cudaError_t set_smem(Kernel kernel, int bytes) {
   X(false, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true)          \
   X(false, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, true)         \
   X(false, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, true)        \
-  X(false, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, true)
+  X(false, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, true)           \
+  X(false, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, true)          \
+  X(false, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, true)         \
+  X(false, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, true)        \
+  X(false, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, true)         \
+  X(false, false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false, true)        \
+  X(true, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, true)          \
+  X(true, true, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true)
 
 int ensure_device(int device_index, DeviceState** out) {
   if (device_index < 0 || device_index >= kMaxDevices) return fail("device_index out of range");

@@ -171,3 +171,44 @@ def test_config5_ragged_backward(pkg):
                                      bf16_bits(sa[g:g + 1]), bf16_bits(sb[g:g + 1]), layout="tn")
         np.testing.assert_array_equal(out[g].cpu().numpy(), want[0], err_msg=f"group {g}")
     assert torch.equal(out, pkg.ragged_dot_int4_bwd(lhs, rhs, sizes.cuda(), a_scale=sa, b_scale=sb, layout=pkg.GemmLayout.TN))
+
+
+def test_config5_forward_with_tasks_built_on_the_device(pkg):
+    """Same launch with the task arrays and their count built and kept on the GPU: identical output."""
+    sizes = _config5_group_sizes().cuda()
+    rows, k, n, groups = 32768, 2048, 1408, 64
+    lhs, rhs = _random_bytes((rows, k // 2), 20), _random_bytes((groups, k // 2, n), 21)
+    sa, sb = _scales((rows,), 22).cuda(), _scales((groups, n), 23).cuda()
+    want = pkg.ragged_dot_int4(lhs, rhs, sizes, a_scale=sa, b_scale=sb)
+    cfg = pkg.RaggedDotConfig(block_m=256)
+    info = pkg.calculate_group_info_on_device(sizes, cfg.block_m, total_rows=rows, align_tile=cfg.align_tile)
+    got = pkg.ragged_dot_int4(lhs, rhs, sizes, a_scale=sa, b_scale=sb, config=cfg, group_info=info)
+    torch.cuda.synchronize()
+    assert int(info.device_overflow.item()) == 0
+    assert torch.equal(got, want)
+
+
+def test_config5_flat_backward_from_forward_format_operands(pkg):
+    """x [32768, 2048] and dy [32768, 1408] in the forward packing -> token repack on the GPU -> flat backward;
+    checked against the oracle on the smallest, the median and the largest group and against a second run."""
+    sizes = _config5_group_sizes()
+    tokens, groups, m, n = 32768, 64, 2048, 1408
+    x, dy = _random_bytes((tokens, m // 2), 40), _random_bytes((tokens, n // 2), 41)
+    sa, sb = _scales((groups, m), 42).cuda(), _scales((groups, n), 43).cuda()
+    lhs, rhs = pkg.repack_int4_tokens(x), pkg.repack_int4_tokens(dy)
+    assert tuple(lhs.shape) == (tokens // 2, m) and tuple(rhs.shape) == (tokens // 2, n)
+    out = pkg.ragged_dot_int4_bwd_flat(lhs, rhs, sizes.cuda(), a_scale=sa, b_scale=sb)
+    torch.cuda.synchronize()
+    ends = torch.cumsum(sizes, 0)
+    order = torch.argsort(sizes)
+    nonempty = [int(g) for g in order if sizes[g] > 0]
+    empty = [int(g) for g in order if sizes[g] == 0]
+    assert float(out[empty].abs().max()) == 0.0
+    for g in (nonempty[0], nonempty[len(nonempty) // 2], nonempty[-1]):
+        lo, hi = int(ends[g] - sizes[g]), int(ends[g])
+        xg = oracle.unpack_int4_k_major(x[lo:hi].cpu().numpy())      # [tokens of g, m]
+        dg = oracle.unpack_int4_k_major(dy[lo:hi].cpu().numpy())     # [tokens of g, n]
+        want = oracle.scaled_matmul(np.ascontiguousarray(xg.T), dg, oracle.bf16_bits_to_f32(bf16_bits(sa[g])),
+                                    oracle.bf16_bits_to_f32(bf16_bits(sb[g])))
+        np.testing.assert_array_equal(out[g].cpu().numpy(), want, err_msg=f"group {g}")
+    assert torch.equal(out, pkg.ragged_dot_int4_bwd_flat(lhs, rhs, sizes.cuda(), a_scale=sa, b_scale=sb, static_scratch=True))
