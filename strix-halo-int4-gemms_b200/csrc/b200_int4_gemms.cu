@@ -198,9 +198,15 @@ int ensure_device(int device_index, DeviceState** out) {
     cudaFuncAttributes attr;                                                                             \
     err = cudaFuncGetAttributes(&attr, gemm_i8_tcgen05_kernel<I4, AMN, BMN, SC, EP, OT, MK, PR>);           \
     if (err != cudaSuccess) return fail_cuda("cudaFuncGetAttributes", err);                              \
-    if (attr.numRegs * KernelTraits<I4, AMN, BMN, SC, EP, OT, MK, PR>::kThreads <                            \
-        KernelTraits<I4, AMN, BMN, SC, EP, OT, MK, PR>::kRegPoolNeeded)                                      \
-      return fail("a subchannel kernel was compiled with too few registers for its register re-balance"); \
+    using KT = KernelTraits<I4, AMN, BMN, SC, EP, OT, MK, PR>;                                             \
+    const bool pool_ok = attr.numRegs * KT::kThreads >= KT::kRegPoolNeeded;                              \
+    /* setmaxnreg.inc may not lower and setmaxnreg.dec may not raise a warp's register count */           \
+    const bool moves_ok = attr.numRegs >= KT::kRegsLight && attr.numRegs <= KT::kRegsEpilogue &&         \
+                          (KT::kUnpackWarps == 0 ||                                                     \
+                           (KT::kUnpackRaises ? attr.numRegs <= KT::kRegsUnpack : attr.numRegs >= KT::kRegsUnpack)); \
+    if (!pool_ok || !moves_ok)                                                                           \
+      return fail("a kernel was compiled with " + std::to_string(attr.numRegs) +                        \
+                  " registers per thread, which does not fit its setmaxnreg register re-balance");      \
   }
     B200_FOR_EACH_TC_KERNEL(X)
 #undef X

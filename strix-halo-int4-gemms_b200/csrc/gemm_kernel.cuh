@@ -213,6 +213,12 @@ struct KernelTraits {
   static constexpr int kRegsLight = 40;    // TMA / MMA warpgroup
   static constexpr int kRegsUnpack = (kScale == SCALE_SC) ? 96 : 80;
   static constexpr int kRegsEpilogue = (kScale == SCALE_SC) ? 184 : 136;
+  // The most registers per thread the kernel can be launched with (what the compiler may use before the
+  // re-balance).  setmaxnreg.dec must not name more than a warp currently has, setmaxnreg.inc not less: a
+  // role whose target is at or above this cap raises its count, one below it lowers it, and the host checks
+  // the compiled kernel's actual register count against both before the first launch.
+  static constexpr int kCapRegs = (65536 / kThreads) / 8 * 8 > 255 ? 255 : (65536 / kThreads) / 8 * 8;
+  static constexpr bool kUnpackRaises = kRegsUnpack >= kCapRegs;
   // registers the CTA needs after the re-balance; the host checks this against regs-per-thread x threads
   static constexpr int kRegPoolNeeded = kRegBalance ? (128 * kRegsLight + 256 * kRegsEpilogue + kUnpackWarps * 32 * kRegsUnpack) : 0;
 #ifndef B200_INT8_STAGES
@@ -997,7 +1003,10 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (lane == 0) bulk_wait_all();  // TMA stores issued by this lane have landed
   } else if (warp >= T::kUnpackWarp0) {
     // ------------------------------------------------------------------ unpack (int4 only)
-    if constexpr (T::kRegBalance) reg_dealloc<T::kRegsUnpack>();
+    if constexpr (T::kRegBalance) {
+      if constexpr (T::kUnpackRaises) reg_alloc<T::kRegsUnpack>();
+      else reg_dealloc<T::kRegsUnpack>();
+    }
     if constexpr (kInt4) {
       constexpr int UT = T::kUnpackWarps * 32;           // unpack threads: 128 or 256
       const int ut = threadIdx.x - T::kUnpackWarp0 * 32;
