@@ -243,7 +243,6 @@ def make_runner(torch, pkg, w, problems):
     from strix_halo_int4_gemms_b200 import native
     from strix_halo_int4_gemms_b200.ragged import RaggedBwdDotConfig, RaggedDotConfig
 
-    stream = torch.cuda.current_stream().cuda_stream
     device_index = torch.cuda.current_device()
     pc = pkg.ScaleSpec(pkg.ScaleMode.PER_CHANNEL)
     if w["kind"] == "dense":
@@ -255,7 +254,9 @@ def make_runner(torch, pkg, w, problems):
 
         def step():
             for ptrs in args:
-                native.launch_dense(variant, device_index=device_index, stream_handle=stream, m=w["m"], n=w["n"], k=w["k"], **ptrs)
+                # the stream is looked up per call: under CUDA-graph capture the current stream is the capturing one
+                native.launch_dense(variant, device_index=device_index, stream_handle=torch.cuda.current_stream().cuda_stream,
+                                    m=w["m"], n=w["n"], k=w["k"], **ptrs)
         return step, len(problems)
     if w["kind"] == "ragged_fwd":
         # the task height ragged_dot_int4 itself picks for groups this large: 256-row tasks on pairs of SMs
@@ -492,6 +493,7 @@ def main() -> None:
                     help="time the vendor library's int8 GEMM (torch._int_mm, 8192^3, best of 10) and print it: "
                          "a measured int8 figure to set beside the nominal 4500 TOPS; not a bench line")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of replaying a CUDA graph of one step")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -569,6 +571,17 @@ def main() -> None:
         dist.all_reduce(ops_t)
     ops_per_step = float(ops_t.item())
 
+    # One step (its `launches_per_step` kernels) is captured into a CUDA graph and replayed: at 60 us per kernel the
+    # Python launch loop is otherwise the bottleneck as soon as several ranks share the host's cores.
+    graphed = False
+    if not args.no_graph:
+        step()  # first-call set-up of the library happens outside the capture
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        step = graph.replay
+        graphed = True
     sampler = ClockSampler(visible_device_index(local_rank))
     native.reset_device_status(local_rank)
     ms = timed_region(torch, dist, world, step, args.steps, args.warmup, sampler)
@@ -623,6 +636,7 @@ def main() -> None:
         "data": "synthetic",
         "config": {
             "workload": w["name"], "problems_per_step": batch,
+            "launch": "one CUDA graph replay per step" if graphed else "one Python call per kernel",
             "l2": f"{batch} independent operand/output sets per step, {batch * per_problem_bytes / 1e6:.0f} MB touched between reuses (> 126 MB L2)",
             "parallelism": "none" if world == 1 else ("column-parallel along N, one shard per GPU" if w["kind"] == "dense" else f"expert-parallel, LPT assignment, max/mean load {imbalance:.3f}"),
             "per_gpu_problem": "same as 1-GPU (weak scaling)",
