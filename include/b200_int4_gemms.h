@@ -52,9 +52,9 @@ enum { B200_PATH_AUTO = 0, B200_PATH_TCGEN05 = 1, B200_PATH_SIMT = 2 };
 /* PERSISTENT: one CTA per SM walks the tile list.  STANDARD: one CTA per output tile. */
 enum { B200_SCHEDULE_PERSISTENT = 0, B200_SCHEDULE_STANDARD = 1 };
 
-/* AUTO: the library pairs CTAs (clusters of two SMs, 256 x 256 tiles, tcgen05 cta_group::2) when the
- * problem has enough 256-row tiles and a paired kernel exists for the variant, else one CTA per
- * 128 x 256 tile.  SINGLE / PAIR force one of them (PAIR falls back to SINGLE when no paired kernel
+/* AUTO: the library pairs CTAs (clusters of two SMs, 256 x 256 tiles, tcgen05 cta_group::2) when a
+ * paired kernel exists for the variant, M exceeds 128 and the 256-row tiling does not cost more waves
+ * than it saves per tile; else one CTA per 128 x 256 tile.  SINGLE / PAIR force one of them (PAIR falls back to SINGLE when no paired kernel
  * exists).  Results are bit-identical either way. */
 enum { B200_CTA_GROUP_AUTO = 0, B200_CTA_GROUP_SINGLE = 1, B200_CTA_GROUP_PAIR = 2 };
 

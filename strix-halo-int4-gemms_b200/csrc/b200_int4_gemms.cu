@@ -495,16 +495,21 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
   p.K = k;
   p.tile_cols = swiglu ? NBLK : BN;
   p.tiles_n = (n + p.tile_cols - 1) / p.tile_cols;
-  // CTA pairs: 256-row tiles over two SMs.  Worth it when the paired kernel exists, every pair of SMs
-  // gets at least one tile, and pairing does not pad M by much (an M that is not a multiple of 256
-  // leaves the peer CTA of the last row of tiles with nothing to store).
+  // CTA pairs: 256-row tiles over two SMs.  A pair's K block takes about 0.87 of the time a single CTA needs
+  // for its 128 x 256 tile (a third less operand traffic per SM), so pairs win whenever they do not need
+  // more waves than that: compare waves x time per tile of the two schedules.  An M that is not a multiple
+  // of 256 leaves the peer CTA of the last row of tiles without rows, which the wave count accounts for.
   {
     TcLaunch pl = tl;
     pl.pair = true;
     const bool sc_ok = sc_mode == SCALE_PC || v->subchannel >= BK;
-    const int pair_tiles = ((m + 2 * BM - 1) / (2 * BM)) * p.tiles_n;
+    const long long single_tiles = static_cast<long long>((m + BM - 1) / BM) * p.tiles_n;
+    const long long pair_tiles = static_cast<long long>((m + 2 * BM - 1) / (2 * BM)) * p.tiles_n;
+    const long long single_waves = (single_tiles + dev->sm_count - 1) / dev->sm_count;
+    const int pairs = dev->max_pair_clusters > 0 ? dev->max_pair_clusters : 1;
+    const long long pair_waves = (pair_tiles + pairs - 1) / pairs;
     bool want = v->cta_group == B200_CTA_GROUP_PAIR ||
-                (v->cta_group == B200_CTA_GROUP_AUTO && pair_tiles >= dev->sm_count / 2 && m % (2 * BM) == 0);
+                (v->cta_group == B200_CTA_GROUP_AUTO && m > BM && 87 * pair_waves <= 100 * single_waves);
     if (v->schedule == B200_SCHEDULE_STANDARD && v->cta_group != B200_CTA_GROUP_PAIR) want = false;
     if (want && sc_ok && tc_has(pl)) tl = pl;
   }

@@ -33,25 +33,30 @@ def test_accumulator_headroom_extreme_values(pkg):
     assert got[:, 1::2].unique().tolist() == [64 * k] and got[:, ::2].unique().tolist() == [-56 * k]
 
 
+@pytest.mark.parametrize("cta_group", [0, 1])   # the library's choice (CTA pairs where they exist), and single CTAs
 @pytest.mark.parametrize("dtype", ["int4", "int8"])
 @pytest.mark.parametrize("epilogue", ["none", "relu2", "swiglu"])
 @pytest.mark.parametrize("sub", [0, 32, 64, 128, 256])
-def test_scale_modes_and_epilogues(pkg, dtype, epilogue, sub):
-    check_dense(pkg, m=256, n=384, k=512, dtype=dtype, sub=sub, epilogue=epilogue, path=TCGEN05, seed=sub + 1)
+def test_scale_modes_and_epilogues(pkg, dtype, epilogue, sub, cta_group):
+    check_dense(pkg, m=256, n=384, k=512, dtype=dtype, sub=sub, epilogue=epilogue, path=TCGEN05, seed=sub + 1,
+                cta_group=cta_group)
 
 
 @pytest.mark.parametrize("layout", ["nn", "tn", "nt"])
 @pytest.mark.parametrize("dtype", ["int4", "int8"])
 def test_layouts(pkg, layout, dtype):
-    check_dense(pkg, m=256, n=512, k=512, dtype=dtype, layout=layout, seed=3)
-    check_dense(pkg, m=256, n=512, k=512, dtype=dtype, layout=layout, sub=128, epilogue="relu2", seed=4)
+    for cta_group in (0, 1):
+        check_dense(pkg, m=256, n=512, k=512, dtype=dtype, layout=layout, seed=3, cta_group=cta_group)
+        check_dense(pkg, m=256, n=512, k=512, dtype=dtype, layout=layout, sub=128, epilogue="relu2", seed=4, cta_group=cta_group)
 
 
 @pytest.mark.parametrize("shape", [(1, 16, 32), (200, 272, 160), (129, 48, 96), (17, 1040, 4128), (513, 2064, 32)])
 def test_partial_tiles_on_the_tensor_core_path(pkg, shape):
     m, n, k = shape
     check_dense(pkg, m=m, n=n, k=k, path=TCGEN05)
+    check_dense(pkg, m=m, n=n, k=k, path=TCGEN05, cta_group=1)
     check_dense(pkg, m=m, n=n, k=k, out="f32", path=TCGEN05)
+    check_dense(pkg, m=m, n=n, k=k, out="f32", path=TCGEN05, cta_group=1)
     check_dense(pkg, m=m, n=n, k=k, sub=32, epilogue="swiglu" if n % 32 == 0 else "relu2", path=TCGEN05)
 
 
