@@ -145,6 +145,12 @@ cudaError_t set_smem(Kernel kernel, int bytes) {
   X(false, false, false, SCALE_SC, EPI_NONE, OUT_BF16, false, false)               \
   X(false, false, false, SCALE_SC, EPI_RELU2, OUT_BF16, false, false)              \
   X(false, false, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false)                \
+  /* layout TT: A [Kb, M] with B [N, Kb] */                                  \
+  X(true, true, false, SCALE_PC, EPI_NONE, OUT_BF16, false, false)          \
+  X(true, true, false, SCALE_PC, EPI_NONE, OUT_F32, false, false)           \
+  X(true, true, false, SCALE_SC, EPI_NONE, OUT_BF16, false, false)          \
+  X(false, true, true, SCALE_PC, EPI_NONE, OUT_BF16, false, false)          \
+  X(false, true, false, SCALE_PC, EPI_NONE, OUT_BF16, false, false)         \
   /* CTA pairs (cta_group::2): 256 x 256 output tiles over two SMs */       \
   X(true, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true)           \
   X(true, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, true)          \
@@ -437,7 +443,7 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
   tc_ok = tc_ok && ((a_t ? m : kb) % 16 == 0) && ((b_t ? kb : b_cols) % 16 == 0);
   if (v->path == B200_PATH_SIMT) tc_ok = false;
   if (v->path == B200_PATH_TCGEN05 && !tc_ok)
-    return fail("the tcgen05 kernel needs 16-byte aligned operands, operand pitches that are multiples of 16 bytes, and a layout other than TT");
+    return fail("the tcgen05 kernel needs 16-byte aligned operands, operand pitches that are multiples of 16 bytes, and a kernel instantiated for the variant");
 
   if (!tc_ok) {
     SimtParams sp{};

@@ -42,7 +42,7 @@ def test_scale_modes_and_epilogues(pkg, dtype, epilogue, sub, cta_group):
                 cta_group=cta_group)
 
 
-@pytest.mark.parametrize("layout", ["nn", "tn", "nt"])
+@pytest.mark.parametrize("layout", ["nn", "tn", "nt", "tt"])
 @pytest.mark.parametrize("dtype", ["int4", "int8"])
 def test_layouts(pkg, layout, dtype):
     for cta_group in (0, 1):
@@ -125,6 +125,16 @@ def test_cta_pair_and_single_agree_bit_for_bit(pkg):
         one = abi_dense(pkg, case, cta_group=SINGLE, **kw)
         two = abi_dense(pkg, case, cta_group=PAIR, **kw)
         assert torch.equal(one, two)
+
+
+@pytest.mark.parametrize("dtype", ["int4", "int8"])
+def test_layout_tt_on_the_tensor_core_kernel(pkg, dtype):
+    """A [Kb, M] with B [N, Kb]: both operands in the layout the other one usually has."""
+    check_dense(pkg, m=384, n=512, k=1024, dtype=dtype, layout="tt", path=TCGEN05, seed=31)
+    check_dense(pkg, m=208, n=272, k=160, dtype=dtype, layout="tt", path=TCGEN05, seed=32)
+    if dtype == "int4":
+        check_dense(pkg, m=256, n=256, k=512, dtype=dtype, layout="tt", sub=128, path=TCGEN05, seed=33)
+        check_dense(pkg, m=256, n=256, k=512, dtype=dtype, layout="tt", out="f32", path=TCGEN05, seed=34)
 
 
 def test_cta_pair_falls_back_when_no_paired_kernel_exists(pkg):
