@@ -120,8 +120,9 @@ size_t b200_int4_gemms_dense_workspace_bytes(const b200_gemm_variant* variant, i
  *   lhs_scale  bf16 [m] or [m, scale_cols];  rhs_scale bf16 [groups, n] or [groups, scale_cols, n]
  *   task_*     int64 [num_tasks] row-block tasks as built by calculate_group_info
  *              (reference ragged.py:201-323); block_rows = the tile they were built with (<= 256;
- *              tasks of more than 128 rows run on pairs of SMs and need layout NN and per-channel scales
- *              or K-groups of at least 128 on the tensor-core path)
+ *              tasks of more than 128 rows run on pairs of SMs and need per-channel scales or K-groups of
+ *              at least 128 on the tensor-core path).  The tensor-core path takes a row-major lhs
+ *              (layouts NN and NT); TN / TT run on the CUDA-core kernel
  *   out        [m, n] bf16 or f32; rows outside every task's [actual_start, actual_end) are untouched */
 int b200_int4_gemms_launch_ragged_fwd(const b200_gemm_variant* variant, int device_index,
                                       uintptr_t stream_handle, const void* lhs, const void* rhs,

@@ -578,14 +578,16 @@ int launch_ragged_fwd_impl(
     return fail("scale_cols does not match ceil(K / subchannel)");
 
   // Tasks of more than 128 rows run on CTA pairs: rank 0 takes the first 128 rows of the block, rank 1 the rest.
-  TcLaunch tl{true, a_t, true, false, sc_mode, EPI_NONE, v->out_dtype};
+  // lhs must be row-major (a transposed lhs would put the task's first row, any multiple of align_tile, on
+  // the TMA x axis, which wants multiples of 16 bytes); rhs may be [G, Kb, N] (NN) or [G, N, Kb] (NT)
+  TcLaunch tl{true, a_t, !b_t, false, sc_mode, EPI_NONE, v->out_dtype};
   tl.pair = block_rows > BM;
   const bool pair_ok = !tl.pair || sc_mode == SCALE_PC || v->subchannel >= BK;
-  bool tc_ok = !b_t && !a_t && pair_ok && tc_has(tl) && aligned16(lhs) && aligned16(rhs) && (k_packed % 16 == 0) && (n % 16 == 0);
+  bool tc_ok = !a_t && pair_ok && tc_has(tl) && aligned16(lhs) && aligned16(rhs) && (k_packed % 16 == 0) && (b_t || n % 16 == 0);
   if (v->path == B200_PATH_SIMT) tc_ok = false;
   if (v->path == B200_PATH_TCGEN05 && !tc_ok)
-    return fail("the tcgen05 ragged forward kernel needs layout NN, 16-byte aligned operands, k_packed and n multiples of 16, "
-                "and (for block_rows > 128) per-channel scales or K-groups of at least 128");
+    return fail("the tcgen05 ragged forward kernel needs layout NN or NT, 16-byte aligned operands, k_packed (and for NN n) "
+                "multiples of 16, and (for block_rows > 128) per-channel scales or K-groups of at least 128");
 
   if (!tc_ok) {
     SimtParams sp{};
@@ -619,8 +621,13 @@ int launch_ragged_fwd_impl(
 
   CUtensorMap ta, tb;
   if (int rc = make_map_2d(&ta, lhs, k_packed, m, k_packed, BK / 2, BM, 0, "lhs"); rc != 0) return rc;
-  if (int rc = make_map_2d(&tb, rhs, n, static_cast<uint64_t>(groups) * k_packed, n, NBLK, BK / 2, 0, "rhs"); rc != 0)
-    return rc;
+  if (b_t) {
+    if (int rc = make_map_2d(&tb, rhs, k_packed, static_cast<uint64_t>(groups) * n, k_packed, BK / 2, NBLK, 0, "rhs"); rc != 0)
+      return rc;
+  } else {
+    if (int rc = make_map_2d(&tb, rhs, n, static_cast<uint64_t>(groups) * k_packed, n, NBLK, BK / 2, 0, "rhs"); rc != 0)
+      return rc;
+  }
   GemmParams p{};
   p.mode = MODE_RAGGED_FWD;
   p.M = m;
@@ -637,7 +644,7 @@ int launch_ragged_fwd_impl(
   p.scale_cols = sc_mode == SCALE_SC ? scale_cols : 1;
   p.lds_b = n;
   p.num_groups = groups;
-  p.rows_per_group_b = k_packed;
+  p.rows_per_group_b = b_t ? n : k_packed;  // rows of the stacked rhs map per group
   p.task_group_ids = reinterpret_cast<const long long*>(task_group_ids);
   p.task_block_starts = reinterpret_cast<const long long*>(task_block_starts);
   p.task_actual_starts = reinterpret_cast<const long long*>(task_actual_starts);

@@ -68,6 +68,15 @@ def test_forward_256_row_tasks_on_cta_pairs(pkg, sub, out_dtype):
     np.testing.assert_array_equal(as_f32(out), want)
 
 
+@pytest.mark.parametrize("sub", [0, 128])
+def test_forward_nt_layout_on_the_tensor_core_kernel(pkg, sub):
+    """rhs stored [G, N, K/2] (K-major B): groups stacked along N, column edge inside the last tile."""
+    out, want = _fwd(pkg, [100, 0, 260, 128, 7], 512, 1408, layout="nt", sub=sub, seed=13)
+    np.testing.assert_array_equal(as_f32(out), want)
+    out, want = _fwd(pkg, [300, 40], 256, 200, layout="nt", sub=sub, seed=14, out_dtype=torch.float32)
+    np.testing.assert_array_equal(out.cpu().numpy(), want)
+
+
 def test_forward_widens_tasks_for_large_groups(pkg):
     """Default config: groups averaging >= 256 rows are cut into 256-row tasks; the result is the same
     as with 128-row tasks pinned."""
