@@ -522,7 +522,9 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
   const int tile_rows = tl.pair ? 2 * BM : BM;
   p.tiles_m = (m + tile_rows - 1) / tile_rows;
   p.num_tiles = p.tiles_m * p.tiles_n;
-  p.group_m = v->group_m > 0 ? v->group_m : 8;
+  // raster width (row tiles walked before the next column tile), measured on this part: 16 for the 256-row
+  // tiles of CTA pairs, 32 for single-CTA int8 tiles, 8 for single-CTA int4 tiles
+  p.group_m = v->group_m > 0 ? v->group_m : (tl.pair ? 16 : (int4 ? 8 : 32));
   p.gate_col_offset = swiglu ? n : NBLK;
   p.ldc = n;
   p.subchannel = sc_mode == SCALE_SC ? v->subchannel : 0;

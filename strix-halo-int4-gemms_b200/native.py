@@ -409,7 +409,7 @@ def launch_generated_kernel(
         out_dtype=OUT_F32 if want_dtype is torch.float32 else OUT_BF16,
         split_k=kernel.tile.split_k,
         path=path,
-        group_m=kernel.tile.group_size_m,
+        group_m=0,  # the library picks the raster width per kernel form; the registry's gm label is descriptive
         schedule=kernel.schedule,
     )
     launch_dense(
