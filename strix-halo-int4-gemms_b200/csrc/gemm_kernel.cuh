@@ -203,16 +203,16 @@ struct KernelTraits {
   static constexpr bool kShortK = kMaskK && kInt4 && !k2Cta;
   // Kernels with eight epilogue warps re-balance registers between roles with setmaxnreg, which works on
   // warpgroups (4 consecutive warps): warps 0..3 = TMA, MMA and two idle warps, 4..11 = epilogue, then unpack
-  // (4 warps next to the subchannel epilogue, whose running sums need 184 registers; 8 warps otherwise).
+  // (4 warps next to the subchannel epilogue, whose running sums need 200 registers; 8 warps otherwise).
   static constexpr bool kRegBalance = (kScale == SCALE_SC) || kShortK;
   static constexpr int kUnpackWarps = kInt4 ? ((kScale == SCALE_SC) ? 4 : B200_UNPACK_WARPS) : 0;
   static constexpr int kEpiWarps = kRegBalance ? 8 : 4;
   static constexpr int kEpiWarp0 = kRegBalance ? 4 : 2;
   static constexpr int kUnpackWarp0 = kEpiWarp0 + kEpiWarps;
   static constexpr int kThreads = (kUnpackWarp0 + kUnpackWarps) * 32;
-  static constexpr int kRegsLight = 40;    // TMA / MMA warpgroup
-  static constexpr int kRegsUnpack = (kScale == SCALE_SC) ? 96 : 80;
-  static constexpr int kRegsEpilogue = (kScale == SCALE_SC) ? 184 : 136;
+  static constexpr int kRegsLight = (kScale == SCALE_SC) ? 32 : 40;    // TMA / MMA warpgroup (subchannel: every register counts)
+  static constexpr int kRegsUnpack = 80;
+  static constexpr int kRegsEpilogue = (kScale == SCALE_SC) ? 200 : 136;  // subchannel: 128 running sums + room to interleave
   // The most registers per thread the kernel can be launched with (what the compiler may use before the
   // re-balance).  setmaxnreg.dec must not name more than a warp currently has, setmaxnreg.inc not less: a
   // role whose target is at or above this cap raises its count, one below it lowers it, and the host checks
