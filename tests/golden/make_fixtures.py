@@ -2,7 +2,7 @@
 
 Run once, in a container where the reference checkout is mounted:
 
-    python tests/golden/make_fixtures.py /root/reference
+    python tests/golden/make_fixtures.py <path of the reference checkout>
 
 It imports ``amd_strix_halo_kernels`` from ``<reference>/src`` and the grouped-dot reference
 functions from ``<reference>/tests/test_ragged_dot.py`` (the package itself has no reference mode
@@ -228,4 +228,6 @@ def ragged_tests_kernel_args(ref, a_q, b_q, kernel):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_fixtures.py <path of the reference checkout>")
+    main(sys.argv[1])
