@@ -171,7 +171,10 @@ cudaError_t set_smem(Kernel kernel, int bytes) {
   X(false, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, true)         \
   X(false, false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false, true)        \
   X(true, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, true)          \
-  X(true, true, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true)
+  X(true, true, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true)            \
+  /* grouped backward on CTA pairs */                                        \
+  X(true, true, true, SCALE_PC, EPI_NONE, OUT_F32, true, true)              \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, true, true)
 
 int ensure_device(int device_index, DeviceState** out) {
   if (device_index < 0 || device_index >= kMaxDevices) return fail("device_index out of range");
@@ -794,6 +797,13 @@ int launch_ragged_bwd_impl(const b200_gemm_variant* v, int device_index, uintptr
 
   TcLaunch tl{true, a_t, true, true, sc_mode, EPI_NONE, OUT_F32};
   bool tc_ok = !b_t && tc_has(tl) && aligned16(lhs) && aligned16(rhs) && ((a_t ? m : k_packed) % 16 == 0) && (n % 16 == 0);
+  // CTA pairs (256-row tiles) where a paired kernel exists and the rows fill them: a third less operand
+  // traffic through each SM's shared memory, which this kernel shares with its fp32 output staging
+  if (tc_ok && dev->max_pair_clusters > 0 && m % (2 * BM) == 0 && v->cta_group != B200_CTA_GROUP_SINGLE) {
+    TcLaunch pl = tl;
+    pl.pair = true;
+    if (tc_has(pl)) tl = pl;
+  }
   if (v->path == B200_PATH_SIMT) tc_ok = false;
   if (v->path == B200_PATH_TCGEN05 && !tc_ok)
     return fail("the tcgen05 ragged backward kernel needs rhs stored [G, K, N], 16-byte aligned operands and operand pitches that are multiples of 16 bytes");
@@ -843,7 +853,7 @@ int launch_ragged_bwd_impl(const b200_gemm_variant* v, int device_index, uintptr
   p.N = n;
   p.K = k;
   p.tile_cols = BN;
-  p.tiles_m = (m + BM - 1) / BM;
+  p.tiles_m = (m + (tl.pair ? 2 * BM : BM) - 1) / (tl.pair ? 2 * BM : BM);
   p.tiles_n = (n + BN - 1) / BN;
   p.num_tiles = groups * p.tiles_m * p.tiles_n;
   p.group_m = 1;
@@ -862,7 +872,8 @@ int launch_ragged_bwd_impl(const b200_gemm_variant* v, int device_index, uintptr
   p.status = dev->status_dev;
   CUtensorMap tc;
   if (int rc = make_output_map(&tc, out, OUT_F32, static_cast<uint64_t>(groups) * m, n, &p.tma_store); rc != 0) return rc;
-  const int grid = p.num_tiles < dev->sm_count ? p.num_tiles : dev->sm_count;
+  const int units = tl.pair ? dev->max_pair_clusters : dev->sm_count;
+  const int grid = (p.num_tiles < units ? p.num_tiles : units) * (tl.pair ? 2 : 1);
   int rc = launch_tc(tl, ta, tb, tc, p, grid, stream);
   if (rc < 0) return fail("internal: no tcgen05 instantiation for this variant");
   return rc;

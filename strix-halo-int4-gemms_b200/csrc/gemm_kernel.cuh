@@ -200,7 +200,7 @@ struct KernelTraits {
   // K-masked kernels serve the grouped backward pass: short reductions (a group's tokens) and large fp32
   // tiles.  Their epilogue is the long pole, so it gets eight warps (two per TMEM lane quarter, half of the
   // columns each) and one of the operand stages as output staging.
-  static constexpr bool kShortK = kMaskK && kInt4 && !k2Cta;
+  static constexpr bool kShortK = kMaskK && kInt4;
   // Kernels with eight epilogue warps re-balance registers between roles with setmaxnreg, which works on
   // warpgroups (4 consecutive warps): warps 0..3 = TMA, MMA and two idle warps, 4..11 = epilogue, then unpack
   // (4 warps next to the subchannel epilogue, whose running sums need 200 registers; 8 warps otherwise).
@@ -236,10 +236,11 @@ struct KernelTraits {
   // A CTA of a pair holds one 128-wide block of B (the MMA reads the other one from the peer), so
   // its stages are a third smaller and more of them fit.
   static constexpr int kBBlocks = k2Cta ? 1 : 2;
-  static constexpr int kStages = kShortK ? 2
+  static constexpr int kStages = kShortK ? (k2Cta ? 3 : 2)
                                  : kInt4 ? (k2Cta ? B200_PAIR_INT4_STAGES : B200_INT4_STAGES)
                                          : (k2Cta ? B200_PAIR_INT8_STAGES : B200_INT8_STAGES);  // int8 UMMA stages
-  static constexpr int kPkStages = kInt4 ? (k2Cta ? B200_PAIR_INT4_PK_STAGES : B200_INT4_PK_STAGES) : 0; // packed staging stages
+  static constexpr int kPkStages =
+      kInt4 ? (k2Cta ? (kShortK ? 3 : B200_PAIR_INT4_PK_STAGES) : B200_INT4_PK_STAGES) : 0; // packed staging stages
   static constexpr int kA8Bytes = BM * BK;                  // 16 KB
   static constexpr int kB8Bytes = kBBlocks * NBLK * BK;     // 32 KB (pair: 16 KB)
   static constexpr int kStageBytes = kA8Bytes + kB8Bytes;

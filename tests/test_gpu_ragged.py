@@ -148,6 +148,17 @@ def _bwd(pkg, sizes, m, n, *, layout="tn", sub=0, seed=0, k_capacity=None, confi
     return out, want
 
 
+@pytest.mark.parametrize("layout", ["tn", "nn"])
+def test_backward_on_cta_pairs_and_on_single_ctas(pkg, layout, monkeypatch):
+    """M = 512 is two 256-row pair tiles per group; the per-channel backward kernels exist in both forms and
+    the binding's environment switch pins either: both must reproduce the oracle."""
+    sizes = [17, 0, 300, 128, 255, 512, 1]
+    for forced in ("2", "1"):
+        monkeypatch.setenv("B200_INT4_GEMMS_CTA_GROUP", forced)
+        out, want = _bwd(pkg, sizes, 512, 1408, layout=layout, k_capacity=512, seed=41)
+        np.testing.assert_array_equal(out.cpu().numpy(), want, err_msg=f"cta_group {forced}")
+
+
 @pytest.mark.parametrize("layout", ["tn", "nn", "nt", "tt"])
 @pytest.mark.parametrize("sub", [0, 32, 128])
 def test_backward_matches_oracle(pkg, layout, sub):
