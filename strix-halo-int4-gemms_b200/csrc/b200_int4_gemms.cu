@@ -174,7 +174,9 @@ cudaError_t set_smem(Kernel kernel, int bytes) {
   X(true, true, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true)            \
   /* grouped backward on CTA pairs */                                        \
   X(true, true, true, SCALE_PC, EPI_NONE, OUT_F32, true, true)              \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, true, true)
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, true, true)             \
+  X(true, true, true, SCALE_SC, EPI_NONE, OUT_F32, true, true)              \
+  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, true, true)
 
 int ensure_device(int device_index, DeviceState** out) {
   if (device_index < 0 || device_index >= kMaxDevices) return fail("device_index out of range");
@@ -802,7 +804,8 @@ int launch_ragged_bwd_impl(const b200_gemm_variant* v, int device_index, uintptr
   if (tc_ok && dev->max_pair_clusters > 0 && m % (2 * BM) == 0 && v->cta_group != B200_CTA_GROUP_SINGLE) {
     TcLaunch pl = tl;
     pl.pair = true;
-    if (tc_has(pl)) tl = pl;
+    const bool sc_ok = sc_mode == SCALE_PC || v->subchannel >= BK;  // paired kernels hand accumulators over per K block
+    if (sc_ok && tc_has(pl)) tl = pl;
   }
   if (v->path == B200_PATH_SIMT) tc_ok = false;
   if (v->path == B200_PATH_TCGEN05 && !tc_ok)
