@@ -1,22 +1,32 @@
 #!/usr/bin/env python
 """Benchmark of the quantized-GEMM hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5fwd|c5bwd|c5bwd_flat] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|c5fwd|c5bwd|c5bwd_flat] [--impl ours|reference]
 
-Prints ONE JSON line (rank 0).  Default workload is the headline one: int4 x int4 per-channel GEMM at
-M = N = K = 4096 (metric: TOPS = 2*M*N*K / t).  One *step* is one pass over a batch of ``--batch``
-independent problems of that shape, each with its own operands and output, so that the operand bytes
-touched between two uses of the same buffer exceed the 126 MB L2 (stated in ``config.l2``).
+Prints ONE JSON line (rank 0).  The headline workload (default c2) is the int4 x int4 per-channel GEMM at
+M = N = K = 4096 (metric: TOPS = 2*M*N*K / t).  One *pass* runs ``problems_per_step`` independent problems of
+that shape, each with its own operands and output, so that the bytes touched between two uses of a buffer exceed
+the 126 MB L2; one *step* is ``passes_per_step`` passes, chosen so that the K timed steps last at least a second
+(a sustained figure, with the SM clock sampled throughout); the short first-touch figure is kept as ``burst``.
 
-Multi-GPU (launched by torchrun, one rank per GPU): every rank runs the same per-GPU problem on its own
-shard - dense workloads are column-parallel along N (global N = N_per_gpu * world), grouped workloads are
-expert-parallel - with no collective on the data path; time is the max over ranks; ``scaling`` is weak.
+The same line carries ``workloads``: the other BASELINE configurations (c1 as a latency, c3, c4, c5 forward and
+backward), each measured the same way in the same run, with its own roofline fraction, clocks and end-to-end
+figure.
 
-Timing: CUDA events on the launching stream around exactly K steps, barrier + synchronize on both sides,
-SM clock and throttle reasons polled through NVML during the timed region.
+Multi-GPU (launched by torchrun, one rank per GPU, no collective on the data path, time = max over ranks):
+  * the headline is weak scaling: dense workloads are column-parallel along N with a global N of N_per_gpu * world,
+    every rank taking its columns of the global B through ``distributed.shard_dense_rhs``; grouped workloads are
+    expert-parallel with 64 * world groups assigned by ``distributed.assign_groups``;
+  * ``strong`` holds the BASELINE problems themselves split over the ranks: c2 and c4 column-parallel, c5 forward
+    and backward expert-parallel over the actual 64 groups (with the load imbalance of the assignment), and the
+    NCCL all-gather of the output timed separately.
 
-``e2e`` is the same metric through the public Python API with HOST operands: every step copies the
-operands from pinned host memory, runs the op, and copies the result back, all inside the timed region.
+Timing: CUDA events on the launching stream around exactly K steps, barrier + synchronize on both sides, SM clock
+and throttle reasons polled through NVML during the timed region.
+
+``e2e`` is the same metric through the public Python API, called with default arguments, with HOST operands: every
+step copies the operands from pinned host memory, runs the op, and copies the result back, all inside the timed
+region.
 
 ``--impl reference`` times the reference's own CPU path for the workload (the oracle port of its PyTorch
 int32-matmul math; the reference package is Python and is not present on the GPU box) on the host cores.
@@ -25,6 +35,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import sys
 import threading
@@ -35,14 +46,19 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 NOMINAL_INT8_TOPS = 4500.0   # dense int8 tensor peak of a B200 (public figure)
+NOMINAL_HBM_GBS = 8000.0     # public HBM3e figure the brief quotes
 L2_BYTES = 126 * 1024 * 1024
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+SUSTAINED_SECONDS = 1.05     # the timed steps of every workload last at least this long
 
 
 # ----------------------------------------------------------------------------------------------
 # workloads
 # ----------------------------------------------------------------------------------------------
 WORKLOADS = {
+    "c1": dict(kind="dense", m=128, n=1024, k=64, dtype="int4", sub=0, epilogue="none",
+               name="quick-start int4 x int4 per-channel GEMM, M=128 N=1024 K=64 (BASELINE config 1)",
+               metric="W4A4 GEMM latency @128x1024x64"),
     "c2": dict(kind="dense", m=4096, n=4096, k=4096, dtype="int4", sub=0, epilogue="none",
                name="int4 x int4 per-channel GEMM, M=N=K=4096, bf16 out (BASELINE config 2)",
                metric="W4A4 GEMM TOPS @4096^3"),
@@ -63,6 +79,8 @@ WORKLOADS = {
                        name="ragged_dot_int4_bwd_flat, 64 groups, 32768 tokens back to back, out [64,2048,1408] fp32 (BASELINE config 5, flat dy)",
                        metric="ragged_dot_int4 bwd TOPS"),
 }
+SUB_WORKLOADS = ("c1", "c3", "c4", "c5fwd", "c5bwd")      # reported beside the headline at one GPU
+STRONG_WORKLOADS = ("c2", "c4", "c5fwd", "c5bwd")         # the given problems split over the ranks
 
 
 def config5_group_sizes(torch):
@@ -74,34 +92,47 @@ def config5_group_sizes(torch):
     return torch.bincount(draws, minlength=64)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the workload's GEMM kernel, from one `ncu --set full`
-# capture of the same command at 1 GPU (summaries under profiles/).  Smaller than the algorithmic bytes where the
-# result is still in the 126 MB L2 when the kernel ends.
-NCU_DRAM_TRAFFIC_BYTES = {
-    "c2": 17.08e6, "c3": 358.7e6, "c4": 147.2e6, "c5fwd": 175.2e6, "c5bwd": 749.2e6, "c5bwd_flat": 742.7e6,
-}
-VENDOR_INT8_GEMM_TOPS = 2973.1  # torch._int_mm (cuBLASLt) int8 8192^3 on this pool's B200: `bench.py --probe-int8-peak`
+def load_measured_traffic() -> dict:
+    """DRAM read + write bytes of one launch per workload, from the ncu captures summarised in
+    ``profiles/dram_traffic.txt`` (lines ``<workload> <bytes> <capture>``).  Absent file or workload: no figure."""
+    found = {}
+    path = ROOT / "profiles" / "dram_traffic.txt"
+    if path.exists():
+        for line in path.read_text().splitlines():
+            parts = line.split(None, 2)
+            if len(parts) >= 2 and not line.startswith("#"):
+                try:
+                    found[parts[0]] = {"bytes": float(parts[1]), "source": parts[2] if len(parts) > 2 else ""}
+                except ValueError:
+                    pass
+    return found
 
 
-def workload_ops(w, sizes=None) -> float:
-    if w["kind"] == "dense":
-        cols = 2 * w["n"] if w["epilogue"] == "swiglu" else w["n"]
-        return 2.0 * w["m"] * cols * w["k"]
+def dense_ops(w, n=None) -> float:
+    n = w["n"] if n is None else n
+    cols = 2 * n if w["epilogue"] == "swiglu" else n
+    return 2.0 * w["m"] * cols * w["k"]
+
+
+def dense_bytes(w, n=None) -> float:
+    n = w["n"] if n is None else n
+    cols = 2 * n if w["epilogue"] == "swiglu" else n
+    kb = w["k"] // 2 if w["dtype"] == "int4" else w["k"]
+    groups = max(1, w["k"] // w["sub"]) if w["sub"] else 1
+    return w["m"] * kb + kb * cols + 2 * groups * (w["m"] + cols) + 2 * w["m"] * n
+
+
+def ragged_ops(w, rows) -> float:
     if w["kind"] == "ragged_fwd":
-        return 2.0 * w["rows"] * w["k"] * w["n"]
-    return 2.0 * w["m"] * w["n"] * w["rows"]  # backward: K = sum(group_sizes)
+        return 2.0 * rows * w["k"] * w["n"]
+    return 2.0 * w["m"] * w["n"] * rows  # backward: K = sum(group_sizes)
 
 
-def workload_bytes(w) -> float:
+def ragged_bytes(w, rows, groups) -> float:
     """Algorithmic HBM bytes of one problem: every operand read once, the result written once."""
-    if w["kind"] == "dense":
-        cols = 2 * w["n"] if w["epilogue"] == "swiglu" else w["n"]
-        kb = w["k"] // 2 if w["dtype"] == "int4" else w["k"]
-        groups = max(1, w["k"] // w["sub"]) if w["sub"] else 1
-        return w["m"] * kb + kb * cols + 2 * groups * (w["m"] + cols) + 2 * w["m"] * w["n"]
     if w["kind"] == "ragged_fwd":
-        return w["rows"] * w["k"] // 2 + w["groups"] * (w["k"] // 2) * w["n"] + 2 * (w["rows"] + w["groups"] * w["n"]) + 2 * w["rows"] * w["n"]
-    return w["rows"] // 2 * (w["m"] + w["n"]) + 2 * w["groups"] * (w["m"] + w["n"]) + 4 * w["groups"] * w["m"] * w["n"]
+        return rows * w["k"] // 2 + groups * (w["k"] // 2) * w["n"] + 2 * (rows + groups * w["n"]) + 2 * rows * w["n"]
+    return rows // 2 * (w["m"] + w["n"]) + 2 * groups * (w["m"] + w["n"]) + 4 * groups * w["m"] * w["n"]
 
 
 # ----------------------------------------------------------------------------------------------
@@ -115,6 +146,7 @@ class ClockSampler:
 
     def __init__(self, device_index: int) -> None:
         self.samples: list[int] = []
+        self.power_w: list[float] = []
         self.reason_bits = 0
         self.max_mhz = None
         self._stop = threading.Event()
@@ -135,6 +167,7 @@ class ClockSampler:
             try:
                 self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM)))
                 self.reason_bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._handle))
+                self.power_w.append(nv.nvmlDeviceGetPowerUsage(self._handle) / 1000.0)
             except Exception:
                 pass
             time.sleep(0.002)
@@ -155,7 +188,11 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
         ordered = sorted(self.samples)
         reasons = [name for bit, name in self.REASONS.items() if self.reason_bits & bit]
-        return {"sm_mhz": ordered[len(ordered) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(reasons), "samples": len(ordered)}
+        out = {"sm_mhz": ordered[len(ordered) // 2], "sm_mhz_min": ordered[0], "sm_max_mhz": self.max_mhz,
+               "reasons": sorted(reasons), "samples": len(ordered)}
+        if self.power_w:
+            out["power_w_max"] = round(max(self.power_w), 1)
+        return out
 
 
 def visible_device_index(local_rank: int) -> int:
@@ -179,69 +216,154 @@ def load_peaks() -> tuple[dict, str]:
     return dict(FALLBACK_PEAKS), "fallback"
 
 
+def host_numa_nodes() -> list[int]:
+    """NUMA nodes of the CPUs this process may run on (where its pinned host buffers are first touched)."""
+    try:
+        allowed = os.sched_getaffinity(0)
+    except AttributeError:
+        return []
+    nodes = []
+    base = Path("/sys/devices/system/node")
+    if not base.exists():
+        return []
+    for node in sorted(base.glob("node[0-9]*")):
+        cpus = set()
+        try:
+            for part in (node / "cpulist").read_text().strip().split(","):
+                if "-" in part:
+                    lo, hi = part.split("-")
+                    cpus.update(range(int(lo), int(hi) + 1))
+                elif part:
+                    cpus.add(int(part))
+        except Exception:
+            continue
+        if cpus & allowed:
+            nodes.append(int(node.name[4:]))
+    return nodes
+
+
 # ----------------------------------------------------------------------------------------------
 # our arm
 # ----------------------------------------------------------------------------------------------
-def build_problem_set(torch, pkg, w, batch: int, seed: int, device):
-    """``batch`` independent problems on ``device`` (operands generated there as random codes)."""
-    from strix_halo_int4_gemms_b200 import native
+class Ctx:
+    """What every measurement needs: modules, rank layout, device."""
 
-    gen = torch.Generator(device=device).manual_seed(seed)
-    cpu_gen = torch.Generator().manual_seed(seed)
+    def __init__(self, torch, dist, pkg, native, shard, rank, local_rank, world):
+        self.torch, self.dist, self.pkg, self.native, self.shard = torch, dist, pkg, native, shard
+        self.rank, self.local_rank, self.world = rank, local_rank, world
+        self.device = torch.device("cuda", local_rank)
 
-    def scales(shape, mult=0.05):
-        return ((torch.rand(shape, generator=cpu_gen) + 0.5) * mult).to(torch.bfloat16).to(device)
+    def max_over_ranks(self, value: float) -> float:
+        if self.world == 1:
+            return value
+        t = self.torch.tensor([value], device="cuda", dtype=self.torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
 
-    def codes(shape, int4=True):
-        if int4:
-            return torch.randint(0, 256, shape, generator=gen, device=device, dtype=torch.uint8)
-        return torch.randint(-127, 128, shape, generator=gen, device=device, dtype=torch.int8)
+    def sum_over_ranks(self, value: float) -> float:
+        if self.world == 1:
+            return value
+        t = self.torch.tensor([value], device="cuda", dtype=self.torch.float64)
+        self.dist.all_reduce(t)
+        return float(t.item())
 
+    def gather(self, value) -> list:
+        if self.world == 1:
+            return [value]
+        out = [None] * self.world
+        self.dist.all_gather_object(out, value)
+        return out
+
+
+def _scales(torch, shape, gen, device, mult=0.05):
+    return ((torch.rand(shape, generator=gen) + 0.5) * mult).to(torch.bfloat16).to(device)
+
+
+def _codes(torch, shape, gen, device, int4=True):
+    if int4:
+        return torch.randint(0, 256, shape, generator=gen, device=device, dtype=torch.uint8)
+    return torch.randint(-127, 128, shape, generator=gen, device=device, dtype=torch.int8)
+
+
+def build_dense_problems(ctx: Ctx, w, batch: int, *, seed: int, split: str | None):
+    """``batch`` dense problems on this rank.  ``split`` None: the workload as given; "weak": this rank's columns of
+    a global problem with N * world columns; "strong": this rank's columns of the given problem.  A sharded problem
+    is generated whole (same seed on every rank) and cut by ``distributed.shard_dense_rhs``."""
+    torch, pkg = ctx.torch, ctx.pkg
+    int4 = w["dtype"] == "int4"
+    swiglu = w["epilogue"] == "swiglu"
+    kb = w["k"] // 2 if int4 else w["k"]
+    mult = 0.05 if int4 else 0.01
+    groups = w["k"] // w["sub"] if w["sub"] else 0
+    n_global = w["n"] * ctx.world if split == "weak" else w["n"]
+    cols_global = 2 * n_global if swiglu else n_global
+    shared = torch.Generator(device=ctx.device).manual_seed(seed)          # same stream on every rank
+    shared_cpu = torch.Generator().manual_seed(seed)
     problems = []
     for _ in range(batch):
-        if w["kind"] == "dense":
-            int4 = w["dtype"] == "int4"
-            cols = 2 * w["n"] if w["epilogue"] == "swiglu" else w["n"]
-            kb = w["k"] // 2 if int4 else w["k"]
-            mult = 0.05 if int4 else 0.01
-            groups = w["k"] // w["sub"] if w["sub"] else 0
-            problems.append(dict(
-                a=codes((w["m"], kb), int4), b=codes((kb, cols), int4),
-                a_scale=scales((w["m"], groups) if groups else (w["m"],), mult),
-                b_scale=scales((groups, cols) if groups else (cols,), mult),
-                out=torch.empty((w["m"], w["n"]), device=device, dtype=torch.bfloat16),
-            ))
-        elif w["kind"] == "ragged_fwd":
-            sizes = w["sizes"]
-            problems.append(dict(
-                lhs=codes((int(sizes.sum()), w["k"] // 2)), rhs=codes((len(sizes), w["k"] // 2, w["n"])),
-                a_scale=scales((int(sizes.sum()),)), b_scale=scales((len(sizes), w["n"])),
-                group_sizes=sizes.to(device), out=torch.empty((int(sizes.sum()), w["n"]), device=device, dtype=torch.bfloat16),
-            ))
-        elif w.get("flat"):
-            sizes = w["sizes"]
-            pairs = (int(sizes.sum()) + 1) // 2
-            problems.append(dict(
-                lhs=codes((pairs, w["m"])), rhs=codes((pairs, w["n"])),
-                a_scale=scales((len(sizes), w["m"])), b_scale=scales((len(sizes), w["n"])),
-                group_sizes=sizes.to(device), out=torch.empty((len(sizes), w["m"], w["n"]), device=device, dtype=torch.float32),
-            ))
-        else:
-            sizes = w["sizes"]
-            cap = int(sizes.max()) if len(sizes) else 2
-            cap = max(32, cap + (-cap) % 32)
-            problems.append(dict(
-                lhs=codes((len(sizes), cap // 2, w["m"])), rhs=codes((len(sizes), cap // 2, w["n"])),
-                a_scale=scales((len(sizes), w["m"])), b_scale=scales((len(sizes), w["n"])),
-                group_sizes=sizes.to(device), out=torch.empty((len(sizes), w["m"], w["n"]), device=device, dtype=torch.float32),
-            ))
+        a = _codes(torch, (w["m"], kb), shared, ctx.device, int4)
+        a_scale = _scales(torch, (w["m"], groups) if groups else (w["m"],), shared_cpu, ctx.device, mult)
+        b = _codes(torch, (kb, cols_global), shared, ctx.device, int4)
+        b_scale = _scales(torch, (groups, cols_global) if groups else (cols_global,), shared_cpu, ctx.device, mult)
+        columns = (0, n_global)
+        if split is not None and ctx.world > 1:
+            b, b_scale, columns = ctx.shard.shard_dense_rhs(b, b_scale, layout=pkg.GemmLayout.NN, world_size=ctx.world,
+                                                            rank=ctx.rank, swiglu=swiglu)
+        n_local = columns[1] - columns[0]
+        problems.append(dict(a=a, b=b, a_scale=a_scale, b_scale=b_scale, n=n_local, columns=columns,
+                             out=torch.empty((w["m"], n_local), device=ctx.device, dtype=torch.bfloat16)))
     return problems
 
 
-def make_runner(torch, pkg, w, problems):
-    """A zero-argument callable that launches one step (all problems) with as little host work as possible."""
-    from strix_halo_int4_gemms_b200 import native
-    from strix_halo_int4_gemms_b200.ragged import RaggedBwdDotConfig, RaggedDotConfig
+def build_ragged_problems(ctx: Ctx, w, batch: int, *, seed: int, sizes, owned):
+    """``batch`` grouped problems holding the groups ``owned`` (indices into ``sizes``) of a global problem that is
+    generated whole with the same seed on every rank and cut by ``distributed.shard_ragged_fwd`` / ``_bwd``."""
+    torch, pkg = ctx.torch, ctx.pkg
+    shared = torch.Generator(device=ctx.device).manual_seed(seed)
+    shared_cpu = torch.Generator().manual_seed(seed)
+    total, groups = int(sizes.sum()), len(sizes)
+    whole = len(owned) == groups
+    problems = []
+    for _ in range(batch):
+        if w["kind"] == "ragged_fwd":
+            lhs = _codes(torch, (total, w["k"] // 2), shared, ctx.device)
+            rhs = _codes(torch, (groups, w["k"] // 2, w["n"]), shared, ctx.device)
+            a_scale = _scales(torch, (total,), shared_cpu, ctx.device)
+            b_scale = _scales(torch, (groups, w["n"]), shared_cpu, ctx.device)
+            if whole:
+                local = dict(lhs=lhs, rhs=rhs, a_scale=a_scale, b_scale=b_scale, group_sizes=sizes.to(ctx.device), row_index=None)
+            else:
+                part = ctx.shard.shard_ragged_fwd(lhs, rhs, a_scale, b_scale, sizes, owned)
+                local = dict(lhs=part.lhs, rhs=part.rhs, a_scale=part.a_scale, b_scale=part.b_scale,
+                             group_sizes=part.group_sizes.to(ctx.device), row_index=part.row_index)
+            local["out"] = torch.empty((local["lhs"].shape[0], w["n"]), device=ctx.device, dtype=torch.bfloat16)
+        elif w.get("flat"):
+            mine = sizes[list(owned)]
+            pairs = (int(mine.sum()) + 1) // 2
+            local = dict(lhs=_codes(torch, (pairs, w["m"]), shared, ctx.device), rhs=_codes(torch, (pairs, w["n"]), shared, ctx.device),
+                         a_scale=_scales(torch, (len(mine), w["m"]), shared_cpu, ctx.device),
+                         b_scale=_scales(torch, (len(mine), w["n"]), shared_cpu, ctx.device), group_sizes=mine.to(ctx.device))
+            local["out"] = torch.empty((len(mine), w["m"], w["n"]), device=ctx.device, dtype=torch.float32)
+        else:
+            cap = int(sizes.max()) if groups else 2
+            cap = max(32, cap + (-cap) % 32)
+            lhs = _codes(torch, (groups, cap // 2, w["m"]), shared, ctx.device)
+            rhs = _codes(torch, (groups, cap // 2, w["n"]), shared, ctx.device)
+            a_scale = _scales(torch, (groups, w["m"]), shared_cpu, ctx.device)
+            b_scale = _scales(torch, (groups, w["n"]), shared_cpu, ctx.device)
+            gs = sizes.to(ctx.device)
+            if not whole:
+                lhs, rhs, a_scale, b_scale, gs = ctx.shard.shard_ragged_bwd(lhs, rhs, a_scale, b_scale, gs, owned)
+            local = dict(lhs=lhs, rhs=rhs, a_scale=a_scale, b_scale=b_scale, group_sizes=gs)
+            local["out"] = torch.empty((len(owned), w["m"], w["n"]), device=ctx.device, dtype=torch.float32)
+        problems.append(local)
+    return problems
+
+
+def make_pass(ctx: Ctx, w, problems):
+    """``(callable, launches)``: one pass over all problems through the pointer-level binding of the C ABI."""
+    torch, pkg, native = ctx.torch, ctx.pkg, ctx.native
+    from strix_halo_int4_gemms_b200.ragged import PAIR_MIN_MEAN_GROUP_ROWS, PAIR_TASK_ROWS, RaggedBwdDotConfig, RaggedDotConfig
 
     device_index = torch.cuda.current_device()
     pc = pkg.ScaleSpec(pkg.ScaleMode.PER_CHANNEL)
@@ -250,61 +372,78 @@ def make_runner(torch, pkg, w, problems):
         variant = native.make_variant(dtype=pkg.OperandDType(w["dtype"]), layout=pkg.GemmLayout.NN, scale=scale,
                                       epilogue=pkg.Epilogue(w["epilogue"]), out_dtype=native.OUT_BF16)
         args = [dict(a_ptr=p["a"].data_ptr(), b_ptr=p["b"].data_ptr(), a_scale_ptr=p["a_scale"].data_ptr(),
-                     b_scale_ptr=p["b_scale"].data_ptr(), c_ptr=p["out"].data_ptr()) for p in problems]
+                     b_scale_ptr=p["b_scale"].data_ptr(), c_ptr=p["out"].data_ptr(), n=p["n"]) for p in problems]
 
-        def step():
+        def run():
             for ptrs in args:
                 # the stream is looked up per call: under CUDA-graph capture the current stream is the capturing one
                 native.launch_dense(variant, device_index=device_index, stream_handle=torch.cuda.current_stream().cuda_stream,
-                                    m=w["m"], n=w["n"], k=w["k"], **ptrs)
-        return step, len(problems)
+                                    m=w["m"], k=w["k"], **ptrs)
+        return run, len(problems)
     if w["kind"] == "ragged_fwd":
         # the task height ragged_dot_int4 itself picks for groups this large: 256-row tasks on pairs of SMs
-        from strix_halo_int4_gemms_b200.ragged import PAIR_MIN_MEAN_GROUP_ROWS, PAIR_TASK_ROWS
         rows, groups = problems[0]["lhs"].shape[0], len(problems[0]["group_sizes"])
-        cfg = RaggedDotConfig(block_m=PAIR_TASK_ROWS if rows >= PAIR_MIN_MEAN_GROUP_ROWS * groups else 128)
+        cfg = RaggedDotConfig(block_m=PAIR_TASK_ROWS if rows >= PAIR_MIN_MEAN_GROUP_ROWS * max(groups, 1) else 128)
         infos = [pkg.calculate_group_info(p["group_sizes"], cfg.block_m, align_tile=cfg.align_tile) for p in problems]
 
-        def step():
+        def run():
             for p, info in zip(problems, infos):
                 native.launch_ragged_fwd_kernel(p["lhs"], p["rhs"], group_info=info, a_scale=p["a_scale"], b_scale=p["b_scale"], out=p["out"],
                                                 scale=pc, config=cfg, layout=pkg.GemmLayout.NN, rows=p["lhs"].shape[0], cols=w["n"],
                                                 k_packed=w["k"] // 2, scale_cols=1)
-        return step, len(problems)
+        return run, len(problems)
     cfg = RaggedBwdDotConfig()
     if w.get("flat"):
         tokens = [int(p["group_sizes"].sum()) for p in problems]
 
-        def step():
+        def run():
             for p, t in zip(problems, tokens):
                 native.launch_ragged_bwd_flat_kernel(p["lhs"], p["rhs"], p["group_sizes"], a_scale=p["a_scale"], b_scale=p["b_scale"],
                                                      out=p["out"], tokens=t)
-        return step, 2 * len(problems)  # the group-start scan + the GEMM kernel per problem
+        return run, 2 * len(problems)  # the group-start scan + the GEMM kernel per problem
 
-    def step():
+    def run():
         for p in problems:
             native.launch_ragged_bwd_kernel(p["lhs"], p["rhs"], p["group_sizes"], a_scale=p["a_scale"], b_scale=p["b_scale"], out=p["out"],
                                             scale=pc, config=cfg, layout=pkg.GemmLayout.TN, rows=w["m"], cols=w["n"],
                                             k_packed=p["lhs"].shape[1], scale_cols=1)
-    return step, len(problems)
+    return run, len(problems)
 
 
-def make_e2e_runner(torch, pkg, w, problem):
-    """One step through the PUBLIC API from pinned host buffers and back; returns (callable, h2d, d2h bytes).
+def make_e2e_runner(ctx: Ctx, w, problem):
+    """One step through the PUBLIC API, default arguments, from pinned host buffers and back; returns
+    ``(callable, h2d bytes, d2h bytes)``.
 
     Every step uploads its operands, calls the API and downloads the result.  Steps alternate between two
     streams with their own device and host buffers, the way a host pipeline would run them, so that one step's
     upload overlaps the previous step's download (PCIe is full duplex); the work of each step is unchanged.
     ``step.finish()`` joins both streams into the current one (called before the stop event is recorded)."""
+    torch, pkg = ctx.torch, ctx.pkg
     lanes = 2
     streams = [torch.cuda.Stream() for _ in range(lanes)]
-    host = {k: v.cpu().pin_memory() for k, v in problem.items() if k != "out"}
+    names = ("a", "b", "a_scale", "b_scale") if w["kind"] == "dense" else ("lhs", "rhs", "a_scale", "b_scale", "group_sizes")
+    host = {k: problem[k].cpu().pin_memory() for k in names}
     out_host = [torch.empty(problem["out"].shape, dtype=problem["out"].dtype).pin_memory() for _ in range(lanes)]
     dev_sets = [{k: torch.empty_like(v, device="cuda") for k, v in host.items()} for _ in range(lanes)]
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     d2h = out_host[0].numel() * out_host[0].element_size()
     pc = pkg.ScaleSpec(pkg.ScaleMode.PER_CHANNEL)
     state = {"i": 0}
+
+    def call_api(dev):
+        if w["kind"] == "dense":
+            scale = pkg.ScaleSpec(pkg.ScaleMode.SUBCHANNEL, w["sub"]) if w["sub"] else pc
+            if w["epilogue"] == "swiglu":
+                return pkg.fused_swiglu_up_gate(dev["a"], dev["b"], a_scale=dev["a_scale"], b_scale=dev["b_scale"], scale=scale,
+                                                dtype=pkg.OperandDType(w["dtype"]))
+            return pkg.mm(dev["a"], dev["b"], a_scale=dev["a_scale"], b_scale=dev["b_scale"], scale=scale,
+                          dtype=pkg.OperandDType(w["dtype"]), epilogue=pkg.Epilogue(w["epilogue"]))
+        if w["kind"] == "ragged_fwd":
+            return pkg.ragged_dot_int4(dev["lhs"], dev["rhs"], dev["group_sizes"], a_scale=dev["a_scale"], b_scale=dev["b_scale"])
+        if w.get("flat"):
+            return pkg.ragged_dot_int4_bwd_flat(dev["lhs"], dev["rhs"], dev["group_sizes"], a_scale=dev["a_scale"], b_scale=dev["b_scale"])
+        return pkg.ragged_dot_int4_bwd(dev["lhs"], dev["rhs"], dev["group_sizes"], a_scale=dev["a_scale"], b_scale=dev["b_scale"],
+                                       layout=pkg.GemmLayout.TN)
 
     def step():
         lane = state["i"] % lanes
@@ -314,41 +453,44 @@ def make_e2e_runner(torch, pkg, w, problem):
         with torch.cuda.stream(stream):
             for k, v in host.items():
                 dev[k].copy_(v, non_blocking=True)
-            if w["kind"] == "dense":
-                scale = pkg.ScaleSpec(pkg.ScaleMode.SUBCHANNEL, w["sub"]) if w["sub"] else pc
-                if w["epilogue"] == "swiglu":
-                    out = pkg.fused_swiglu_up_gate(dev["a"], dev["b"], a_scale=dev["a_scale"], b_scale=dev["b_scale"], scale=scale,
-                                                   dtype=pkg.OperandDType(w["dtype"]))
-                else:
-                    out = pkg.mm(dev["a"], dev["b"], a_scale=dev["a_scale"], b_scale=dev["b_scale"], scale=scale,
-                                 dtype=pkg.OperandDType(w["dtype"]), epilogue=pkg.Epilogue(w["epilogue"]), schedule=pkg.KernelSchedule.PERSISTENT)
-            elif w["kind"] == "ragged_fwd":
-                out = pkg.ragged_dot_int4(dev["lhs"], dev["rhs"], dev["group_sizes"], a_scale=dev["a_scale"], b_scale=dev["b_scale"])
-            elif w.get("flat"):
-                out = pkg.ragged_dot_int4_bwd_flat(dev["lhs"], dev["rhs"], dev["group_sizes"], a_scale=dev["a_scale"], b_scale=dev["b_scale"])
-            else:
-                out = pkg.ragged_dot_int4_bwd(dev["lhs"], dev["rhs"], dev["group_sizes"], a_scale=dev["a_scale"], b_scale=dev["b_scale"],
-                                              layout=pkg.GemmLayout.TN)
+            out = call_api(dev)
             out_host[lane].copy_(out, non_blocking=True)
 
     def finish():
         for stream in streams:
             torch.cuda.current_stream().wait_stream(stream)
 
+    def copy_rates(reps: int = 3) -> dict:
+        """GB/s of the upload and of the download alone (pinned host memory, this rank)."""
+        rates = {}
+        for name, fn, nbytes in (("h2d_gbs", lambda: [dev_sets[0][k].copy_(v, non_blocking=True) for k, v in host.items()], h2d),
+                                 ("d2h_gbs", lambda: out_host[0].copy_(problem["out"], non_blocking=True), d2h)):
+            fn()
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(reps):
+                fn()
+            stop.record()
+            stop.synchronize()
+            rates[name] = round(nbytes * reps / (start.elapsed_time(stop) * 1e-3) / 1e9, 2)
+        return rates
+
     step.finish = finish
+    step.copy_rates = copy_rates
     return step, h2d, d2h
 
 
-def timed_region(torch, dist, world, step, steps: int, warmup: int, sampler=None) -> float:
+def timed_region(ctx: Ctx, step, steps: int, warmup: int, sampler=None) -> float:
     """ms for exactly ``steps`` steps, max over ranks, CUDA events on the current stream."""
+    torch = ctx.torch
     for _ in range(warmup):
         step()
     torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
+    if ctx.world > 1:
+        ctx.dist.barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ctx = sampler if sampler is not None else _Null()
-    with ctx:
+    with (sampler if sampler is not None else _Null()):
         start.record()
         for _ in range(steps):
             step()
@@ -358,12 +500,9 @@ def timed_region(torch, dist, world, step, steps: int, warmup: int, sampler=None
         stop.record()
         stop.synchronize()
     torch.cuda.synchronize()
-    ms = float(start.elapsed_time(stop))
-    if world > 1:
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dist.barrier()
-        ms = float(t.item())
+    ms = ctx.max_over_ranks(float(start.elapsed_time(stop)))
+    if ctx.world > 1:
+        ctx.dist.barrier()
     return ms
 
 
@@ -373,6 +512,196 @@ class _Null:
 
     def __exit__(self, *exc):
         return False
+
+
+def measure(ctx: Ctx, key: str, w, problems, *, ops_per_pass_rank: float, bytes_per_problem: float, steps: int, warmup: int,
+            graph: bool, sustained_s: float, passes_override: int, e2e: bool, peaks, peak_source, traffic, vendor_tops,
+            warm_steps: int = 1) -> dict:
+    """Burst and sustained device-timed throughput of one workload on this rank's problems, its roofline fraction,
+    clocks and (optionally) the end-to-end figure.  Every rank calls it; the numbers are whole-job (all ranks)."""
+    torch, native = ctx.torch, ctx.native
+    run_pass, launches_per_pass = make_pass(ctx, w, problems)
+    batch = len(problems)
+    run_pass()  # first-call set-up of the library happens outside any capture
+    torch.cuda.synchronize()
+    replay = run_pass
+    if graph:
+        captured = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(captured):
+            run_pass()
+        replay = captured.replay
+    native.reset_device_status(ctx.local_rank)
+    ops_per_pass = ctx.sum_over_ranks(ops_per_pass_rank)
+
+    # burst: a short region once the clocks have come up from idle (about 50 ms of replays), before the part has
+    # drawn power for long
+    first_ms = timed_region(ctx, replay, 2, max(warmup, 3)) / 2
+    ramp = max(3, min(2000, int(50.0 / max(first_ms, 1e-3))))
+    burst_passes = max(5, min(200, int(10.0 / max(first_ms, 1e-3))))
+    if passes_override > 0:  # a short run was asked for (profiling): no ramp either
+        ramp, burst_passes = 3, 2
+    burst_ms = timed_region(ctx, replay, burst_passes, ramp) / burst_passes
+    if passes_override > 0:
+        passes = passes_override
+    else:
+        passes = max(1, math.ceil(1.1 * sustained_s * 1e3 / (steps * burst_ms)))
+
+    def step():
+        for _ in range(passes):
+            replay()
+
+    sampler = ClockSampler(visible_device_index(ctx.local_rank))
+    ms = timed_region(ctx, step, steps, warm_steps, sampler)
+    status = native.device_status(ctx.local_rank)
+    if status[0] != 0:
+        raise SystemExit(f"{key}: a kernel reported status {status}")
+    ms_per_step = ms / steps
+    ms_per_pass = ms_per_step / passes
+    value = ops_per_pass / (ms_per_pass * 1e-3) / 1e12
+    kernel_us = ms_per_pass * 1e3 / batch
+    clocks = sampler.summary()
+    per_gpu_tops = value / ctx.world
+    sustained = ms >= 1000.0
+    record = {
+        "workload": w["name"], "metric": w["metric"], "value": value, "unit": "TOPS", "kernel_us": kernel_us,
+        "ms_per_step": ms_per_step, "steps": steps, "passes_per_step": passes, "problems_per_pass": batch, "timed_region_s": ms / 1e3,
+        "gpu_launches": launches_per_pass * passes * steps,
+        "burst": {"value": ops_per_pass / (burst_ms * 1e-3) / 1e12, "unit": "TOPS", "kernel_us": burst_ms * 1e3 / batch,
+                  "passes": burst_passes, "note": "first passes after warm-up, before the power cap settles the clock"},
+        "clocks": clocks,
+        "kernel_us_x_sm_mhz": kernel_us * clocks["sm_mhz"] if clocks.get("sm_mhz") else None,
+    }
+    bf16_peak = peaks["bf16_tflops_sustained"] if sustained and "bf16_tflops_sustained" in peaks else peaks["bf16_tflops"]
+    which = "sustained" if bf16_peak != peaks["bf16_tflops"] else "burst"
+    info = traffic.get(key) if ctx.world == 1 else None
+    if w["kind"] == "ragged_bwd":
+        achieved = bytes_per_problem / (kernel_us * 1e-6) / 1e9
+        record["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                              "traffic": info["bytes"] if info else None, "traffic_source": info["source"] if info else None,
+                              "peak_source": f"{peak_source} STREAM-style copy", "frac_of_nominal_hbm_8000": achieved / NOMINAL_HBM_GBS,
+                              "algorithmic_bytes_per_launch": bytes_per_problem, "kernel_us": kernel_us}
+    else:
+        peak = 2.0 * bf16_peak
+        record["roofline"] = {"bound": "tensor", "achieved": per_gpu_tops, "peak": peak, "unit": "TFLOP/s", "frac": per_gpu_tops / peak,
+                              "traffic": info["bytes"] if info else None, "traffic_source": info["source"] if info else None,
+                              "peak_source": f"2 x {peak_source} cuBLAS bf16 {which} ({bf16_peak} TFLOP/s): kind::i8 runs at twice the bf16 rate",
+                              "frac_of_nominal_int8_4500": per_gpu_tops / NOMINAL_INT8_TOPS,
+                              "frac_of_nominal_at_sampled_clock": (per_gpu_tops / (NOMINAL_INT8_TOPS * clocks["sm_mhz"] / clocks["sm_max_mhz"])
+                                                                   if clocks.get("sm_mhz") and clocks.get("sm_max_mhz") else None),
+                              "algorithmic_bytes_per_launch": bytes_per_problem, "kernel_us": kernel_us}
+        if vendor_tops:
+            record["roofline"]["frac_of_vendor_int8_gemm"] = per_gpu_tops / vendor_tops[which]
+    if key == "c1":
+        record["latency_us"] = kernel_us
+        record["note"] = "16.8 MOP on 4 tiles: launch-latency bound; kernel_us is the time per launch of back-to-back launches replayed from a CUDA graph"
+    if e2e:
+        e2e_step, h2d, d2h = make_e2e_runner(ctx, w, problems[0])
+        e2e_steps = max(3, min(steps, 10))
+        e2e_ms = timed_region(ctx, e2e_step, e2e_steps, 3) / e2e_steps
+        rates = e2e_step.copy_rates()
+        record["e2e"] = {"value": (ops_per_pass / batch) / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS", "h2d_bytes_per_step": int(h2d),
+                         "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms, "steps": e2e_steps,
+                         "per_rank_copy_gbs": ctx.gather(rates), "host_numa_nodes_per_rank": ctx.gather(host_numa_nodes()),
+                         "note": "one problem per step through the public API with default arguments; pinned host operands in, result out, "
+                                 "copies inside the timed region; steps alternate between two streams so that uploads overlap the previous "
+                                 "step's download.  Bound by the host link: with several ranks the copies of all GPUs share one socket's memory"}
+    return record
+
+
+def vendor_int8_probe(torch) -> dict:
+    """The vendor library's int8 GEMM (torch._int_mm -> cuBLASLt) at 8192^3 in this run: best of 10 launches and a
+    back-to-back loop of about half a second.  A measured int8 figure to set beside the nominal 4500 TOPS."""
+    n = 8192
+    a = torch.randint(-127, 128, (n, n), device="cuda", dtype=torch.int8)
+    b = torch.randint(-127, 128, (n, n), device="cuda", dtype=torch.int8).t()   # column-major B, as cuBLASLt wants it
+    for _ in range(3):
+        torch._int_mm(a, b)
+    best = float("inf")
+    for _ in range(10):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        torch._int_mm(a, b)
+        stop.record()
+        stop.synchronize()
+        best = min(best, float(start.elapsed_time(stop)))
+    reps = max(10, int(500.0 / best))
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(reps):
+        torch._int_mm(a, b)
+    stop.record()
+    stop.synchronize()
+    loop = float(start.elapsed_time(stop)) / reps
+    ops = 2.0 * n ** 3 / 1e12
+    return {"probe": "torch._int_mm int8 8192^3 -> int32", "burst": ops / (best * 1e-3), "sustained": ops / (loop * 1e-3), "loop_reps": reps}
+
+
+def batch_for(bytes_per_problem: float) -> int:
+    return max(2, int(-(-2.2 * L2_BYTES // bytes_per_problem)))
+
+
+def plan_problem(ctx: Ctx, key: str, *, split: str | None, batch_override: int, seed: int):
+    """Problems of workload ``key`` for this rank and their per-pass ops / per-problem bytes.
+    Returns ``(w, problems, ops_per_pass_rank, bytes_per_problem, extra_config)``."""
+    torch, shard = ctx.torch, ctx.shard
+    w = dict(WORKLOADS[key])
+    extra = {}
+    if w["kind"] == "dense":
+        n_local = w["n"]
+        if split == "strong" and ctx.world > 1:
+            lo, hi = shard.column_block(w["n"], ctx.world, ctx.rank)
+            n_local = hi - lo
+        per_problem = dense_bytes(w, n_local)
+        batch = batch_override or min(batch_for(per_problem), 1024)
+        problems = build_dense_problems(ctx, w, batch, seed=seed, split=split)
+        ops = sum(dense_ops(w, p["n"]) for p in problems)
+        return w, problems, ops, per_problem, extra
+    sizes = config5_group_sizes(torch)
+    if split == "weak" and ctx.world > 1:
+        # expert-parallel, weak scaling: the global problem has 64 * world groups
+        sizes = torch.cat([sizes[torch.randperm(64, generator=torch.Generator().manual_seed(r))] for r in range(ctx.world)])
+    plan = shard.assign_groups(sizes.tolist(), ctx.world) if (split and ctx.world > 1) else [list(range(len(sizes)))]
+    owned = plan[ctx.rank] if (split and ctx.world > 1) else plan[0]
+    if split and ctx.world > 1:
+        extra["load_imbalance_max_over_mean"] = shard.load_imbalance(sizes.tolist(), plan)
+    rows_local = int(sizes[list(owned)].sum())
+    per_problem = ragged_bytes(w, rows_local, len(owned))
+    batch = batch_override or batch_for(per_problem)
+    problems = build_ragged_problems(ctx, w, batch, seed=seed, sizes=sizes, owned=owned)
+    w["plan"], w["sizes"] = plan, sizes
+    return w, problems, ragged_ops(w, rows_local) * batch, per_problem, extra
+
+
+def time_all_gather(ctx: Ctx, w, problem, reps: int = 10) -> dict | None:
+    """The NCCL all-gather that assembles the full result from the ranks' local outputs, timed on its own."""
+    torch, shard, dist = ctx.torch, ctx.shard, ctx.dist
+    if ctx.world == 1 or w["kind"] == "ragged_bwd":
+        return None  # backward outputs are whole [g] slabs that stay with their expert
+    if w["kind"] == "dense":
+        ranges = [shard.column_block(w["n"], ctx.world, r) for r in range(ctx.world)]
+        fn = lambda: shard.all_gather_columns(problem["out"], ranges)
+        nbytes = 2 * w["m"] * w["n"]
+    else:
+        sizes, plan = w["sizes"], w["plan"]
+        ends = torch.cumsum(sizes, 0)
+        starts = ends - sizes
+        indices = [torch.cat([torch.arange(int(starts[g]), int(ends[g])) for g in groups]) if groups else torch.zeros(0, dtype=torch.int64)
+                   for groups in plan]
+        indices = [idx.to(ctx.device) for idx in indices]
+        fn = lambda: shard.all_gather_rows(problem["out"], indices, int(sizes.sum()))
+        nbytes = 2 * int(sizes.sum()) * w["n"]
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(reps):
+        fn()
+    stop.record()
+    stop.synchronize()
+    us = ctx.max_over_ranks(float(start.elapsed_time(stop))) / reps * 1e3
+    return {"us": us, "gathered_bytes": nbytes, "backend": "nccl all_gather_into_tensor + local placement", "reps": reps}
 
 
 # ----------------------------------------------------------------------------------------------
@@ -484,28 +813,27 @@ def run_reference_arm(args, w) -> dict:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
-    ap.add_argument("--batch", type=int, default=0, help="independent problems per step (0 = enough to exceed L2 twice over)")
+    ap.add_argument("--batch", type=int, default=0, help="independent problems per pass (0 = enough to exceed L2 twice over)")
+    ap.add_argument("--passes", type=int, default=0, help="passes per step (0 = enough for the timed steps to last a second)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--probe-int8-peak", action="store_true",
-                    help="time the vendor library's int8 GEMM (torch._int_mm, 8192^3, best of 10) and print it: "
-                         "a measured int8 figure to set beside the nominal 4500 TOPS; not a bench line")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of replaying a CUDA graph of one step")
+    ap.add_argument("--no-graph", action="store_true", help="launch every pass from Python instead of replaying a CUDA graph of one pass")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-sub", action="store_true", help="measure the headline workload only (no `workloads` / `strong` records, no vendor probe)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    w = dict(WORKLOADS[args.workload])
+    head = dict(WORKLOADS[args.workload])
 
     if args.impl == "reference":
         if rank == 0:
-            print(json.dumps(run_reference_arm(args, w)), flush=True)
+            print(json.dumps(run_reference_arm(args, head)), flush=True)
         return
 
     import torch
@@ -522,134 +850,93 @@ def main() -> None:
     from strix_halo_int4_gemms_b200 import distributed as shard
     from strix_halo_int4_gemms_b200 import native
 
-    if args.probe_int8_peak:
-        n = 8192
-        a = torch.randint(-127, 128, (n, n), device="cuda", dtype=torch.int8)
-        b = torch.randint(-127, 128, (n, n), device="cuda", dtype=torch.int8).t()   # column-major B, as cuBLASLt wants it
-        for _ in range(3):
-            torch._int_mm(a, b)
-        best = float("inf")
-        for _ in range(10):
-            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
-            torch._int_mm(a, b)
-            stop.record()
-            stop.synchronize()
-            best = min(best, float(start.elapsed_time(stop)))
-        print(json.dumps({"probe": "torch._int_mm int8 8192^3 -> int32, best of 10", "ms": best,
-                          "tops": 2.0 * n ** 3 / (best * 1e-3) / 1e12}), flush=True)
-        return
-
     status = pkg.dispatch_runtime_status()
     if not status.has_linked_kernels:
         raise SystemExit(f"CUDA library at {status.library_path} cannot run here: {status}")
+    ctx = Ctx(torch, dist, pkg, native, shard, rank, local_rank, world)
+    peaks, peak_source = load_peaks()
+    traffic = load_measured_traffic()
+    vendor = None
+    if not args.no_sub and world == 1:
+        vendor = vendor_int8_probe(torch)
+    common = dict(steps=args.steps, warmup=args.warmup, graph=not args.no_graph, sustained_s=SUSTAINED_SECONDS,
+                  passes_override=args.passes, peaks=peaks, peak_source=peak_source, traffic=traffic, vendor_tops=vendor)
 
-    imbalance = 1.0
-    if w["kind"] != "dense":
-        sizes = config5_group_sizes(torch)
-        if world > 1:
-            # expert-parallel: the global problem has 64 * world groups (weak scaling), LPT-assigned
-            all_sizes = torch.cat([sizes[torch.randperm(64, generator=torch.Generator().manual_seed(r))] for r in range(world)])
-            plan = shard.assign_groups(all_sizes.tolist(), world)
-            imbalance = shard.load_imbalance(all_sizes.tolist(), plan)
-            sizes = all_sizes[plan[rank]]
-        w["sizes"] = sizes
-        w["rows_local"] = int(sizes.sum())
-    per_problem_bytes = workload_bytes(w)
-    batch = args.batch or max(2, int(-(-2.2 * L2_BYTES // per_problem_bytes)))
-    problems = build_problem_set(torch, pkg, w, batch, seed=1234 + rank, device=torch.device("cuda", local_rank))
-    step, launches_per_step = make_runner(torch, pkg, w, problems)
+    # ---- headline (weak scaling at N > 1)
+    w, problems, ops, per_problem, extra = plan_problem(ctx, args.workload, split="weak" if world > 1 else None,
+                                                        batch_override=args.batch, seed=1234)
+    headline = measure(ctx, args.workload, w, problems, ops_per_pass_rank=ops, bytes_per_problem=per_problem, e2e=not args.no_e2e,
+                       warm_steps=args.warmup, **common)
+    batch = len(problems)
+    del problems
+    torch.cuda.empty_cache()
 
-    if w["kind"] == "dense":
-        ops_per_step_rank = workload_ops(w) * batch
-    elif w["kind"] == "ragged_fwd":
-        ops_per_step_rank = 2.0 * w["rows_local"] * w["k"] * w["n"] * batch
-    else:
-        ops_per_step_rank = 2.0 * w["m"] * w["n"] * w["rows_local"] * batch
-    ops_t = torch.tensor([ops_per_step_rank], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(ops_t)
-    ops_per_step = float(ops_t.item())
-
-    # One step (its `launches_per_step` kernels) is captured into a CUDA graph and replayed: at 60 us per kernel the
-    # Python launch loop is otherwise the bottleneck as soon as several ranks share the host's cores.
-    graphed = False
-    if not args.no_graph:
-        step()  # first-call set-up of the library happens outside the capture
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            step()
-        step = graph.replay
-        graphed = True
-    sampler = ClockSampler(visible_device_index(local_rank))
-    native.reset_device_status(local_rank)
-    ms = timed_region(torch, dist, world, step, args.steps, args.warmup, sampler)
-    dev_status = native.device_status(local_rank)
-    if dev_status[0] != 0:
-        raise SystemExit(f"a kernel reported status {dev_status}")
-    ms_per_step = ms / args.steps
-    value = ops_per_step / (ms_per_step * 1e-3) / 1e12
-    # duration of the dominant (GEMM) kernel: one per problem; the flat backward's group-start scan (one tiny
-    # CTA per problem, counted in gpu_launches) rides along inside it
-    kernel_us = ms_per_step * 1e3 / batch
-
-    e2e = None
-    if not args.no_e2e:
-        e2e_step, h2d, d2h = make_e2e_runner(torch, pkg, w, problems[0])
-        e2e_steps = max(3, min(args.steps, 20))
-        e2e_ms = timed_region(torch, dist, world, e2e_step, e2e_steps, 3) / e2e_steps
-        e2e = {"value": (ops_per_step / batch) / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS", "h2d_bytes_per_step": int(h2d),
-               "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms, "steps": e2e_steps,
-               "note": "one problem per step through the public API; pinned host operands in, result out, copies inside the timed region; "
-                       "steps alternate between two streams so that uploads overlap the previous step's download"}
+    # ---- the other BASELINE configurations (one GPU) / the given problems split over the ranks (N > 1)
+    workloads, strong = {}, {}
+    if not args.no_sub:
+        if world == 1:
+            for key in SUB_WORKLOADS:
+                if key == args.workload:
+                    continue
+                ws, ps, ops_s, bytes_s, _ = plan_problem(ctx, key, split=None, batch_override=0, seed=4321)
+                workloads[key] = measure(ctx, key, ws, ps, ops_per_pass_rank=ops_s, bytes_per_problem=bytes_s, e2e=not args.no_e2e, **common)
+                del ps
+                torch.cuda.empty_cache()
+        else:
+            for key in STRONG_WORKLOADS:
+                ws, ps, ops_s, bytes_s, extra_s = plan_problem(ctx, key, split="strong", batch_override=0, seed=4321)
+                rec = measure(ctx, key, ws, ps, ops_per_pass_rank=ops_s, bytes_per_problem=bytes_s, e2e=False, **common)
+                rec.update(extra_s)
+                rec["scaling"] = "strong"
+                rec["parallelism"] = ("column-parallel along N through distributed.shard_dense_rhs (A replicated, [M, N/ranks] local output)"
+                                      if ws["kind"] == "dense" else "expert-parallel over the 64 groups, distributed.assign_groups (LPT)")
+                gather = time_all_gather(ctx, ws, ps[0])
+                if gather is not None:
+                    rec["all_gather"] = gather
+                strong[key] = rec
+                del ps
+                torch.cuda.empty_cache()
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    peaks, peak_source = load_peaks()
-    timed_s = ms / 1e3
-    bf16_peak = peaks["bf16_tflops_sustained"] if timed_s > 1.0 and "bf16_tflops_sustained" in peaks else peaks["bf16_tflops"]
-    hbm_bound = args.workload in ("c5bwd", "c5bwd_flat")
-    per_gpu_tops = value / world
-    traffic = NCU_DRAM_TRAFFIC_BYTES.get(args.workload) if world == 1 else None
-    if hbm_bound:
-        achieved = per_problem_bytes / (kernel_us * 1e-6) / 1e9
-        roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                    "traffic": traffic, "peak_source": f"{peak_source} STREAM-style copy",
-                    "algorithmic_bytes_per_launch": per_problem_bytes, "kernel_us": kernel_us}
-    else:
-        peak = 2.0 * bf16_peak
-        roofline = {"bound": "tensor", "achieved": per_gpu_tops, "peak": peak, "unit": "TFLOP/s", "frac": per_gpu_tops / peak, "traffic": traffic,
-                    "peak_source": f"2 x {peak_source} cuBLAS bf16 {'sustained' if bf16_peak != peaks['bf16_tflops'] else 'burst'} "
-                                   f"({bf16_peak} TFLOP/s): kind::i8 runs at twice the bf16 rate",
-                    "frac_of_nominal_int8_4500": per_gpu_tops / NOMINAL_INT8_TOPS,
-                    "frac_of_vendor_int8_gemm": per_gpu_tops / VENDOR_INT8_GEMM_TOPS,
-                    "algorithmic_bytes_per_launch": per_problem_bytes, "kernel_us": kernel_us}
-
     line = {
-        "metric": w["metric"], "value": value, "unit": "TOPS", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "metric": w["metric"], "value": headline["value"], "unit": "TOPS", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": headline["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "s32 accumulate of int8 tensor-core products (int4 or int8 operands), fp32 scale, bf16/fp32 store",
         "data": "synthetic",
         "config": {
-            "workload": w["name"], "problems_per_step": batch,
-            "launch": "one CUDA graph replay per step" if graphed else "one Python call per kernel",
-            "l2": f"{batch} independent operand/output sets per step, {batch * per_problem_bytes / 1e6:.0f} MB touched between reuses (> 126 MB L2)",
-            "parallelism": "none" if world == 1 else ("column-parallel along N, one shard per GPU" if w["kind"] == "dense" else f"expert-parallel, LPT assignment, max/mean load {imbalance:.3f}"),
+            "workload": w["name"], "problems_per_step": batch * headline["passes_per_step"], "problems_per_pass": batch,
+            "passes_per_step": headline["passes_per_step"],
+            "launch": "one CUDA graph replay per pass" if not args.no_graph else "one Python call per kernel",
+            "l2": f"{batch} independent operand/output sets per pass, {batch * per_problem / 1e6:.0f} MB touched between reuses (> 126 MB L2)",
+            "parallelism": "none" if world == 1 else (
+                "column-parallel along N: global N = N x ranks, each rank's columns of the global B cut by distributed.shard_dense_rhs"
+                if w["kind"] == "dense" else
+                f"expert-parallel: 64 x ranks groups, distributed.assign_groups (LPT), max/mean load {extra.get('load_imbalance_max_over_mean', 1.0):.3f}"),
             "per_gpu_problem": "same as 1-GPU (weak scaling)",
         },
-        "clocks": sampler.summary(),
-        "gpu_launches": launches_per_step * args.steps,
-        "roofline": roofline,
-        "pct_of_nominal_int8_peak": 100.0 * per_gpu_tops / NOMINAL_INT8_TOPS,
+        "timed_region_s": headline["timed_region_s"],
+        "clocks": headline["clocks"],
+        "gpu_launches": headline["gpu_launches"],
+        "kernel_us": headline["kernel_us"],
+        "kernel_us_x_sm_mhz": headline["kernel_us_x_sm_mhz"],
+        "burst": headline["burst"],
+        "roofline": headline["roofline"],
+        "pct_of_nominal_int8_peak": 100.0 * headline["value"] / world / NOMINAL_INT8_TOPS,
     }
-    if e2e is not None:
-        line["e2e"] = e2e
+    if "e2e" in headline:
+        line["e2e"] = headline["e2e"]
+    if vendor is not None:
+        line["vendor_int8_gemm"] = vendor
+    if workloads:
+        line["workloads"] = workloads
+    if strong:
+        line["strong"] = strong
     if not args.no_cpu_baseline:
-        tops, rows, seconds, cores = cpu_reference_sample(w, budget_s=12.0)
+        tops, rows, seconds, cores = cpu_reference_sample(head, budget_s=12.0)
         line["cpu_baseline"] = {"value": tops, "unit": "TOPS", "cores": cores, "kind": "port",
                                 "sample": f"{rows} rows of the same workload in {seconds:.1f} s (reference PyTorch int32-matmul math)"}
     print(json.dumps(line), flush=True)

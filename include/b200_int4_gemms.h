@@ -49,14 +49,25 @@ enum { B200_OUT_BF16 = 0, B200_OUT_F32 = 1, B200_OUT_S32 = 2 };
  * meet its alignment rules and the plain CUDA-core kernel otherwise; the other two
  * force one of them (B200_PATH_TCGEN05 fails when the rules are not met). */
 enum { B200_PATH_AUTO = 0, B200_PATH_TCGEN05 = 1, B200_PATH_SIMT = 2 };
-/* PERSISTENT: one CTA per SM walks the tile list.  STANDARD: one CTA per output tile. */
-enum { B200_SCHEDULE_PERSISTENT = 0, B200_SCHEDULE_STANDARD = 1 };
+/* PERSISTENT: one CTA (or CTA pair) per SM (pair of SMs) walks the tile list, the epilogue of one tile
+ * overlapping the mainloop of the next.  TILE_PER_CTA: one CTA (or pair) per output tile, as a plain
+ * non-persistent kernel would be launched; kept for comparison, slower on anything but tiny problems. */
+enum { B200_SCHEDULE_PERSISTENT = 0, B200_SCHEDULE_TILE_PER_CTA = 1 };
 
 /* AUTO: the library pairs CTAs (clusters of two SMs, 256 x 256 tiles, tcgen05 cta_group::2) when a
  * paired kernel exists for the variant, M exceeds 128 and the 256-row tiling does not cost more waves
  * than it saves per tile; else one CTA per 128 x 256 tile.  SINGLE / PAIR force one of them (PAIR falls back to SINGLE when no paired kernel
  * exists).  Results are bit-identical either way. */
 enum { B200_CTA_GROUP_AUTO = 0, B200_CTA_GROUP_SINGLE = 1, B200_CTA_GROUP_PAIR = 2 };
+
+/* Subchannel scales only: how a dense launch adds the K-groups' contributions to the fp32 running sum.
+ *   FUSED (the default): out = fma(f32(acc_g) * sa_g, sb_g, out) - the last multiply and the add share one
+ *     rounding; half the CUDA-core work per accumulator element, which is what limits these kernels.
+ *   REFERENCE: out += (f32(acc_g) * sa_g) * sb_g with every rounding of the reference's PyTorch math
+ *     (api.py:316-324): bit-identical to it.
+ * Both stay far inside the bf16 output tolerance; the integer accumulators are exact either way.
+ * Grouped (ragged) launches always use the reference order. */
+enum { B200_ACCUMULATE_FUSED = 0, B200_ACCUMULATE_REFERENCE = 1 };
 
 typedef struct b200_gemm_variant {
   int32_t dtype;      /* B200_DTYPE_*      */
@@ -65,12 +76,14 @@ typedef struct b200_gemm_variant {
   int32_t subchannel; /* 32/64/128/256 when scale_mode is SUBCHANNEL, else 0 */
   int32_t epilogue;   /* B200_EPILOGUE_*   */
   int32_t out_dtype;  /* B200_OUT_*        */
-  int32_t split_k;    /* 1, 2, 4 or 8; >1 requires epilogue NONE and out_dtype F32 */
+  int32_t split_k;    /* 1, 2, 4 or 8 slices of K reduced by different CTAs and added by a second kernel in a
+                         fixed order; >1 requires epilogue NONE, out_dtype F32 and a workspace */
   int32_t path;       /* B200_PATH_*       */
   int32_t group_m;    /* raster swizzle width in row tiles, 0 = library default */
   int32_t schedule;   /* B200_SCHEDULE_*   */
   int32_t cta_group;  /* B200_CTA_GROUP_*: SMs per output tile of the tensor-core kernel */
-  int32_t reserved[5];
+  int32_t accumulate_order; /* B200_ACCUMULATE_*: subchannel dense launches only */
+  int32_t reserved[4];
 } b200_gemm_variant;
 
 /* Replaces amd_strix_halo_kernels_dispatch_version (dispatch.cpp:206). */
@@ -82,13 +95,14 @@ int b200_int4_gemms_has_compiled_kernels(void);
  * and at least one device are usable from this process. */
 int b200_int4_gemms_has_cuda_runtime(void);
 /* Replaces amd_strix_halo_kernels_has_linked_kernels (dispatch.cpp:216): both of the above
- * and device 0 is compute capability 10.x. */
+ * and at least one visible device is compute capability 10.x. */
 int b200_int4_gemms_has_linked_kernels(void);
 /* Replaces amd_strix_halo_kernels_last_error (dispatch.cpp:220). */
 const char* b200_int4_gemms_last_error(void);
 
 /* Device-side status word of the most recent launches on a device: 0 = no kernel reported
- * a problem, 1 = a bounded wait inside a kernel ran out (the kernel gave up and returned).
+ * a problem, 1 = a bounded wait inside a kernel ran out (the kernel gave up and returned),
+ * 3 = a grouped forward launch was given a device-built task list that had overflowed its arrays.
  * Reading it does not synchronise; call it after synchronising the stream.  detail[0..2]
  * (may be NULL) receive the block index and wait site.  No reference counterpart. */
 int b200_int4_gemms_device_status(int device_index, int32_t* detail);
@@ -112,6 +126,39 @@ int b200_int4_gemms_launch_dense(const b200_gemm_variant* variant, int device_in
                                  int32_t k);
 size_t b200_int4_gemms_dense_workspace_bytes(const b200_gemm_variant* variant, int32_t m,
                                              int32_t n, int32_t k);
+
+/* Split-K (variant->split_k = 2, 4, 8; the reference's SPLIT_K kernels, scripts/generate_amdgcn.py:189-192,
+ * whose fp32 output the caller zero-fills, native.py:739-740).  Here K is cut into slices of whole 128-deep
+ * K blocks (whole K-groups for subchannel scales); each slice is reduced by its own CTAs into the workspace
+ * ([slices, m, n]; exact s32 partial sums for per-channel scales, fp32 partial sums for subchannel scales)
+ * and a second kernel adds the slices in ascending order and, for per-channel scales, applies the scales
+ * once.  No atomics: results are bit-identical from run to run, and for per-channel scales bit-identical
+ * to split_k = 1.  The output needs no zero-fill.  Fewer slices than asked for are used when K is short. */
+
+/* What b200_int4_gemms_launch_dense would do for a variant and shape on a device, without launching:
+ * the kernel form, its grid and tile, the raster width and the effective split.  No reference counterpart
+ * (the reference's caller computes the grid itself, native.py:306-332). */
+enum {
+  B200_LAUNCHED_NOTHING = 0,
+  B200_LAUNCHED_TCGEN05 = 1,      /* tensor-core kernel, one CTA per tile */
+  B200_LAUNCHED_TCGEN05_PAIR = 2, /* tensor-core kernel, CTA pair per tile */
+  B200_LAUNCHED_SIMT = 3          /* CUDA-core kernel: correct, far slower; shapes and layouts the
+                                     tensor-core kernel does not take */
+};
+typedef struct b200_dense_plan {
+  int32_t path;      /* B200_LAUNCHED_* */
+  int32_t grid;      /* CTAs */
+  int32_t tile_rows; /* output rows per scheduled tile: 128, or 256 for a CTA pair */
+  int32_t tile_cols; /* 256, or 128 for SwiGLU (up + gate) */
+  int32_t group_m;   /* raster width in row tiles */
+  int32_t split_k;   /* slices actually used */
+  int32_t reserved[2];
+} b200_dense_plan;
+int b200_int4_gemms_plan_dense(const b200_gemm_variant* variant, int device_index, int32_t m, int32_t n,
+                               int32_t k, b200_dense_plan* plan);
+/* B200_LAUNCHED_* of the most recent launch call made by the calling thread (dense or grouped):
+ * lets a caller of B200_PATH_AUTO see that a launch went to the CUDA-core kernel. */
+int b200_int4_gemms_last_launch_path(void);
 
 /* Grouped forward (M-ragged):  out[rows of group g] = (lhs_rows @ rhs[g]) * a_scale * b_scale[g].
  * Replaces amd_strix_halo_kernels_launch_ragged_fwd_hsaco (dispatch.cpp:286-389).
@@ -178,14 +225,18 @@ int b200_int4_gemms_group_info(int device_index, uintptr_t stream_handle, const 
                                int32_t* overflow_dev);
 
 /* b200_int4_gemms_launch_ragged_fwd with the task count left on the device (num_tasks_dev, as written
- * by b200_int4_gemms_group_info); max_tasks is the capacity of the task arrays.  No reference
+ * by b200_int4_gemms_group_info); max_tasks is the capacity of the task arrays.  overflow_dev (may be
+ * NULL) is the builder's overflow flag: when it is set the kernel still runs the tasks that fit, and
+ * reports code 3 (detail[0] = tasks kept) through b200_int4_gemms_device_status, because rows of the
+ * tasks that did not fit stay unwritten.  Task bounds are clamped to [0, m] on the device.  No reference
  * counterpart: the reference reads the task count back to the host (ragged.py:275). */
 int b200_int4_gemms_launch_ragged_fwd_device_tasks(
     const b200_gemm_variant* variant, int device_index, uintptr_t stream_handle, const void* lhs,
     const void* rhs, const void* lhs_scale, const void* rhs_scale, const int64_t* task_group_ids,
     const int64_t* task_block_starts, const int64_t* task_actual_starts,
-    const int64_t* task_actual_ends, const int32_t* num_tasks_dev, void* out, int32_t m, int32_t n,
-    int32_t k_packed, int32_t scale_cols, int32_t max_tasks, int32_t groups, int32_t block_rows);
+    const int64_t* task_actual_ends, const int32_t* num_tasks_dev, const int32_t* overflow_dev, void* out,
+    int32_t m, int32_t n, int32_t k_packed, int32_t scale_cols, int32_t max_tasks, int32_t groups,
+    int32_t block_rows);
 
 /* Grouped backward over FLAT operands: all tokens back to back, no per-group padding.
  *   out[g] = (lhs[tokens of g, :]^T @ rhs[tokens of g, :]) * a_scale[g] * b_scale[g]

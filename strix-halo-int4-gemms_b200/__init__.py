@@ -41,6 +41,7 @@ from .metadata import (
 )
 from .native import (
     NativeRuntimeStatus,
+    accumulation_order,
     device_status,
     dispatch_runtime_status,
     launch_accumulators,
@@ -91,6 +92,7 @@ __all__ = [
     "KernelSchedule",
     "KernelStatus",
     "NativeRuntimeStatus",
+    "accumulation_order",
     "OperandDType",
     "RHS_SUBCHANNEL_SCALE_LAYOUT",
     "RaggedAutotuneCandidate",

@@ -38,7 +38,7 @@ from .ragged import (
     ragged_dot_int4,
     ragged_dot_int4_bwd,
 )
-from .registry import KernelRegistry, default_registry
+from .registry import KernelRegistry, default_registry, launch_signature
 
 BenchmarkRunner = Callable[[KernelMetadata, BenchmarkShape], BenchmarkRecord]
 RaggedBenchmarkRunner = Callable[["RaggedAutotuneCandidate", BenchmarkShape], BenchmarkRecord]
@@ -111,28 +111,32 @@ def find_autotune_candidates(
     layout: GemmLayout = GemmLayout.NN,
     scale: ScaleSpec,
     epilogue: Epilogue,
-    schedule: KernelSchedule = KernelSchedule.STANDARD,
+    schedule: KernelSchedule | None = None,
     registry: KernelRegistry = default_registry,
     root: str | Path | None = None,
     require_exact_generated_shape: bool = True,
 ) -> tuple[KernelMetadata, ...]:
-    """Registry entries of the requested cell that accept the shape (even-K, multiples divide).
+    """Entries of the requested cell that accept the shape and launch differently from one another.
 
-    ``root`` and ``require_exact_generated_shape`` are accepted for compatibility; every entry
-    is compiled into the library and none is tied to a single shape.
+    ``schedule=None`` (the default) spans every launch form: the library's own choice, one CTA per tile,
+    CTA pairs, one CTA per tile without the persistent grid, each with its raster widths and split-K factors.
+    Entries that differ only in the shape multiples they are registered for run the same launch, so one per
+    launch signature is kept (the one with the largest multiples).  ``root`` and
+    ``require_exact_generated_shape`` are accepted for compatibility; every entry is compiled into the
+    library and none is tied to a single shape.
     """
     del root, require_exact_generated_shape
-    return tuple(
-        kernel
-        for kernel in registry.all()
-        if kernel.a_dtype is dtype
-        and kernel.b_dtype is dtype
-        and kernel.layout is layout
-        and kernel.scale == scale
-        and kernel.epilogue is epilogue
-        and kernel.schedule is schedule
-        and kernel_supports_shape(kernel, m=m, n=n, k=k)
-    )
+    kept: dict[tuple, KernelMetadata] = {}
+    for kernel in registry.all():
+        if not (kernel.a_dtype is dtype and kernel.b_dtype is dtype and kernel.layout is layout and kernel.scale == scale
+                and kernel.epilogue is epilogue and (schedule is None or kernel.schedule is schedule)
+                and kernel_supports_shape(kernel, m=m, n=n, k=k)):
+            continue
+        signature = launch_signature(kernel)
+        held = kept.get(signature)
+        if held is None or kernel.tile.block_m * kernel.tile.block_n > held.tile.block_m * held.tile.block_n:
+            kept[signature] = kernel
+    return tuple(kept.values())
 
 
 def _load_db(benchmark_db: BenchmarkDatabase | None, path: str | Path | None) -> tuple[BenchmarkRecord, ...]:
@@ -150,7 +154,7 @@ def autotune(
     layout: GemmLayout = GemmLayout.NN,
     scale: ScaleSpec,
     epilogue: Epilogue,
-    schedule: KernelSchedule = KernelSchedule.STANDARD,
+    schedule: KernelSchedule | None = None,
     registry: KernelRegistry = default_registry,
     benchmark_db: BenchmarkDatabase | None = None,
     benchmark_db_path: str | Path | None = None,
@@ -161,7 +165,10 @@ def autotune(
     validate: bool = False,
     benchmark_runner: BenchmarkRunner | None = None,
 ) -> AutotuneResult:
-    """Time every candidate entry on seeded synthetic operands and return the fastest."""
+    """Time every candidate entry on seeded synthetic operands and return the fastest.
+
+    The candidates are launches that differ (see ``find_autotune_candidates``): with ``schedule=None`` the
+    result says which launch form, raster width and split factor is fastest for the shape."""
     shape = BenchmarkShape(m, n, k)
     candidates = find_autotune_candidates(
         m=m, n=n, k=k, dtype=dtype, layout=layout, scale=scale, epilogue=epilogue,
@@ -170,7 +177,7 @@ def autotune(
     if not candidates:
         raise LookupError(
             f"no pregenerated kernels match dtype={dtype.value}, layout={layout.value}, scale={scale.label}, "
-            f"epilogue={epilogue.value}, schedule={schedule.value}, shape=({m}, {n}, {k})"
+            f"epilogue={epilogue.value}, schedule={schedule.value if schedule is not None else 'any'}, shape=({m}, {n}, {k})"
         )
     earlier = _load_db(benchmark_db, benchmark_db_path)
 
@@ -200,8 +207,9 @@ def _check_ragged_mode(mode: RaggedDotMode) -> RaggedDotMode:
     return mode
 
 
-# Task heights the forward kernel accepts (rows per task, column tile, K stage).
-_FWD_SEEDS = ((128, 256, 128, 1), (64, 256, 128, 1), (32, 256, 128, 1), (128, 256, 128, 2))
+# Task heights of the forward kernel (rows per task, column tile, K stage, tasks per raster group): 256-row tasks
+# run on CTA pairs, the others on single CTAs.
+_FWD_SEEDS = ((256, 256, 128, 1), (128, 256, 128, 1), (64, 256, 128, 1), (32, 256, 128, 1))
 _BWD_SEEDS = ((128, 256, 128),)
 
 
@@ -216,8 +224,12 @@ def default_ragged_dot_candidates(
     mode = _check_ragged_mode(mode)
     layout = _check_layout(layout)
     if mode is RaggedDotMode.FWD:
+        # pair_tasks=False: a candidate runs with the task height it names (the default would widen 128 to 256)
+        pair_ok = layout is GemmLayout.NN and (scale.mode is ScaleMode.PER_CHANNEL or (scale.subchannel_size or 0) >= 128)
         configs: list[Any] = [
-            RaggedDotConfig(block_m=bm, block_n=bn, block_k=bk, group_size_tasks=gst) for bm, bn, bk, gst in _FWD_SEEDS
+            RaggedDotConfig(block_m=bm, block_n=bn, block_k=bk, group_size_tasks=gst, pair_tasks=False)
+            for bm, bn, bk, gst in _FWD_SEEDS
+            if bm <= 128 or pair_ok
         ]
     else:
         configs = [

@@ -12,7 +12,9 @@
 #include <string>
 
 #include "../../include/b200_int4_gemms.h"
-#include "gemm_kernel.cuh"
+#include <vector>
+
+#include "tc_table.h"
 #include "simt_kernel.cuh"
 #include "prep_kernels.cuh"
 
@@ -97,86 +99,80 @@ struct DeviceState {
 DeviceState g_devices[kMaxDevices];
 std::mutex g_device_mutex;
 
-template <typename Kernel>
-cudaError_t set_smem(Kernel kernel, int bytes) {
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+// ---------------------------------------------------------------------------------------
+// the tensor-core kernels this library holds (compiled in tc_kernels.cu, several parts)
+// ---------------------------------------------------------------------------------------
+const std::vector<TcKernelInfo>& tc_kernels() {
+  static const std::vector<TcKernelInfo> table = [] {
+    std::vector<TcKernelInfo> t;
+    tc_register_part_0(t);
+    tc_register_part_1(t);
+    tc_register_part_2(t);
+    tc_register_part_3(t);
+    tc_register_part_4(t);
+    tc_register_part_5(t);
+    tc_register_part_6(t);
+    tc_register_part_7(t);
+    return t;
+  }();
+  return table;
 }
 
-#define B200_FOR_EACH_TC_KERNEL(X)                                          \
-  /*  int4  A-MN   B-MN  scale     epilogue    out       maskK  pair */          \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, false)                 \
-  X(true, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, false)                \
-  X(true, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false)               \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, false, false)                  \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, false)                  \
-  X(true, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false)                 \
-  X(true, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, false)                \
-  X(true, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false)               \
-  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, false, false)                  \
-  X(true, true, true, SCALE_PC, EPI_NONE, OUT_BF16, false, false)                  \
-  X(true, true, true, SCALE_PC, EPI_NONE, OUT_F32, false, false)                   \
-  X(true, true, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false)                  \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, true, false)                   \
-  X(true, true, true, SCALE_PC, EPI_NONE, OUT_F32, true, false)                    \
-  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, true, false)                   \
-  X(true, true, true, SCALE_SC, EPI_NONE, OUT_F32, true, false)                    \
-  X(true, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, false)                \
-  X(true, false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false, false)               \
-  X(true, false, false, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false)              \
-  X(true, false, false, SCALE_PC, EPI_NONE, OUT_F32, false, false)                 \
-  X(true, false, false, SCALE_PC, EPI_NONE, OUT_S32, false, false)                 \
-  X(true, false, false, SCALE_SC, EPI_NONE, OUT_BF16, false, false)                \
-  X(true, false, false, SCALE_SC, EPI_RELU2, OUT_BF16, false, false)               \
-  X(true, false, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false)              \
-  X(true, false, false, SCALE_SC, EPI_NONE, OUT_F32, false, false)                 \
-  X(false, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, false)                \
-  X(false, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, false)               \
-  X(false, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false)              \
-  X(false, false, true, SCALE_PC, EPI_NONE, OUT_F32, false, false)                 \
-  X(false, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, false)                 \
-  X(false, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false)                \
-  X(false, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, false)               \
-  X(false, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false)              \
-  X(false, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, false)               \
-  X(false, false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false, false)              \
-  X(false, false, false, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false)             \
-  X(false, false, false, SCALE_PC, EPI_NONE, OUT_F32, false, false)                \
-  X(false, false, false, SCALE_PC, EPI_NONE, OUT_S32, false, false)                \
-  X(false, false, false, SCALE_SC, EPI_NONE, OUT_BF16, false, false)               \
-  X(false, false, false, SCALE_SC, EPI_RELU2, OUT_BF16, false, false)              \
-  X(false, false, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false)                \
-  /* layout TT: A [Kb, M] with B [N, Kb] */                                  \
-  X(true, true, false, SCALE_PC, EPI_NONE, OUT_BF16, false, false)          \
-  X(true, true, false, SCALE_PC, EPI_NONE, OUT_F32, false, false)           \
-  X(true, true, false, SCALE_SC, EPI_NONE, OUT_BF16, false, false)          \
-  X(false, true, true, SCALE_PC, EPI_NONE, OUT_BF16, false, false)          \
-  X(false, true, false, SCALE_PC, EPI_NONE, OUT_BF16, false, false)         \
-  /* CTA pairs (cta_group::2): 256 x 256 output tiles over two SMs */       \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true)           \
-  X(true, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, true)          \
-  X(true, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, true)         \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, false, true)            \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, true)            \
-  X(true, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, true)           \
-  X(true, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, true)         \
-  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, false, true)            \
-  X(true, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, true)          \
-  X(false, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true)          \
-  X(false, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, true)         \
-  X(false, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, true)        \
-  X(false, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, true)           \
-  X(false, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, true)          \
-  X(false, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, true)         \
-  X(false, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, true)        \
-  X(false, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, true)         \
-  X(false, false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false, true)        \
-  X(true, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, true)          \
-  X(true, true, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true)            \
-  /* grouped backward on CTA pairs */                                        \
-  X(true, true, true, SCALE_PC, EPI_NONE, OUT_F32, true, true)              \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, true, true)             \
-  X(true, true, true, SCALE_SC, EPI_NONE, OUT_F32, true, true)              \
-  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, true, true)
+struct TcLaunch {
+  bool int4, a_mn, b_mn, mask_k;
+  int scale, epi, out;
+  bool pair = false;     // CTA-pair kernel (clusters of two, 256-row tiles)
+  bool fast_sc = false;  // subchannel kernels: fused accumulation order
+};
+
+const TcKernelInfo* tc_find(const TcLaunch& l) {
+  for (const TcKernelInfo& k : tc_kernels()) {
+    if (k.int4 == l.int4 && k.a_mn == l.a_mn && k.b_mn == l.b_mn && k.scale == l.scale && k.epi == l.epi &&
+        k.out == l.out && k.mask_k == l.mask_k && k.pair == l.pair && k.fast_sc == l.fast_sc)
+      return &k;
+  }
+  return nullptr;
+}
+
+bool tc_has(const TcLaunch& l) { return tc_find(l) != nullptr; }
+
+// One-time set-up of one kernel on the current device: its dynamic shared-memory size and, for kernels that
+// re-balance registers between roles with setmaxnreg, a check of the compiled register count.  setmaxnreg.inc
+// waits for ever if the CTA's register pool is smaller than the roles ask for, .inc may not lower and .dec may
+// not raise a warp's count: a build whose compiler allocated differently is refused here, with a message,
+// instead of faulting or hanging on the device.  Allocates nothing.
+int prepare_kernel(const TcKernelInfo& k) {
+  cudaError_t err = cudaFuncSetAttribute(k.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, k.smem_bytes);
+  if (err != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(max dynamic shared memory)", err);
+  if (k.reg_pool_needed > 0) {
+    cudaFuncAttributes attr;
+    err = cudaFuncGetAttributes(&attr, k.fn);
+    if (err != cudaSuccess) return fail_cuda("cudaFuncGetAttributes", err);
+    const bool pool_ok = attr.numRegs * k.threads >= k.reg_pool_needed;
+    const bool moves_ok = attr.numRegs >= k.regs_light && attr.numRegs <= k.regs_epilogue &&
+                          (k.unpack_warps == 0 ||
+                           (k.unpack_raises ? attr.numRegs <= k.regs_unpack : attr.numRegs >= k.regs_unpack));
+    if (!pool_ok || !moves_ok)
+      return fail("a kernel was compiled with " + std::to_string(attr.numRegs) +
+                  " registers per thread, which does not fit its setmaxnreg register re-balance");
+  }
+  return 0;
+}
+
+void cluster_launch_config(const TcKernelInfo& k, int grid, cudaStream_t stream, cudaLaunchConfig_t* cfg,
+                           cudaLaunchAttribute* attr) {
+  *cfg = cudaLaunchConfig_t{};
+  cfg->gridDim = dim3(grid);
+  cfg->blockDim = dim3(k.threads);
+  cfg->dynamicSmemBytes = k.smem_bytes;
+  cfg->stream = stream;
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = k.pair ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg->attrs = attr;
+  cfg->numAttrs = 1;
+}
 
 int ensure_device(int device_index, DeviceState** out) {
   if (device_index < 0 || device_index >= kMaxDevices) return fail("device_index out of range");
@@ -200,62 +196,20 @@ int ensure_device(int device_index, DeviceState** out) {
     std::memset(st.status_host, 0, 4 * sizeof(int));
     err = cudaHostGetDevicePointer(reinterpret_cast<void**>(&st.status_dev), st.status_host, 0);
     if (err != cudaSuccess) return fail_cuda("cudaHostGetDevicePointer(status)", err);
-#define X(I4, AMN, BMN, SC, EP, OT, MK, PR)                                                             \
-  err = set_smem(gemm_i8_tcgen05_kernel<I4, AMN, BMN, SC, EP, OT, MK, PR>,                               \
-                 KernelTraits<I4, AMN, BMN, SC, EP, OT, MK, PR>::kSmemBytes);                            \
-  if (err != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(max dynamic shared memory)", err);   \
-  if (KernelTraits<I4, AMN, BMN, SC, EP, OT, MK, PR>::kRegPoolNeeded > 0) {                                  \
-    /* setmaxnreg.inc would wait for ever if the CTA's register pool were smaller than the roles ask for */ \
-    cudaFuncAttributes attr;                                                                             \
-    err = cudaFuncGetAttributes(&attr, gemm_i8_tcgen05_kernel<I4, AMN, BMN, SC, EP, OT, MK, PR>);           \
-    if (err != cudaSuccess) return fail_cuda("cudaFuncGetAttributes", err);                              \
-    using KT = KernelTraits<I4, AMN, BMN, SC, EP, OT, MK, PR>;                                             \
-    const bool pool_ok = attr.numRegs * KT::kThreads >= KT::kRegPoolNeeded;                              \
-    /* setmaxnreg.inc may not lower and setmaxnreg.dec may not raise a warp's register count */           \
-    const bool moves_ok = attr.numRegs >= KT::kRegsLight && attr.numRegs <= KT::kRegsEpilogue &&         \
-                          (KT::kUnpackWarps == 0 ||                                                     \
-                           (KT::kUnpackRaises ? attr.numRegs <= KT::kRegsUnpack : attr.numRegs >= KT::kRegsUnpack)); \
-    if (!pool_ok || !moves_ok)                                                                           \
-      return fail("a kernel was compiled with " + std::to_string(attr.numRegs) +                        \
-                  " registers per thread, which does not fit its setmaxnreg register re-balance");      \
-  }
-    B200_FOR_EACH_TC_KERNEL(X)
-#undef X
     // CTA-pair kernels are persistent: every cluster of the grid must be resident at once, so the grid
     // is sized by what the device can co-schedule (not every SM can always be paired).
     st.max_pair_clusters = st.sm_count / 2;
-#define X(I4, AMN, BMN, SC, EP, OT, MK, PR)                                                            \
-  if (PR) {                                                                                          \
-    using T = KernelTraits<I4, AMN, BMN, SC, EP, OT, MK, PR>;                                         \
-    cudaLaunchConfig_t cfg{};                                                                        \
-    cfg.gridDim = dim3(st.sm_count & ~1);                                                            \
-    cfg.blockDim = dim3(T::kThreads);                                                                \
-    cfg.dynamicSmemBytes = T::kSmemBytes;                                                            \
-    cudaLaunchAttribute attr[1];                                                                     \
-    attr[0].id = cudaLaunchAttributeClusterDimension;                                                \
-    attr[0].val.clusterDim.x = 2;                                                                    \
-    attr[0].val.clusterDim.y = 1;                                                                    \
-    attr[0].val.clusterDim.z = 1;                                                                    \
-    cfg.attrs = attr;                                                                                \
-    cfg.numAttrs = 1;                                                                                \
-    int clusters = 0;                                                                                \
-    err = cudaOccupancyMaxActiveClusters(&clusters, gemm_i8_tcgen05_kernel<I4, AMN, BMN, SC, EP, OT, MK, PR>, &cfg); \
-    if (err != cudaSuccess) return fail_cuda("cudaOccupancyMaxActiveClusters", err);                 \
-    if (clusters < st.max_pair_clusters) st.max_pair_clusters = clusters;                            \
-  }
-    B200_FOR_EACH_TC_KERNEL(X)
-#undef X
-    // B200_INT4_GEMMS_MAX_SMS=<n>: use at most n SMs (scaling experiments; results do not change)
-    if (const char* cap = std::getenv("B200_INT4_GEMMS_MAX_SMS"); cap != nullptr) {
-      const int n = std::atoi(cap);
-      if (n >= 2 && n < st.sm_count) {
-        st.sm_count = n;
-        if (st.max_pair_clusters > n / 2) st.max_pair_clusters = n / 2;
-      }
+    for (const TcKernelInfo& k : tc_kernels()) {
+      if (int rc = prepare_kernel(k); rc != 0) return rc;
+      if (!k.pair) continue;
+      cudaLaunchConfig_t cfg;
+      cudaLaunchAttribute attr[1];
+      cluster_launch_config(k, st.sm_count & ~1, nullptr, &cfg, attr);
+      int clusters = 0;
+      err = cudaOccupancyMaxActiveClusters(&clusters, k.fn, &cfg);
+      if (err != cudaSuccess) return fail_cuda("cudaOccupancyMaxActiveClusters", err);
+      if (clusters < st.max_pair_clusters) st.max_pair_clusters = clusters;
     }
-    if (std::getenv("B200_INT4_GEMMS_VERBOSE") != nullptr)
-      std::fprintf(stderr, "b200_int4_gemms: device %d: %d SMs, %d co-resident CTA pairs\n", device_index,
-                   st.sm_count, st.max_pair_clusters);
     st.ready = true;
   }
   *out = &st;
@@ -279,49 +233,19 @@ int make_output_map(CUtensorMap* map, void* out, int out_dtype, uint64_t rows, u
   return 0;
 }
 
-struct TcLaunch {
-  bool int4, a_mn, b_mn, mask_k;
-  int scale, epi, out;
-  bool pair = false;  // CTA-pair kernel (clusters of two, 256-row tiles)
-};
-
 int launch_tc(const TcLaunch& l, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
               const GemmParams& p, int grid, cudaStream_t stream) {
-#define X(I4, AMN, BMN, SC, EP, OT, MK, PR)                                                              \
-  if (l.int4 == I4 && l.a_mn == AMN && l.b_mn == BMN && l.scale == SC && l.epi == EP && l.out == OT &&           \
-      l.mask_k == MK && l.pair == PR) {                                                                          \
-    using T = KernelTraits<I4, AMN, BMN, SC, EP, OT, MK, PR>;                                             \
-    cudaLaunchConfig_t cfg{};                                                                    \
-    cfg.gridDim = dim3(grid);                                                                    \
-    cfg.blockDim = dim3(T::kThreads);                                                            \
-    cfg.dynamicSmemBytes = T::kSmemBytes;                                                        \
-    cfg.stream = stream;                                                                         \
-    cudaLaunchAttribute attr[1];                                                                 \
-    attr[0].id = cudaLaunchAttributeClusterDimension;                                            \
-    attr[0].val.clusterDim.x = PR ? 2 : 1;                                                       \
-    attr[0].val.clusterDim.y = 1;                                                                \
-    attr[0].val.clusterDim.z = 1;                                                                \
-    cfg.attrs = attr;                                                                            \
-    cfg.numAttrs = 1;                                                                            \
-    cudaError_t err = cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_kernel<I4, AMN, BMN, SC, EP, OT, MK, PR>, \
-                                         ta, tb, tc, p);                                         \
-    if (err == cudaSuccess) err = cudaGetLastError();                                            \
-    if (err != cudaSuccess) return fail_cuda("tcgen05 GEMM kernel launch", err);                 \
-    return 0;                                                                                    \
-  }
-  B200_FOR_EACH_TC_KERNEL(X)
-#undef X
-  return -1;  // no such instantiation
-}
-
-bool tc_has(const TcLaunch& l) {
-#define X(I4, AMN, BMN, SC, EP, OT, MK, PR)                                                              \
-  if (l.int4 == I4 && l.a_mn == AMN && l.b_mn == BMN && l.scale == SC && l.epi == EP && l.out == OT &&           \
-      l.mask_k == MK && l.pair == PR)                                                                            \
-    return true;
-  B200_FOR_EACH_TC_KERNEL(X)
-#undef X
-  return false;
+  const TcKernelInfo* k = tc_find(l);
+  if (k == nullptr) return -1;  // no such instantiation
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attr[1];
+  cluster_launch_config(*k, grid, stream, &cfg, attr);
+  void* args[4] = {const_cast<CUtensorMap*>(&ta), const_cast<CUtensorMap*>(&tb), const_cast<CUtensorMap*>(&tc),
+                   const_cast<GemmParams*>(&p)};
+  cudaError_t err = cudaLaunchKernelExC(&cfg, k->fn, args);
+  if (err == cudaSuccess) err = cudaGetLastError();
+  if (err != cudaSuccess) return fail_cuda("tcgen05 GEMM kernel launch", err);
+  return 0;
 }
 
 int check_variant(const b200_gemm_variant* v) {
@@ -342,9 +266,11 @@ int check_variant(const b200_gemm_variant* v) {
   if (v->split_k > 1 && (v->epilogue != B200_EPILOGUE_NONE || v->out_dtype != B200_OUT_F32))
     return fail("split_k > 1 needs epilogue NONE and float32 output");
   if (v->path < B200_PATH_AUTO || v->path > B200_PATH_SIMT) return fail("variant.path is unknown");
-  if (v->schedule != B200_SCHEDULE_PERSISTENT && v->schedule != B200_SCHEDULE_STANDARD)
+  if (v->schedule != B200_SCHEDULE_PERSISTENT && v->schedule != B200_SCHEDULE_TILE_PER_CTA)
     return fail("variant.schedule is unknown");
   if (v->cta_group < B200_CTA_GROUP_AUTO || v->cta_group > B200_CTA_GROUP_PAIR) return fail("variant.cta_group is unknown");
+  if (v->accumulate_order != B200_ACCUMULATE_FUSED && v->accumulate_order != B200_ACCUMULATE_REFERENCE)
+    return fail("variant.accumulate_order is unknown");
   return 0;
 }
 
@@ -375,13 +301,20 @@ extern "C" int b200_int4_gemms_has_cuda_runtime(void) {
 }
 
 extern "C" int b200_int4_gemms_has_linked_kernels(void) {
-  if (!b200_int4_gemms_has_cuda_runtime()) return 0;
-  cudaDeviceProp prop;
-  if (cudaGetDeviceProperties(&prop, 0) != cudaSuccess) {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess) {
     (void)cudaGetLastError();
     return 0;
   }
-  return prop.major == 10 ? 1 : 0;
+  for (int device = 0; device < count; ++device) {
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess) {
+      (void)cudaGetLastError();
+      continue;
+    }
+    if (major == 10) return 1;
+  }
+  return 0;
 }
 
 extern "C" const char* b200_int4_gemms_last_error(void) { return g_last_error.c_str(); }
@@ -406,13 +339,141 @@ extern "C" int b200_int4_gemms_reset_device_status(int device_index) {
   return 0;
 }
 
+namespace {
+
+// Everything launch_dense decides before it launches: the kernel form, the tile grid, the split.
+struct DensePlan {
+  bool tensor_core = false;
+  TcLaunch kernel{};
+  int tile_rows = BM;
+  int tile_cols = BN;
+  int tiles_m = 0, tiles_n = 0;
+  int group_m = 1;
+  int grid = 0;
+  int slices = 1;        // effective split-K factor (<= variant.split_k)
+  int k_per_slice = 0;
+  bool integer_partials = false;
+};
+
+int effective_slices(int k, int unit, int requested, int* k_per_slice) {
+  const int units = (k + unit - 1) / unit;
+  const int want = requested < units ? requested : units;
+  const int per = (units + want - 1) / want;  // units per slice
+  *k_per_slice = per * unit;
+  return (units + per - 1) / per;
+}
+
+// `a`, `b`, `c` only decide alignment; nullptr means "assume aligned".
+int plan_dense(const b200_gemm_variant* v, const DeviceState* dev, const void* a, const void* b, int32_t m,
+               int32_t n, int32_t k, DensePlan* plan) {
+  const bool int4 = v->dtype == B200_DTYPE_INT4;
+  const bool swiglu = v->epilogue == B200_EPILOGUE_SWIGLU;
+  const int b_cols = swiglu ? 2 * n : n;
+  const int kb = int4 ? (k + 1) / 2 : k;
+  const bool a_t = (v->layout == B200_LAYOUT_TN || v->layout == B200_LAYOUT_TT);
+  const bool b_t = (v->layout == B200_LAYOUT_NT || v->layout == B200_LAYOUT_TT);
+  const int sc_mode = (v->scale_mode == B200_SCALE_SUBCHANNEL) ? SCALE_SC : SCALE_PC;
+  DensePlan pl;
+  pl.tile_cols = swiglu ? NBLK : BN;
+  pl.tiles_n = (n + pl.tile_cols - 1) / pl.tile_cols;
+
+  // split-K: slices of whole K blocks (and whole K-groups); per-channel slices store exact s32 partial sums,
+  // subchannel slices fp32 partial sums, and splitk_reduce_kernel adds them in slice order
+  int out_kind = v->out_dtype;
+  if (v->split_k > 1) {
+    const int unit = (sc_mode == SCALE_SC && v->subchannel > BK) ? v->subchannel : BK;
+    pl.slices = effective_slices(k, unit, v->split_k, &pl.k_per_slice);
+    if (pl.slices > 1) {
+      pl.integer_partials = sc_mode == SCALE_PC;
+      out_kind = pl.integer_partials ? OUT_S32 : OUT_F32;
+    }
+  }
+  TcLaunch tl{int4, a_t, !b_t, false, sc_mode, v->epilogue, out_kind};
+  // subchannel scales: the fused accumulation order unless the caller asks for the reference's order of
+  // roundings (or the variant has no kernel in the fused order, e.g. K-groups of 32 / 64 would gain nothing)
+  if (sc_mode == SCALE_SC && v->accumulate_order == B200_ACCUMULATE_FUSED) {
+    TcLaunch fused = tl;
+    fused.fast_sc = true;
+    if (tc_has(fused)) tl = fused;
+  }
+  bool tc_ok = tc_has(tl) && (a == nullptr || aligned16(a)) && (b == nullptr || aligned16(b));
+  tc_ok = tc_ok && ((a_t ? m : kb) % 16 == 0) && ((b_t ? kb : b_cols) % 16 == 0);  // TMA needs 16-byte pitches
+  if (v->path == B200_PATH_SIMT) tc_ok = false;
+  if (v->path == B200_PATH_TCGEN05 && !tc_ok)
+    return fail("the tcgen05 kernel needs 16-byte aligned operands, operand pitches that are multiples of 16 bytes, and a kernel instantiated for the variant");
+  if (!tc_ok && pl.slices > 1)
+    return fail("split_k > 1 runs on the tensor-core kernel only (layouts NN / NT per-channel, NN subchannel; 16-byte aligned operands and pitches)");
+  pl.tensor_core = tc_ok;
+  if (tc_ok) {
+    // CTA pairs: 256-row tiles over two SMs.  A pair's K block takes about 0.87 of the time a single CTA needs
+    // for its 128 x 256 tile (a third less operand traffic per SM), so pairs win whenever they do not need
+    // more waves than that: compare waves x time per tile of the two schedules.  An M that is not a multiple
+    // of 256 leaves the peer CTA of the last row of tiles without rows, which the wave count accounts for.
+    TcLaunch pair = tl;
+    pair.pair = true;
+    const bool sc_ok = sc_mode == SCALE_PC || v->subchannel >= BK;
+    const long long single_tiles = static_cast<long long>((m + BM - 1) / BM) * pl.tiles_n * pl.slices;
+    const long long pair_tiles = static_cast<long long>((m + 2 * BM - 1) / (2 * BM)) * pl.tiles_n * pl.slices;
+    const long long single_waves = (single_tiles + dev->sm_count - 1) / dev->sm_count;
+    const int pairs = dev->max_pair_clusters > 0 ? dev->max_pair_clusters : 1;
+    const long long pair_waves = (pair_tiles + pairs - 1) / pairs;
+    const bool want = v->cta_group == B200_CTA_GROUP_PAIR ||
+                      (v->cta_group == B200_CTA_GROUP_AUTO && m > BM && 87 * pair_waves <= 100 * single_waves);
+    if (want && sc_ok && dev->max_pair_clusters > 0 && tc_has(pair)) tl = pair;
+    pl.kernel = tl;
+    pl.tile_rows = tl.pair ? 2 * BM : BM;
+    pl.tiles_m = (m + pl.tile_rows - 1) / pl.tile_rows;
+    // raster width (row tiles walked before the next column tile), from sweeps on a B200: 16 for the 256-row
+    // tiles of CTA pairs, 32 for single-CTA int8 tiles, 8 for single-CTA int4 tiles
+    pl.group_m = v->group_m > 0 ? v->group_m : (tl.pair ? 16 : (int4 ? 8 : 32));
+    const int num_tiles = pl.tiles_m * pl.tiles_n * pl.slices;
+    const int cta_per_tile = tl.pair ? 2 : 1;
+    const int max_units = tl.pair ? dev->max_pair_clusters : dev->sm_count;  // tiles in flight
+    pl.grid = (num_tiles < max_units ? num_tiles : max_units) * cta_per_tile;
+    if (v->schedule == B200_SCHEDULE_TILE_PER_CTA) pl.grid = num_tiles * cta_per_tile;
+  } else {
+    pl.tiles_m = (m + 3) / 4;  // the CUDA-core kernel: 4 rows x 64 columns per block
+    pl.tiles_n = (n + 63) / 64;
+    pl.grid = pl.tiles_m * pl.tiles_n;
+  }
+  *plan = pl;
+  return 0;
+}
+
+thread_local int g_last_path = B200_LAUNCHED_NOTHING;
+
+}  // namespace
+
+extern "C" int b200_int4_gemms_last_launch_path(void) { return g_last_path; }
+
 extern "C" size_t b200_int4_gemms_dense_workspace_bytes(const b200_gemm_variant* variant, int32_t m,
                                                         int32_t n, int32_t k) {
-  (void)variant;
-  (void)m;
-  (void)n;
-  (void)k;
-  return 0;  // every output tile is reduced by one CTA; no split-K scratch is needed
+  if (variant == nullptr || variant->split_k <= 1 || m <= 0 || n <= 0 || k <= 0) return 0;
+  const int sc = variant->scale_mode == B200_SCALE_SUBCHANNEL ? variant->subchannel : 0;
+  int per = 0;
+  const int slices = effective_slices(k, sc > BK ? sc : BK, variant->split_k, &per);
+  if (slices <= 1) return 0;
+  return static_cast<size_t>(slices) * static_cast<size_t>(m) * static_cast<size_t>(n) * 4u;  // s32 or f32 partials
+}
+
+extern "C" int b200_int4_gemms_plan_dense(const b200_gemm_variant* v, int device_index, int32_t m, int32_t n,
+                                          int32_t k, b200_dense_plan* out) {
+  g_last_error.clear();
+  if (int rc = check_variant(v); rc != 0) return rc;
+  if (out == nullptr) return fail("plan must be non-null");
+  if (m <= 0 || n <= 0 || k <= 0) return fail("m, n and k must be positive");
+  DeviceState* dev = nullptr;
+  if (int rc = ensure_device(device_index, &dev); rc != 0) return rc;
+  DensePlan pl;
+  if (int rc = plan_dense(v, dev, nullptr, nullptr, m, n, k, &pl); rc != 0) return rc;
+  std::memset(out, 0, sizeof(*out));
+  out->path = !pl.tensor_core ? B200_LAUNCHED_SIMT : (pl.kernel.pair ? B200_LAUNCHED_TCGEN05_PAIR : B200_LAUNCHED_TCGEN05);
+  out->grid = pl.grid;
+  out->tile_rows = pl.tensor_core ? pl.tile_rows : 4;
+  out->tile_cols = pl.tensor_core ? pl.tile_cols : 64;
+  out->group_m = pl.tensor_core ? pl.group_m : 0;
+  out->split_k = pl.slices;
+  return 0;
 }
 
 extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int device_index,
@@ -421,8 +482,7 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
                                             void* workspace, size_t workspace_bytes, int32_t m,
                                             int32_t n, int32_t k) {
   g_last_error.clear();
-  (void)workspace;
-  (void)workspace_bytes;
+  g_last_path = B200_LAUNCHED_NOTHING;
   if (int rc = check_variant(v); rc != 0) return rc;
   if (a == nullptr || b == nullptr || c == nullptr) return fail("a, b and c pointers must be non-null");
   if (v->out_dtype != B200_OUT_S32 && (a_scale == nullptr || b_scale == nullptr))
@@ -442,15 +502,10 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
   const int sc_mode = (v->scale_mode == B200_SCALE_SUBCHANNEL) ? SCALE_SC : SCALE_PC;
   const int scale_cols = sc_mode == SCALE_SC ? (k + v->subchannel - 1) / v->subchannel : 1;
 
-  TcLaunch tl{int4, a_t, !b_t, false, sc_mode, v->epilogue, v->out_dtype};
-  bool tc_ok = tc_has(tl) && aligned16(a) && aligned16(b);
-  // TMA needs 16-byte pitches
-  tc_ok = tc_ok && ((a_t ? m : kb) % 16 == 0) && ((b_t ? kb : b_cols) % 16 == 0);
-  if (v->path == B200_PATH_SIMT) tc_ok = false;
-  if (v->path == B200_PATH_TCGEN05 && !tc_ok)
-    return fail("the tcgen05 kernel needs 16-byte aligned operands, operand pitches that are multiples of 16 bytes, and a kernel instantiated for the variant");
+  DensePlan pl;
+  if (int rc = plan_dense(v, dev, a, b, m, n, k, &pl); rc != 0) return rc;
 
-  if (!tc_ok) {
+  if (!pl.tensor_core) {
     SimtParams sp{};
     sp.mode = MODE_DENSE;
     sp.int4 = int4;
@@ -471,7 +526,15 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
     sp.a_scale = static_cast<const __nv_bfloat16*>(a_scale);
     sp.b_scale = static_cast<const __nv_bfloat16*>(b_scale);
     sp.out = c;
+    g_last_path = B200_LAUNCHED_SIMT;
     return launch_simt(sp, m, 1, stream);
+  }
+
+  const bool split = pl.slices > 1;
+  if (split) {
+    const size_t need = static_cast<size_t>(pl.slices) * m * n * 4u;
+    if (workspace == nullptr || workspace_bytes < need || !aligned16(workspace))
+      return fail("split_k > 1 needs a 16-byte aligned workspace of b200_int4_gemms_dense_workspace_bytes(...) bytes");
   }
 
   CUtensorMap ta, tb;
@@ -504,32 +567,13 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
   p.M = m;
   p.N = n;
   p.K = k;
-  p.tile_cols = swiglu ? NBLK : BN;
-  p.tiles_n = (n + p.tile_cols - 1) / p.tile_cols;
-  // CTA pairs: 256-row tiles over two SMs.  A pair's K block takes about 0.87 of the time a single CTA needs
-  // for its 128 x 256 tile (a third less operand traffic per SM), so pairs win whenever they do not need
-  // more waves than that: compare waves x time per tile of the two schedules.  An M that is not a multiple
-  // of 256 leaves the peer CTA of the last row of tiles without rows, which the wave count accounts for.
-  {
-    TcLaunch pl = tl;
-    pl.pair = true;
-    const bool sc_ok = sc_mode == SCALE_PC || v->subchannel >= BK;
-    const long long single_tiles = static_cast<long long>((m + BM - 1) / BM) * p.tiles_n;
-    const long long pair_tiles = static_cast<long long>((m + 2 * BM - 1) / (2 * BM)) * p.tiles_n;
-    const long long single_waves = (single_tiles + dev->sm_count - 1) / dev->sm_count;
-    const int pairs = dev->max_pair_clusters > 0 ? dev->max_pair_clusters : 1;
-    const long long pair_waves = (pair_tiles + pairs - 1) / pairs;
-    bool want = v->cta_group == B200_CTA_GROUP_PAIR ||
-                (v->cta_group == B200_CTA_GROUP_AUTO && m > BM && 87 * pair_waves <= 100 * single_waves);
-    if (v->schedule == B200_SCHEDULE_STANDARD && v->cta_group != B200_CTA_GROUP_PAIR) want = false;
-    if (want && sc_ok && tc_has(pl)) tl = pl;
-  }
-  const int tile_rows = tl.pair ? 2 * BM : BM;
-  p.tiles_m = (m + tile_rows - 1) / tile_rows;
-  p.num_tiles = p.tiles_m * p.tiles_n;
-  // raster width (row tiles walked before the next column tile), measured on this part: 16 for the 256-row
-  // tiles of CTA pairs, 32 for single-CTA int8 tiles, 8 for single-CTA int4 tiles
-  p.group_m = v->group_m > 0 ? v->group_m : (tl.pair ? 16 : (int4 ? 8 : 32));
+  p.tile_cols = pl.tile_cols;
+  p.tiles_n = pl.tiles_n;
+  p.tiles_m = pl.tiles_m;
+  p.k_slices = pl.slices;
+  p.k_per_slice = pl.k_per_slice;
+  p.num_tiles = p.tiles_m * p.tiles_n * pl.slices;
+  p.group_m = pl.group_m;
   p.gate_col_offset = swiglu ? n : NBLK;
   p.ldc = n;
   p.subchannel = sc_mode == SCALE_SC ? v->subchannel : 0;
@@ -537,17 +581,28 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
   p.lds_b = b_cols;
   p.a_scale = static_cast<const __nv_bfloat16*>(a_scale);
   p.b_scale = static_cast<const __nv_bfloat16*>(b_scale);
-  p.out = c;
+  p.out = split ? workspace : c;
   p.status = dev->status_dev;
   CUtensorMap tc;
-  if (int rc = make_output_map(&tc, c, v->out_dtype, m, n, &p.tma_store); rc != 0) return rc;
-  const int cta_per_tile = tl.pair ? 2 : 1;
-  const int max_units = tl.pair ? dev->max_pair_clusters : dev->sm_count;  // tiles in flight
-  int grid = (p.num_tiles < max_units ? p.num_tiles : max_units) * cta_per_tile;
-  if (v->schedule == B200_SCHEDULE_STANDARD) grid = p.num_tiles * cta_per_tile;
-  int rc = launch_tc(tl, ta, tb, tc, p, grid, stream);
+  std::memset(&tc, 0, sizeof(tc));
+  if (!split) {
+    if (int rc = make_output_map(&tc, c, v->out_dtype, m, n, &p.tma_store); rc != 0) return rc;
+  }
+  int rc = launch_tc(pl.kernel, ta, tb, tc, p, pl.grid, stream);
   if (rc < 0) return fail("internal: no tcgen05 instantiation for this variant");
-  return rc;
+  if (rc != 0) return rc;
+  g_last_path = pl.kernel.pair ? B200_LAUNCHED_TCGEN05_PAIR : B200_LAUNCHED_TCGEN05;
+  if (split) {
+    const long long items = (n % 4 == 0) ? static_cast<long long>(m) * n / 4 : static_cast<long long>(m) * n;
+    long long blocks = (items + 255) / 256;
+    const long long cap = static_cast<long long>(dev->sm_count) * 16;
+    if (blocks > cap) blocks = cap;
+    splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        workspace, static_cast<float*>(c), p.a_scale, p.b_scale, m, n, pl.slices, pl.integer_partials ? 1 : 0);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return fail_cuda("split-K reduction kernel launch", err);
+  }
+  return 0;
 }
 
 namespace {
@@ -558,8 +613,9 @@ int launch_ragged_fwd_impl(
     const b200_gemm_variant* v, int device_index, uintptr_t stream_handle, const void* lhs,
     const void* rhs, const void* lhs_scale, const void* rhs_scale, const int64_t* task_group_ids,
     const int64_t* task_block_starts, const int64_t* task_actual_starts,
-    const int64_t* task_actual_ends, const int32_t* num_tasks_dev, void* out, int32_t m, int32_t n,
-    int32_t k_packed, int32_t scale_cols, int32_t num_tasks, int32_t groups, int32_t block_rows) {
+    const int64_t* task_actual_ends, const int32_t* num_tasks_dev, const int32_t* overflow_dev, void* out,
+    int32_t m, int32_t n, int32_t k_packed, int32_t scale_cols, int32_t num_tasks, int32_t groups,
+    int32_t block_rows) {
   if (int rc = check_variant(v); rc != 0) return rc;
   if (v->dtype != B200_DTYPE_INT4) return fail("ragged kernels take packed int4 operands");
   if (v->epilogue != B200_EPILOGUE_NONE) return fail("ragged kernels have no fused activation");
@@ -623,6 +679,7 @@ int launch_ragged_fwd_impl(
     sp.task_actual_ends = reinterpret_cast<const long long*>(task_actual_ends);
     sp.out = out;
     // with a device-side count the padding entries are empty tasks (actual_start == actual_end): no rows
+    g_last_path = B200_LAUNCHED_SIMT;
     return launch_simt(sp, block_rows, num_tasks, stream);
   }
 
@@ -657,6 +714,7 @@ int launch_ragged_fwd_impl(
   p.task_actual_starts = reinterpret_cast<const long long*>(task_actual_starts);
   p.task_actual_ends = reinterpret_cast<const long long*>(task_actual_ends);
   p.num_tasks_dev = num_tasks_dev;
+  p.overflow_dev = overflow_dev;
   p.a_scale = static_cast<const __nv_bfloat16*>(lhs_scale);
   p.b_scale = static_cast<const __nv_bfloat16*>(rhs_scale);
   p.out = out;
@@ -668,6 +726,7 @@ int launch_ragged_fwd_impl(
   const int grid = (p.num_tiles < max_units ? p.num_tiles : max_units) * cta_per_tile;
   int rc = launch_tc(tl, ta, tb, tc, p, grid, stream);
   if (rc < 0) return fail("internal: no tcgen05 instantiation for this variant");
+  if (rc == 0) g_last_path = tl.pair ? B200_LAUNCHED_TCGEN05_PAIR : B200_LAUNCHED_TCGEN05;
   return rc;
 }
 
@@ -680,22 +739,25 @@ extern "C" int b200_int4_gemms_launch_ragged_fwd(
     const int64_t* task_actual_ends, void* out, int32_t m, int32_t n, int32_t k_packed,
     int32_t scale_cols, int32_t num_tasks, int32_t groups, int32_t block_rows) {
   g_last_error.clear();
+  g_last_path = B200_LAUNCHED_NOTHING;
   return launch_ragged_fwd_impl(v, device_index, stream_handle, lhs, rhs, lhs_scale, rhs_scale, task_group_ids,
-                                task_block_starts, task_actual_starts, task_actual_ends, nullptr, out, m, n,
-                                k_packed, scale_cols, num_tasks, groups, block_rows);
+                                task_block_starts, task_actual_starts, task_actual_ends, nullptr, nullptr, out, m,
+                                n, k_packed, scale_cols, num_tasks, groups, block_rows);
 }
 
 extern "C" int b200_int4_gemms_launch_ragged_fwd_device_tasks(
     const b200_gemm_variant* v, int device_index, uintptr_t stream_handle, const void* lhs,
     const void* rhs, const void* lhs_scale, const void* rhs_scale, const int64_t* task_group_ids,
     const int64_t* task_block_starts, const int64_t* task_actual_starts,
-    const int64_t* task_actual_ends, const int32_t* num_tasks_dev, void* out, int32_t m, int32_t n,
-    int32_t k_packed, int32_t scale_cols, int32_t max_tasks, int32_t groups, int32_t block_rows) {
+    const int64_t* task_actual_ends, const int32_t* num_tasks_dev, const int32_t* overflow_dev, void* out,
+    int32_t m, int32_t n, int32_t k_packed, int32_t scale_cols, int32_t max_tasks, int32_t groups,
+    int32_t block_rows) {
   g_last_error.clear();
+  g_last_path = B200_LAUNCHED_NOTHING;
   if (num_tasks_dev == nullptr) return fail("num_tasks_dev must be non-null");
   return launch_ragged_fwd_impl(v, device_index, stream_handle, lhs, rhs, lhs_scale, rhs_scale, task_group_ids,
-                                task_block_starts, task_actual_starts, task_actual_ends, num_tasks_dev, out, m, n,
-                                k_packed, scale_cols, max_tasks, groups, block_rows);
+                                task_block_starts, task_actual_starts, task_actual_ends, num_tasks_dev, overflow_dev,
+                                out, m, n, k_packed, scale_cols, max_tasks, groups, block_rows);
 }
 
 extern "C" int b200_int4_gemms_group_info(int device_index, uintptr_t stream_handle, const int64_t* group_sizes,
@@ -835,6 +897,7 @@ int launch_ragged_bwd_impl(const b200_gemm_variant* v, int device_index, uintptr
     sp.group_sizes = reinterpret_cast<const long long*>(group_sizes);
     sp.group_starts = group_starts;
     sp.out = out;
+    g_last_path = B200_LAUNCHED_SIMT;
     return launch_simt(sp, m, groups, stream);
   }
 
@@ -879,6 +942,7 @@ int launch_ragged_bwd_impl(const b200_gemm_variant* v, int device_index, uintptr
   const int grid = (p.num_tiles < units ? p.num_tiles : units) * (tl.pair ? 2 : 1);
   int rc = launch_tc(tl, ta, tb, tc, p, grid, stream);
   if (rc < 0) return fail("internal: no tcgen05 instantiation for this variant");
+  if (rc == 0) g_last_path = tl.pair ? B200_LAUNCHED_TCGEN05_PAIR : B200_LAUNCHED_TCGEN05;
   return rc;
 }
 
@@ -898,6 +962,7 @@ extern "C" int b200_int4_gemms_launch_ragged_bwd(const b200_gemm_variant* v, int
                                                  void* out, int32_t m, int32_t n, int32_t k_packed,
                                                  int32_t scale_cols, int32_t groups) {
   g_last_error.clear();
+  g_last_path = B200_LAUNCHED_NOTHING;
   return launch_ragged_bwd_impl(v, device_index, stream_handle, lhs, rhs, lhs_scale, rhs_scale, group_sizes,
                                 nullptr, out, m, n, k_packed, scale_cols, groups);
 }
@@ -913,6 +978,7 @@ extern "C" int b200_int4_gemms_launch_ragged_bwd_flat(const b200_gemm_variant* v
                                                       void* out, void* workspace, size_t workspace_bytes,
                                                       int32_t m, int32_t n, int64_t tokens, int32_t groups) {
   g_last_error.clear();
+  g_last_path = B200_LAUNCHED_NOTHING;
   if (tokens <= 0 || groups <= 0) return fail("tokens and groups must be positive");
   if ((tokens + 1) / 2 > 0x7FFFFFFF) return fail("too many tokens for one launch");
   if (group_sizes == nullptr) return fail("ragged backward kernel pointers must be non-null");
@@ -966,9 +1032,10 @@ int ensure_static_scratch(int device_index, StaticScratchState** out) {
     err = cudaGetSymbolAddress(&address, g_static_group_starts);
     if (err != cudaSuccess) return fail_cuda("cudaGetSymbolAddress(static group-start scratch)", err);
     if (address == nullptr) return fail("static group-start scratch has no device address");
-    using Kernel = KernelTraits<true, true, true, SCALE_PC, EPI_NONE, OUT_F32, true, false>;
-    err = set_smem(gemm_i8_tcgen05_kernel<true, true, true, SCALE_PC, EPI_NONE, OUT_F32, true, false>, Kernel::kSmemBytes);
-    if (err != cudaSuccess) return fail_cuda("cudaFuncSetAttribute(max dynamic shared memory)", err);
+    // the one tensor-core kernel this entry point launches: same set-up and register check as ensure_device
+    const TcKernelInfo* kernel = tc_find(TcLaunch{true, true, true, true, SCALE_PC, EPI_NONE, OUT_F32, false});
+    if (kernel == nullptr) return fail("internal: the flat backward kernel is not part of this build");
+    if (int rc = prepare_kernel(*kernel); rc != 0) return rc;
     st.view.sm_count = sms;
     st.view.cc_major = major;
     st.view.max_pair_clusters = 0;  // this entry point never launches a CTA-pair kernel
@@ -993,6 +1060,7 @@ extern "C" int b200_int4_gemms_launch_ragged_bwd_flat_static(const b200_gemm_var
                                                              void* out, int32_t m, int32_t n, int64_t tokens,
                                                              int32_t groups) {
   g_last_error.clear();
+  g_last_path = B200_LAUNCHED_NOTHING;
   if (tokens <= 0 || groups <= 0) return fail("tokens and groups must be positive");
   if (groups > B200_STATIC_SCRATCH_MAX_GROUPS)
     return fail("the built-in scratch holds the starts of at most " + std::to_string(B200_STATIC_SCRATCH_MAX_GROUPS) +

@@ -60,6 +60,10 @@ struct GemmParams {
   int scale_cols;        // number of K-groups (subchannel) per row
   int lds_b;             // pitch (elements) of one b_scale K-group row
   int tma_store;         // 1: tmap_c describes the output and the epilogue may use TMA stores
+  // split-K (dense): slice s reduces k in [s * k_per_slice, min(K, (s + 1) * k_per_slice)) and writes its partial
+  // result to out + s * M * ldc (a [k_slices, M, N] workspace); a second kernel adds the slices in a fixed order
+  int k_slices;          // 1: no split
+  int k_per_slice;       // multiple of BK (and of the K-group length)
   // ragged
   int num_groups;
   int rows_per_group_a;  // rows of the stacked A map per group (bwd)
@@ -74,6 +78,7 @@ struct GemmParams {
   // nullptr: operands are stacked per group and padded to a common capacity.
   const long long* group_starts;
   const int* num_tasks_dev;      // fwd: task count left on the device by the task builder (nullptr: tiles_m)
+  const int* overflow_dev;       // fwd: the builder's "tasks did not fit" flag (nullptr: not checked)
   const __nv_bfloat16* a_scale;
   const __nv_bfloat16* b_scale;
   void* out;
@@ -84,6 +89,7 @@ struct TileWork {
   int a_x, a_y;      // TMA coordinates of the first A box of the tile (K block 0)
   int b_y;           // TMA row coordinate of the first B box
   int n0, n1;        // column origins of the two 128-wide B blocks
+  int kb0;           // first K block (split-K slices start past 0)
   int num_kb;        // K blocks to run
   int k_len;         // reduction length of this tile (bwd: group_sizes[g])
   int k_valid;       // number of valid k (masking, bwd); INT_MAX otherwise
@@ -105,11 +111,19 @@ __device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t, int 
   TileWork w;
   w.k_valid = 0x7FFFFFFF;
   w.k_first = 0;
+  w.kb0 = 0;
   w.out_off = 0;
   w.out_row_base = 0;
   w.sa_off = 0;
   w.sb_off = 0;
   if (p.mode == MODE_DENSE) {
+    // split-K: the slice is the slowest index of the tile list
+    int slice = 0;
+    if (p.k_slices > 1) {
+      const int per_slice = p.tiles_m * p.tiles_n;
+      slice = t / per_slice;
+      t -= slice * per_slice;
+    }
     // grouped raster: walk group_m row-tiles down before moving to the next column tile
     const int per_group = p.group_m * p.tiles_n;
     const int grp = t / per_group;
@@ -124,7 +138,19 @@ __device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t, int 
     w.n0 = nt * p.tile_cols;
     w.n1 = w.n0 + p.gate_col_offset;
     w.k_len = p.K;
-    w.num_kb = (p.K + BK - 1) / BK;
+    if (p.k_slices > 1) {
+      const int k0 = slice * p.k_per_slice;
+      w.kb0 = k0 / BK;
+      w.k_len = max(0, min(p.K - k0, p.k_per_slice));
+      w.out_off = static_cast<long long>(slice) * p.M * p.ldc;
+      w.out_row_base = slice * p.M;
+      if (p.subchannel) {
+        const int groups_per_slice = p.k_per_slice / p.subchannel;
+        w.sa_off = static_cast<long long>(slice) * groups_per_slice;
+        w.sb_off = static_cast<long long>(slice) * groups_per_slice * p.lds_b;
+      }
+    }
+    w.num_kb = (w.k_len + BK - 1) / BK;
     w.out_row0 = mt * RM + rank_rows;
     w.row_lo = w.out_row0;
     w.row_hi = min(p.M, w.out_row0 + BM);
@@ -141,8 +167,9 @@ __device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t, int 
     w.k_len = p.K;
     w.num_kb = (p.K + BK - 1) / BK;
     w.out_row0 = bs + rank_rows;
-    w.row_lo = static_cast<int>(p.task_actual_starts[task]);
-    w.row_hi = static_cast<int>(p.task_actual_ends[task]);
+    // task bounds come from the caller (or from the device-side builder): never trust them past the operand
+    w.row_lo = max(0, static_cast<int>(p.task_actual_starts[task]));
+    w.row_hi = min(p.M, static_cast<int>(p.task_actual_ends[task]));
     w.sb_off = static_cast<long long>(g) * p.lds_b * (p.subchannel ? p.scale_cols : 1);
   } else {
     const int per_g = p.tiles_m * p.tiles_n;
@@ -188,15 +215,6 @@ __device__ __forceinline__ void expand_word(uint32_t w, uint32_t& lo, uint32_t& 
 
 template <bool kInt4, bool kAMn, bool kBMn, int kScale, int kEpi, int kOut, bool kMaskK, bool k2Cta = false>
 struct KernelTraits {
-#ifndef B200_UNPACK_WARPS
-#define B200_UNPACK_WARPS 8
-#endif
-#ifndef B200_INT4_STAGES
-#define B200_INT4_STAGES 3
-#endif
-#ifndef B200_INT4_PK_STAGES
-#define B200_INT4_PK_STAGES 2
-#endif
   // K-masked kernels serve the grouped backward pass: short reductions (a group's tokens) and large fp32
   // tiles.  Their epilogue is the long pole, so it gets eight warps (two per TMEM lane quarter, half of the
   // columns each) and one of the operand stages as output staging.
@@ -205,7 +223,7 @@ struct KernelTraits {
   // warpgroups (4 consecutive warps): warps 0..3 = TMA, MMA and two idle warps, 4..11 = epilogue, then unpack
   // (4 warps next to the subchannel epilogue, whose running sums need 200 registers; 8 warps otherwise).
   static constexpr bool kRegBalance = (kScale == SCALE_SC) || kShortK;
-  static constexpr int kUnpackWarps = kInt4 ? ((kScale == SCALE_SC) ? 4 : B200_UNPACK_WARPS) : 0;
+  static constexpr int kUnpackWarps = kInt4 ? ((kScale == SCALE_SC) ? 4 : 8) : 0;
   static constexpr int kEpiWarps = kRegBalance ? 8 : 4;
   static constexpr int kEpiWarp0 = kRegBalance ? 4 : 2;
   static constexpr int kUnpackWarp0 = kEpiWarp0 + kEpiWarps;
@@ -221,26 +239,14 @@ struct KernelTraits {
   static constexpr bool kUnpackRaises = kRegsUnpack >= kCapRegs;
   // registers the CTA needs after the re-balance; the host checks this against regs-per-thread x threads
   static constexpr int kRegPoolNeeded = kRegBalance ? (128 * kRegsLight + 256 * kRegsEpilogue + kUnpackWarps * 32 * kRegsUnpack) : 0;
-#ifndef B200_INT8_STAGES
-#define B200_INT8_STAGES 4
-#endif
-#ifndef B200_PAIR_INT4_STAGES
-#define B200_PAIR_INT4_STAGES 4
-#endif
-#ifndef B200_PAIR_INT4_PK_STAGES
-#define B200_PAIR_INT4_PK_STAGES 4
-#endif
-#ifndef B200_PAIR_INT8_STAGES
-#define B200_PAIR_INT8_STAGES 6
-#endif
   // A CTA of a pair holds one 128-wide block of B (the MMA reads the other one from the peer), so
   // its stages are a third smaller and more of them fit.
   static constexpr int kBBlocks = k2Cta ? 1 : 2;
   static constexpr int kStages = kShortK ? (k2Cta ? 3 : 2)
-                                 : kInt4 ? (k2Cta ? B200_PAIR_INT4_STAGES : B200_INT4_STAGES)
-                                         : (k2Cta ? B200_PAIR_INT8_STAGES : B200_INT8_STAGES);  // int8 UMMA stages
+                                 : kInt4 ? (k2Cta ? 4 : 3)
+                                         : (k2Cta ? 6 : 4);  // int8 UMMA stages
   static constexpr int kPkStages =
-      kInt4 ? (k2Cta ? (kShortK ? 3 : B200_PAIR_INT4_PK_STAGES) : B200_INT4_PK_STAGES) : 0; // packed staging stages
+      kInt4 ? (k2Cta ? (kShortK ? 3 : 4) : 2) : 0; // packed staging stages
   static constexpr int kA8Bytes = BM * BK;                  // 16 KB
   static constexpr int kB8Bytes = kBBlocks * NBLK * BK;     // 32 KB (pair: 16 KB)
   static constexpr int kStageBytes = kA8Bytes + kB8Bytes;
@@ -265,13 +271,20 @@ struct KernelTraits {
   static_assert(kSmemBytes <= 232448, "over the 227 KB of shared memory a CTA can have");
 };
 
-template <bool kInt4, bool kAMn, bool kBMn, int kScale, int kEpi, int kOut, bool kMaskK, bool k2Cta = false>
+// kFastSc (subchannel kernels only): the order of roundings of the per-K-group accumulation.
+//   false: out += (f32(acc_g) * sa_g) * sb_g with every rounding of the reference (api.py:316-324): bit-identical;
+//   true : out = fma(f32(acc_g) * sa_g, sb_g, out): the last multiply and the add share one rounding, and the
+//          int -> float step costs nothing because the accumulators start from a bias in TMEM (see the epilogue).
+//          Two instructions per element and K-group instead of four; results differ from the reference in the
+//          last bits of the fp32 running sum, far inside the bf16 output tolerance.
+template <bool kInt4, bool kAMn, bool kBMn, int kScale, int kEpi, int kOut, bool kMaskK, bool k2Cta = false, bool kFastSc = false>
 __global__ void __launch_bounds__(KernelTraits<kInt4, kAMn, kBMn, kScale, kEpi, kOut, kMaskK, k2Cta>::kThreads, 1)
 gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b,
                        const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
   using T = KernelTraits<kInt4, kAMn, kBMn, kScale, kEpi, kOut, kMaskK, k2Cta>;
   static_assert(kBMn || !kMaskK, "K masking is applied to an MN-major B operand");
+  static_assert(!kFastSc || kScale == SCALE_SC, "the fused accumulation order belongs to the subchannel kernels");
   constexpr int S = T::kStages;
   constexpr int PS = T::kPkStages;
 
@@ -305,6 +318,13 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   AbortCtx ctx{abort_flag, p.status};
+  // a task list that did not fit its arrays leaves rows of the output unwritten: say so in the status word
+  if (p.overflow_dev != nullptr && blockIdx.x == 0 && threadIdx.x == 0 && *p.overflow_dev != 0 && p.status != nullptr &&
+      p.status[0] == STATUS_OK) {
+    p.status[1] = *p.num_tasks_dev;
+    p.status[2] = 0;
+    p.status[0] = STATUS_TASK_OVERFLOW;
+  }
   // per-epilogue-warp 2 KB staging buffer of the TMA store path (warps 2..5 -> slots 0..3)
   const int epi_slot = (warp - T::kEpiWarp0) & (T::kEpiWarps - 1);
   uint8_t* stage_out = smem_gen + S * T::kStageBytes + PS * T::kPkStageBytes + epi_slot * T::kStagingPerWarp;
@@ -359,7 +379,8 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       for (int t = tile0; t < num_tiles && ok; t += tile_step) {
         const TileWork w = decode_tile<kAMn, k2Cta>(p, t, cta_rank);
-        for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
+        for (int kbl = 0; kbl < w.num_kb; ++kbl, ++it) {
+          const int kb = kbl + w.kb0;  // K block of the whole reduction (a split-K slice starts past 0)
           if constexpr (kInt4) {
             const int s = it % PS;
             const uint32_t ph = (it / PS) & 1;
@@ -389,22 +410,12 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint32_t ph = (it / S) & 1;
             if (!mbar_wait(empty_bar(s), ph ^ 1u, ctx, 11)) { ok = false; break; }
             const uint32_t dst = stage_base + s * T::kStageBytes;
-#if defined(B200_DBG_SKIP_ALL_LOADS)
-            mbar_arrive(full_bar(s));
-            continue;
-#elif defined(B200_DBG_SKIP_B_LOAD)
-            mbar_arrive_expect_tx(full_bar(s), T::kA8Bytes);
-#else
             mbar_arrive_expect_tx(full_bar(s), T::kStageBytes);
-#endif
             if constexpr (kAMn) {
               tma_load_2d(dst, &tmap_a, w.a_x, w.a_y + kb * BK, full_bar(s));
             } else {
               tma_load_2d(dst, &tmap_a, w.a_x + kb * BK, w.a_y, full_bar(s));
             }
-#ifdef B200_DBG_SKIP_B_LOAD
-            continue;
-#endif
             const int nb0 = (k2Cta && cta_rank != 0) ? w.n1 : w.n0;
             if constexpr (kBMn) {
               tma_load_2d(dst + T::kA8Bytes, &tmap_b, nb0, w.b_y + kb * BK, full_bar(s));
@@ -494,7 +505,9 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     (kb | k) != 0 ? 1u : 0u);
             }
             commit(empty_bar(s));
+#ifndef B200_TEST_DROP_ACC_FULL_SIGNAL
             if (kb == w.num_kb - 1) commit(acc_full_bar(b));
+#endif
           }
           __syncwarp();
         }
@@ -510,7 +523,10 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const bool group_start = (kb % kb_per_group) == 0;
           const bool group_end = ((kb + 1) % kb_per_group) == 0 || kb == w.num_kb - 1;
           if (group_start) {
-            if (!__all_sync(0xFFFFFFFFu, wait_acc_empty(b, ((grp >> 1) & 1) ^ 1u))) { ok = false; break; }
+            // fused order: the epilogue warps arm both buffers before the first group, which is phase 0 of the
+            // "empty" barriers; otherwise the buffers start out free
+            const uint32_t free_parity = kFastSc ? ((grp >> 1) & 1) : (((grp >> 1) & 1) ^ 1u);
+            if (!__all_sync(0xFFFFFFFFu, wait_acc_empty(b, free_parity))) { ok = false; break; }
           }
           if (!__all_sync(0xFFFFFFFFu, wait_operands(s, ph))) { ok = false; break; }
           tc_fence_after_sync();
@@ -522,7 +538,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             for (int k = 0; k < BK / 32; ++k) {
               if (k < left)
                 mma(tmem_base + b * BN, make_desc(a_lo + k * kAStep), make_desc(b_lo + k * kBStep),
-                    (group_start && k == 0) ? 0u : 1u);
+                    (!kFastSc && group_start && k == 0) ? 0u : 1u);  // fused order: always onto the bias
             }
             commit(empty_bar(s));
             if (group_end) commit(acc_full_bar(b));
@@ -546,13 +562,14 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const int in_group = j % mma_per_group;
             const int b = grp & 1;
             if (in_group == 0) {
-              if (!__all_sync(0xFFFFFFFFu, mbar_wait(acc_empty_bar(b), ((grp >> 1) & 1) ^ 1u, ctx, 21))) { ok = false; break; }
+              const uint32_t free_parity = kFastSc ? ((grp >> 1) & 1) : (((grp >> 1) & 1) ^ 1u);
+              if (!__all_sync(0xFFFFFFFFu, mbar_wait(acc_empty_bar(b), free_parity, ctx, 21))) { ok = false; break; }
               tc_fence_after_sync();
             }
             const bool group_end = (in_group == mma_per_group - 1) || (j == total_mma - 1);
             if (elect_one()) {
               umma_i8(tmem_base + b * BN, make_desc(a_lo + k * kAStep), make_desc(b_lo + k * kBStep), idesc,
-                      in_group != 0 ? 1u : 0u);
+                      (kFastSc || in_group != 0) ? 1u : 0u);
               if (group_end) umma_commit(acc_full_bar(b));
             }
             __syncwarp();
@@ -582,6 +599,31 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     };
     int store_count = 0;  // TMA stores issued by this warp (selects the staging slot)
     bool ok = true;
+    // Fused order.  For |x| <= 2^22 the float with bit pattern 0x4B400000 + x is exactly 1.5 * 2^23 + x.  The
+    // accumulators therefore start from the integer 0x4B400000 instead of 0 (the tensor core adds the products onto
+    // whatever TMEM holds): what comes back from TMEM is already the float 1.5 * 2^23 + acc, no conversion, no
+    // integer add.  The epilogue warps write the bias: once into both buffers here, and again over every chunk
+    // they have read, before they hand the buffer back.
+    constexpr uint32_t kBiasBits = 0x4B400000u;
+    // first TMEM column of this warp's c-th 16-column chunk (the order of its running sums)
+    auto sc_chunk_col = [&](int c) -> int {
+      if constexpr (kEpi == EPI_SWIGLU) return (c < 4) ? (64 * half + 16 * c) : (NBLK + 64 * half + 16 * (c - 4));
+      else return 128 * half + 16 * c;
+    };
+    if constexpr (kFastSc) {
+#pragma unroll
+      for (int b = 0; b < 2; ++b) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) tmem_st_fill_32x32b_x16(tmem_base + lane_addr + b * BN + sc_chunk_col(c), kBiasBits);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        release_acc(0);
+        release_acc(1);
+      }
+    }
     // Columns of the 256-wide accumulator this warp owns:
     //   per-channel, 4 warps: all 256 (SwiGLU: up 0..127 with gate 128..255)
     //   subchannel, 8 warps : plain -> [128*half, +128); SwiGLU -> up [64*half,+64) with gate 128+[64*half,+64)
@@ -634,7 +676,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // dense output are clipped by the tensor map itself)
         const int wrow0 = w.out_row0 + q * 32;
         const bool use_tma = T::kTmaStore && p.tma_store != 0 &&
-                             (p.mode == MODE_DENSE || (wrow0 >= w.row_lo && wrow0 + 32 <= w.row_hi));
+                             ((p.mode == MODE_DENSE && p.k_slices == 1) || (wrow0 >= w.row_lo && wrow0 + 32 <= w.row_hi));
         const uint32_t acc_addr = tmem_base + lane_addr + b * BN;
 
         // one 32-column chunk: scale, activation, store
@@ -683,9 +725,6 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 v[i] = x * x;
               }
             }
-#ifdef B200_DBG_NO_STORE
-            if (v[0] == 123.456f)
-#endif
             if (use_tma) {
               // stage 32 rows in shared memory, then one TMA store writes whole lines; columns past N
               // are clipped by the tensor map.  bf16: 64 B per row, two 2 KB slots, 64-byte swizzle
@@ -798,11 +837,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         };
 
-#ifdef B200_DBG_SKIP_EPILOGUE
-        constexpr int kAllChunks = 0;
-#else
         constexpr int kAllChunks = (kEpi == EPI_SWIGLU) ? 4 : 8;
-#endif
         // with eight epilogue warps, the two warps of a lane quarter split the chunks between them
         constexpr int kOutChunks = kAllChunks / (T::kEpiWarps / 4);
         const int c_first = half * kOutChunks;
@@ -900,24 +935,52 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (!__all_sync(0xFFFFFFFFu, mbar_wait(acc_full_bar(b), (grp >> 1) & 1, ctx, 31))) { ok = false; break; }
           tc_fence_after_sync();
           const float csa = -(kMagic * sa);
+          if constexpr (kFastSc) {
+            // two register sets: the TMEM read of the next chunk is in flight while this one is accumulated
+            const uint32_t buf = tmem_base + lane_addr + b * BN;
+            uint32_t ra[16], rb[16];
+            tmem_ld_32x32b_x16(buf + sc_chunk_col(0), ra);
+            // packed fp32 (two elements per instruction): the stream is bound by issue slots, which it shares
+            // with the unpack warps, not by the fp32 pipe
+            const float2 sa2 = make_float2(sa, sa), csa2 = make_float2(csa, csa);
+            auto accumulate = [&](const uint32_t (&r)[16], int c) {
+#pragma unroll
+              for (int i4 = 0; i4 < 4; ++i4) {
+                const float4 s4 = *reinterpret_cast<const float4*>(strip + 16 * c + 4 * i4);  // broadcast read
+#pragma unroll
+                for (int h2 = 0; h2 < 2; ++h2) {
+                  const int j = 16 * c + 4 * i4 + 2 * h2;
+                  const float2 y = make_float2(__uint_as_float(r[4 * i4 + 2 * h2]), __uint_as_float(r[4 * i4 + 2 * h2 + 1]));
+                  const float2 sv = h2 == 0 ? make_float2(s4.x, s4.y) : make_float2(s4.z, s4.w);
+                  const float2 t2 = __ffma2_rn(y, sa2, csa2);                              // = acc * sa, one rounding
+                  const float2 sum = __ffma2_rn(t2, sv, make_float2(acc[j], acc[j + 1]));
+                  acc[j] = sum.x;
+                  acc[j + 1] = sum.y;
+                }
+              }
+            };
+#pragma unroll
+            for (int c = 0; c < kOwnCols / 16; c += 2) {
+              tmem_ld_wait();
+              tmem_ld_fence16(ra);
+              tmem_st_fill_32x32b_x16(buf + sc_chunk_col(c), kBiasBits);      // chunk c is in registers: re-arm it
+              tmem_ld_32x32b_x16(buf + sc_chunk_col(c + 1), rb);
+              accumulate(ra, c);
+              tmem_ld_wait();
+              tmem_ld_fence16(rb);
+              tmem_st_fill_32x32b_x16(buf + sc_chunk_col(c + 1), kBiasBits);
+              if (c + 2 < kOwnCols / 16) tmem_ld_32x32b_x16(buf + sc_chunk_col(c + 2), ra);
+              accumulate(rb, c + 1);
+            }
+            tmem_st_wait();
+          } else {
 #pragma unroll
           for (int c = 0; c < kOwnCols / 16; ++c) {
             // 16 columns at a time; accumulator columns of this warp in strip order
-            int tcol;
-            if constexpr (kEpi == EPI_SWIGLU) tcol = (c < 4) ? (64 * half + 16 * c) : (NBLK + 64 * half + 16 * (c - 4));
-            else tcol = 128 * half + 16 * c;
+            const int tcol = sc_chunk_col(c);
             uint32_t r[16];
-#ifdef B200_DBG_SC_NO_TMEM_LD
-#pragma unroll
-            for (int i = 0; i < 16; ++i) r[i] = tcol + i;
-#else
             tmem_ld_32x32b_x16(tmem_base + lane_addr + b * BN + tcol, r);
             tmem_ld_wait();
-#endif
-#ifdef B200_DBG_SC_NO_MATH
-            if (r[0] == 0x12345u) acc[16 * c] += 1.f;
-            if (true) continue;
-#endif
 #pragma unroll
             for (int i4 = 0; i4 < 4; ++i4) {
               const float4 s4 = *reinterpret_cast<const float4*>(strip + 16 * c + 4 * i4);  // broadcast read
@@ -930,6 +993,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               }
             }
           }
+          }
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) release_acc(b);
@@ -938,7 +1002,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // activation + store, 32 output columns at a time
         const int wrow0 = w.out_row0 + q * 32;
         const bool use_tma = T::kTmaStore && p.tma_store != 0 &&
-                             (p.mode == MODE_DENSE || (wrow0 >= w.row_lo && wrow0 + 32 <= w.row_hi));
+                             ((p.mode == MODE_DENSE && p.k_slices == 1) || (wrow0 >= w.row_lo && wrow0 + 32 <= w.row_hi));
         constexpr int kOutChunksSc = (kEpi == EPI_SWIGLU) ? 2 : 4;
 #pragma unroll
         for (int c = 0; c < kOutChunksSc; ++c) {
@@ -1135,6 +1199,13 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 
   // ------------------------------------------------------------------ teardown
+  // After a wait ran out some role may have left copies or MMAs in flight that target this CTA's shared
+  // memory or TMEM: give them time to land (they take microseconds) before the CTA's resources are released.
+  if (*abort_flag != 0) {
+    const unsigned long long t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < ABORT_DRAIN_NS) {
+    }
+  }
   tc_fence_before_sync();
   if constexpr (k2Cta) cluster_sync_all();  // the peer no longer touches this CTA's shared memory or TMEM
   else __syncthreads();

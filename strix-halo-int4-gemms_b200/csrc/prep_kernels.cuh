@@ -99,6 +99,56 @@ __global__ void repack_tokens_kernel(const uint8_t* __restrict__ src, uint8_t* _
   }
 }
 
+// Second pass of a split-K GEMM: adds the slices' partial results in ascending slice order, one thread per
+// four consecutive output columns (n a multiple of 4) or per single column.
+//   integer partials (per-channel scales): out = (f32(sum of s32 partials) * a_scale[row]) * b_scale[col]; the
+//     integer sum is exact, so the result equals the single-pass kernel's bit for bit;
+//   float partials (subchannel scales, already scaled per K-group inside each slice): out = ((p0 + p1) + p2) ...
+// Deterministic either way: no atomics, a fixed order.
+__global__ void splitk_reduce_kernel(const void* __restrict__ partials, float* __restrict__ out,
+                                     const __nv_bfloat16* __restrict__ a_scale,
+                                     const __nv_bfloat16* __restrict__ b_scale, long long rows, long long cols,
+                                     int slices, int integer_partials) {
+  const long long plane = rows * cols;
+  const bool vec = (cols % 4) == 0;
+  const long long items = vec ? plane / 4 : plane;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < items; i += stride) {
+    const long long e = vec ? 4 * i : i;
+    const long long row = e / cols;
+    const long long col = e - row * cols;
+    const int width = vec ? 4 : 1;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (integer_partials) {
+      int acc[4] = {0, 0, 0, 0};
+      const int* src = static_cast<const int*>(partials);
+      for (int s = 0; s < slices; ++s) {
+        if (vec) {
+          const int4 x = *reinterpret_cast<const int4*>(src + s * plane + e);
+          acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
+        } else {
+          acc[0] += src[s * plane + e];
+        }
+      }
+      const float sa = __bfloat162float(a_scale[row]);
+      for (int j = 0; j < width; ++j)
+        v[j] = __fmul_rn(__fmul_rn(static_cast<float>(acc[j]), sa), __bfloat162float(b_scale[col + j]));
+    } else {
+      const float* src = static_cast<const float*>(partials);
+      for (int s = 0; s < slices; ++s) {
+        if (vec) {
+          const float4 x = *reinterpret_cast<const float4*>(src + s * plane + e);
+          v[0] = __fadd_rn(v[0], x.x); v[1] = __fadd_rn(v[1], x.y); v[2] = __fadd_rn(v[2], x.z); v[3] = __fadd_rn(v[3], x.w);
+        } else {
+          v[0] = __fadd_rn(v[0], src[s * plane + e]);
+        }
+      }
+    }
+    if (vec) *reinterpret_cast<float4*>(out + e) = make_float4(v[0], v[1], v[2], v[3]);
+    else out[e] = v[0];
+  }
+}
+
 // Exclusive prefix sums of the group sizes: starts[g] = first token of group g, starts[groups] = total.
 // One CTA of 1024 threads; groups are scanned in slabs of 1024 with a running carry.
 __global__ void group_starts_kernel(const long long* __restrict__ sizes, long long* __restrict__ starts,
@@ -109,7 +159,7 @@ __global__ void group_starts_kernel(const long long* __restrict__ sizes, long lo
   __syncthreads();
   for (int base = 0; base < groups; base += 1024) {
     const int g = base + threadIdx.x;
-    const long long mine = g < groups ? sizes[g] : 0;
+    const long long mine = g < groups ? max(sizes[g], 0ll) : 0;
     slab[threadIdx.x] = mine;
     __syncthreads();
     for (int off = 1; off < 1024; off <<= 1) {  // Hillis-Steele inclusive scan
@@ -147,7 +197,7 @@ __global__ void group_info_kernel(const long long* __restrict__ sizes, int group
   __syncthreads();
   for (int base = 0; base < groups; base += 1024) {
     const int g = base + threadIdx.x;
-    const long long size = g < groups ? sizes[g] : 0;
+    const long long size = g < groups ? max(sizes[g], 0ll) : 0;  // negative sizes count as empty (reference ragged.py:244)
     slab_rows[threadIdx.x] = size;
     __syncthreads();
     for (int off = 1; off < 1024; off <<= 1) {

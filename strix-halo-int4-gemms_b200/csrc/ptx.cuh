@@ -13,7 +13,16 @@
 
 namespace b200 {
 
+// B200_TEST_WAIT_LIMIT_NS and B200_TEST_DROP_ACC_FULL_SIGNAL exist for ONE purpose: a test-only build of the
+// library (never the shipped one) in which the MMA warp of the per-channel kernels does not signal "accumulator
+// full", so that the epilogue's bounded wait runs out after a few milliseconds and the test can check that the
+// kernel returns, reports STATUS_WAIT_TIMEOUT with the wait site, and leaves the context usable.
+#ifdef B200_TEST_WAIT_LIMIT_NS
+constexpr unsigned long long WAIT_LIMIT_NS = B200_TEST_WAIT_LIMIT_NS;
+#else
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
+#endif
+constexpr unsigned long long ABORT_DRAIN_NS = 200000ull;     // 0.2 ms, after a wait ran out only
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -64,6 +73,7 @@ enum : int {
   STATUS_OK = 0,
   STATUS_WAIT_TIMEOUT = 1,
   STATUS_BAD_ARGUMENT = 2,
+  STATUS_TASK_OVERFLOW = 3,  // grouped forward: the device-built task list did not fit; status[1] = tasks kept
 };
 
 struct AbortCtx {
@@ -291,6 +301,37 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
         "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
+}
+// Each thread of the warp writes the same 32-bit value to 16 consecutive columns of its own TMEM lane.
+__device__ __forceinline__ void tmem_st_fill_32x32b_x16(uint32_t taddr, uint32_t v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
+      ::"r"(taddr), "r"(v)
+      : "memory");
+}
+// Each thread of the warp writes 32 registers to 32 consecutive columns of its own TMEM lane.
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+// tcgen05.st is asynchronous too: its writes are in TMEM only after tcgen05.wait::st.
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void tmem_ld_fence16(uint32_t (&r)[N]) {
+#pragma unroll
+  for (int i = 0; i < N; i += 8)
+    asm volatile("" : "+r"(r[i]), "+r"(r[i + 1]), "+r"(r[i + 2]), "+r"(r[i + 3]), "+r"(r[i + 4]), "+r"(r[i + 5]),
+                      "+r"(r[i + 6]), "+r"(r[i + 7])::"memory");
 }
 // tcgen05.ld is asynchronous: its destination registers are valid only after tcgen05.wait::ld.  When
 // other work is placed between the load and the wait, this empty statement (after the wait) ties the

@@ -59,8 +59,8 @@ __global__ void gemm_simt_kernel(const SimtParams p) {
   const int sc = (p.scale_mode == SCALE_SC) ? p.scale_cols : 1;
   if (p.mode == MODE_RAGGED_FWD) {
     const int task = blockIdx.z;
-    const int lo = static_cast<int>(p.task_actual_starts[task]);
-    const int hi = static_cast<int>(p.task_actual_ends[task]);
+    const int lo = max(0, static_cast<int>(p.task_actual_starts[task]));
+    const int hi = min(p.M, static_cast<int>(p.task_actual_ends[task]));
     row += lo;
     if (row >= hi) return;
     g = static_cast<int>(p.task_group_ids[task]);

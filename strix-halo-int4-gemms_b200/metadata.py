@@ -5,12 +5,19 @@ Mirrors the names and values of the reference's ``metadata.py`` (enums at :19-60
 against the reference keeps working; what the fields *mean* is re-keyed to the sm_100a kernels:
 
 * ``ARCH`` is ``"sm_100a"``;
-* ``TileConfig.block_m / block_n / block_k`` are the shape multiples a variant is registered
-  for.  Every variant runs on the same 128 x 256 x 128 UMMA tile, which masks partial tiles;
-* ``num_warps`` is the real CTA size in warps, ``num_stages`` the depth of the shared-memory
-  operand pipeline, ``group_size_m`` the raster swizzle width, ``waves_per_eu`` is kept for
-  signature compatibility and always 0;
-* ``KernelSchedule.STANDARD`` launches one CTA per output tile, ``PERSISTENT`` one CTA per SM.
+* ``KernelSchedule`` names the launch form, which is what distinguishes one entry's launch from
+  another's: ``STANDARD`` is the library's own choice for the shape (persistent grid; a CTA pair
+  per 256-row tile when that pays, else one CTA per 128-row tile), ``PERSISTENT`` forces one CTA
+  per tile on a persistent grid, ``PERSISTENT_2CTA`` forces CTA pairs (``tcgen05 cta_group::2``),
+  ``TILE_PER_CTA`` launches one CTA per output tile like a plain non-persistent kernel;
+* ``TileConfig.block_m / block_n`` are the rows and columns an entry's shapes must be multiples
+  of: the output tile of the forced forms (128 or 256 rows, 256 columns, 128 for SwiGLU), and for
+  ``STANDARD`` entries also the smaller row multiples the kernel accepts by masking a partial
+  tile; ``block_k`` is the K multiple (32, the K of one ``tcgen05.mma kind::i8``);
+* ``group_size_m`` is the raster width in row tiles passed to the launch (0: the library's default
+  for the form), ``split_k`` the number of K slices (a real split with a second reduction kernel),
+  ``num_warps`` the CTA size in warps, ``num_stages`` the depth of the shared-memory operand
+  pipeline of the single-CTA form; ``waves_per_eu`` is kept for signature compatibility and always 0.
 """
 from __future__ import annotations
 
@@ -61,6 +68,8 @@ SUPPORTED_GEMM_LAYOUTS = (GemmLayout.NN, GemmLayout.NT, GemmLayout.TN)
 class KernelSchedule(str, enum.Enum):
     STANDARD = "standard"
     PERSISTENT = "persistent"
+    PERSISTENT_2CTA = "persistent_2cta"
+    TILE_PER_CTA = "tile_per_cta"
 
 
 class KernelStatus(str, enum.Enum):

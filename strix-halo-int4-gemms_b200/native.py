@@ -12,7 +12,6 @@ a CUDA device, the launchers raise.
 from __future__ import annotations
 
 import ctypes
-import os
 import threading
 from dataclasses import dataclass
 from pathlib import Path
@@ -29,8 +28,34 @@ LAYOUT_CODES = {GemmLayout.NN: 0, GemmLayout.NT: 1, GemmLayout.TN: 2, GemmLayout
 EPILOGUE_CODES = {Epilogue.NONE: 0, Epilogue.RELU2: 1, Epilogue.SWIGLU: 2}
 OUT_BF16, OUT_F32, OUT_S32 = 0, 1, 2
 PATH_AUTO, PATH_TCGEN05, PATH_SIMT = 0, 1, 2
-SCHEDULE_PERSISTENT, SCHEDULE_STANDARD = 0, 1
+SCHEDULE_PERSISTENT, SCHEDULE_TILE_PER_CTA = 0, 1
 CTA_GROUP_AUTO, CTA_GROUP_SINGLE, CTA_GROUP_PAIR = 0, 1, 2
+LAUNCHED_NOTHING, LAUNCHED_TCGEN05, LAUNCHED_TCGEN05_PAIR, LAUNCHED_SIMT = 0, 1, 2, 3
+ACCUMULATE_FUSED, ACCUMULATE_REFERENCE = 0, 1
+
+# Order of roundings of subchannel dense launches made through the registry / public API: "fused" (default; the
+# last multiply and the add of each K-group share one rounding) or "reference" (every rounding of the reference's
+# PyTorch math: bit-identical to it, about a third slower on large problems).  See ``accumulation_order``.
+_ACCUMULATION_ORDER = ACCUMULATE_FUSED
+
+
+class accumulation_order:
+    """Context manager (or plain call) that sets the order for subchannel dense launches of this process:
+    ``with accumulation_order("reference"): mm(...)``."""
+
+    def __init__(self, order: str) -> None:
+        global _ACCUMULATION_ORDER
+        if order not in ("fused", "reference"):
+            raise ValueError("order must be 'fused' or 'reference'")
+        self._previous = _ACCUMULATION_ORDER
+        _ACCUMULATION_ORDER = ACCUMULATE_REFERENCE if order == "reference" else ACCUMULATE_FUSED
+
+    def __enter__(self) -> "accumulation_order":
+        return self
+
+    def __exit__(self, *exc: object) -> None:
+        global _ACCUMULATION_ORDER
+        _ACCUMULATION_ORDER = self._previous
 
 EXPORTED_SYMBOLS = (
     "b200_int4_gemms_dispatch_version",
@@ -42,6 +67,8 @@ EXPORTED_SYMBOLS = (
     "b200_int4_gemms_reset_device_status",
     "b200_int4_gemms_launch_dense",
     "b200_int4_gemms_dense_workspace_bytes",
+    "b200_int4_gemms_plan_dense",
+    "b200_int4_gemms_last_launch_path",
     "b200_int4_gemms_launch_ragged_fwd",
     "b200_int4_gemms_launch_ragged_bwd",
     "b200_int4_gemms_unpack_int4",
@@ -70,8 +97,26 @@ class GemmVariant(ctypes.Structure):
         ("group_m", ctypes.c_int32),
         ("schedule", ctypes.c_int32),
         ("cta_group", ctypes.c_int32),
-        ("reserved", ctypes.c_int32 * 5),
+        ("accumulate_order", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 4),
     ]
+
+
+class DensePlan(ctypes.Structure):
+    """``b200_dense_plan`` of include/b200_int4_gemms.h: what a dense launch would do."""
+
+    _fields_ = [
+        ("path", ctypes.c_int32),
+        ("grid", ctypes.c_int32),
+        ("tile_rows", ctypes.c_int32),
+        ("tile_cols", ctypes.c_int32),
+        ("group_m", ctypes.c_int32),
+        ("split_k", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 2),
+    ]
+
+    def as_tuple(self) -> tuple[int, int, int, int, int, int]:
+        return (int(self.path), int(self.grid), int(self.tile_rows), int(self.tile_cols), int(self.group_m), int(self.split_k))
 
 
 @dataclass(frozen=True, slots=True)
@@ -119,6 +164,10 @@ def _declare(library: ctypes.CDLL) -> None:
     ]
     library.b200_int4_gemms_dense_workspace_bytes.restype = size_t
     library.b200_int4_gemms_dense_workspace_bytes.argtypes = [variant_p, i32, i32, i32]
+    library.b200_int4_gemms_plan_dense.restype = ctypes.c_int
+    library.b200_int4_gemms_plan_dense.argtypes = [variant_p, ctypes.c_int, i32, i32, i32, ctypes.POINTER(DensePlan)]
+    library.b200_int4_gemms_last_launch_path.restype = ctypes.c_int
+    library.b200_int4_gemms_last_launch_path.argtypes = []
     library.b200_int4_gemms_launch_ragged_fwd.restype = ctypes.c_int
     library.b200_int4_gemms_launch_ragged_fwd.argtypes = [variant_p, ctypes.c_int, size_t] + [void_p] * 9 + [i32] * 7
     library.b200_int4_gemms_launch_ragged_bwd.restype = ctypes.c_int
@@ -128,7 +177,7 @@ def _declare(library: ctypes.CDLL) -> None:
     library.b200_int4_gemms_group_info.restype = ctypes.c_int
     library.b200_int4_gemms_group_info.argtypes = [ctypes.c_int, size_t, void_p, i32, i32, i32] + [void_p] * 4 + [i32, void_p, void_p]
     library.b200_int4_gemms_launch_ragged_fwd_device_tasks.restype = ctypes.c_int
-    library.b200_int4_gemms_launch_ragged_fwd_device_tasks.argtypes = [variant_p, ctypes.c_int, size_t] + [void_p] * 10 + [i32] * 7
+    library.b200_int4_gemms_launch_ragged_fwd_device_tasks.argtypes = [variant_p, ctypes.c_int, size_t] + [void_p] * 11 + [i32] * 7
     library.b200_int4_gemms_ragged_bwd_flat_workspace_bytes.restype = size_t
     library.b200_int4_gemms_ragged_bwd_flat_workspace_bytes.argtypes = [i32]
     library.b200_int4_gemms_launch_ragged_bwd_flat.restype = ctypes.c_int
@@ -275,18 +324,29 @@ def _validate_scale_shapes(kernel: KernelMetadata, *, m: int, n: int, k: int, a_
 
 
 def launch_grid(kernel: KernelMetadata, m: int, n: int, *, num_sms: int = 148) -> tuple[int, int, int]:
-    """Grid the library uses for a dense launch: one CTA per 128 x 256 tile (x 128 columns for
-    SwiGLU), capped at the SM count for the persistent schedule.  Informational: the library
-    sizes the grid itself (the reference computed it in Python, native.py:306-332)."""
+    """Grid of a dense launch of ``kernel`` when every SM (pair of SMs) can hold a CTA (pair): informational,
+    computed from the entry alone.  The library sizes the grid itself (``plan_dense`` asks it; the reference
+    computed it in Python, native.py:306-332).  A ``STANDARD`` entry is counted in its single-CTA form."""
     tile_cols = 128 if kernel.epilogue is Epilogue.SWIGLU else 256
-    tiles = -(-m // 128) * -(-n // tile_cols)
-    if kernel.schedule is KernelSchedule.PERSISTENT:
-        return (min(num_sms, tiles), 1, 1)
-    return (tiles, 1, 1)
+    pair = kernel.schedule is KernelSchedule.PERSISTENT_2CTA
+    tile_rows, ctas = (256, 2) if pair else (128, 1)
+    tiles = -(-m // tile_rows) * -(-n // tile_cols) * kernel.tile.split_k
+    if kernel.schedule is KernelSchedule.TILE_PER_CTA:
+        return (tiles * ctas, 1, 1)
+    return (min(num_sms // ctas, tiles) * ctas, 1, 1)
 
 
 def block_size(kernel: KernelMetadata) -> int:
     return kernel.tile.num_warps * THREADS_PER_WARP
+
+
+SCHEDULE_LAUNCH = {
+    # registry launch form -> (schedule, cta_group) of the C variant record
+    KernelSchedule.STANDARD: (SCHEDULE_PERSISTENT, CTA_GROUP_AUTO),
+    KernelSchedule.PERSISTENT: (SCHEDULE_PERSISTENT, CTA_GROUP_SINGLE),
+    KernelSchedule.PERSISTENT_2CTA: (SCHEDULE_PERSISTENT, CTA_GROUP_PAIR),
+    KernelSchedule.TILE_PER_CTA: (SCHEDULE_TILE_PER_CTA, CTA_GROUP_SINGLE),
+}
 
 
 def make_variant(
@@ -299,9 +359,12 @@ def make_variant(
     split_k: int = 1,
     path: int = PATH_AUTO,
     group_m: int = 0,
-    schedule: KernelSchedule = KernelSchedule.PERSISTENT,
-    cta_group: int = CTA_GROUP_AUTO,
+    schedule: KernelSchedule = KernelSchedule.STANDARD,
+    cta_group: int | None = None,
+    accumulate_order: int | None = None,
 ) -> GemmVariant:
+    """The C variant record of one launch.  ``schedule`` is the registry's launch form; ``cta_group``
+    (CTA_GROUP_*) overrides the form's CTA choice when given."""
     variant = GemmVariant()
     variant.dtype = DTYPE_CODES[dtype]
     variant.layout = LAYOUT_CODES[layout]
@@ -312,13 +375,53 @@ def make_variant(
     variant.split_k = int(split_k)
     variant.path = int(path)
     variant.group_m = int(group_m)
-    variant.schedule = SCHEDULE_STANDARD if schedule is KernelSchedule.STANDARD else SCHEDULE_PERSISTENT
-    # B200_INT4_GEMMS_CTA_GROUP=1|2 overrides an AUTO choice (A/B measurements of the single-CTA and
-    # CTA-pair kernels without touching call sites); an explicit argument wins.
-    if int(cta_group) == CTA_GROUP_AUTO and os.environ.get("B200_INT4_GEMMS_CTA_GROUP", "") in ("1", "2"):
-        cta_group = int(os.environ["B200_INT4_GEMMS_CTA_GROUP"])
-    variant.cta_group = int(cta_group)
+    variant.schedule, form_cta_group = SCHEDULE_LAUNCH[schedule]
+    variant.cta_group = int(form_cta_group if cta_group is None else cta_group)
+    variant.accumulate_order = int(_ACCUMULATION_ORDER if accumulate_order is None else accumulate_order)
     return variant
+
+
+def variant_for_kernel(kernel: KernelMetadata, *, out_dtype: int, path: int = PATH_AUTO) -> GemmVariant:
+    """The variant record a registry entry launches with: its form, raster width and split factor."""
+    return make_variant(
+        dtype=kernel.a_dtype, layout=kernel.layout, scale=kernel.scale, epilogue=kernel.epilogue, out_dtype=out_dtype,
+        split_k=kernel.tile.split_k, path=path, group_m=kernel.tile.group_size_m, schedule=kernel.schedule,
+    )
+
+
+def plan_dense(variant: GemmVariant, *, m: int, n: int, k: int, device_index: int = 0,
+               library_path: str | Path | None = None) -> DensePlan:
+    """What ``launch_dense`` would do for the variant and shape on the device (needs a CUDA device)."""
+    library = load_dispatch_library(library_path)
+    plan = DensePlan()
+    rc = library.b200_int4_gemms_plan_dense(ctypes.byref(variant), int(device_index), int(m), int(n), int(k), ctypes.byref(plan))
+    if rc != 0:
+        raise RuntimeError(_library_last_error(library))
+    return plan
+
+
+def last_launch_path(*, library_path: str | Path | None = None) -> int:
+    """LAUNCHED_* of the calling thread's most recent launch call."""
+    return int(load_dispatch_library(library_path).b200_int4_gemms_last_launch_path())
+
+
+_SLOW_PATH_WARNED: set[str] = set()
+
+
+def _warn_if_cuda_core_path(library: ctypes.CDLL, what: str, requested_path: int = PATH_AUTO) -> None:
+    """The reference raises where it has no kernel (api.py:136-138); this library has a CUDA-core kernel for
+    the shapes and layouts its tensor-core kernel does not take.  It is correct and very slow: say so once."""
+    if requested_path == PATH_SIMT or what in _SLOW_PATH_WARNED:
+        return
+    if int(library.b200_int4_gemms_last_launch_path()) != LAUNCHED_SIMT:
+        return
+    _SLOW_PATH_WARNED.add(what)
+    import warnings
+
+    warnings.warn(
+        f"{what} ran on the CUDA-core kernel (no tensor cores): the tensor-core kernel needs 16-byte aligned operands "
+        "and pitches and does not cover this layout / scale combination; pass path=PATH_TCGEN05 to fail instead",
+        RuntimeWarning, stacklevel=3)
 
 
 def launch_dense(
@@ -349,6 +452,27 @@ def launch_dense(
     )
     if rc != 0:
         raise RuntimeError(_library_last_error(library))
+    _warn_if_cuda_core_path(library, "a dense GEMM", int(variant.path))
+
+
+def dense_workspace(variant: GemmVariant, *, m: int, n: int, k: int, device: Any, stream_handle: int,
+                    library_path: str | Path | None = None) -> tuple[int, int]:
+    """(pointer, bytes) of the split-K scratch for a launch; (0, 0) when the variant needs none.  The buffer is
+    kept per (device, stream): launches that share it run in stream order and so never overlap."""
+    library = load_dispatch_library(library_path)
+    need = int(library.b200_int4_gemms_dense_workspace_bytes(ctypes.byref(variant), int(m), int(n), int(k)))
+    if need == 0:
+        return 0, 0
+    torch = _torch()
+    key = (int(device.index or 0), int(stream_handle), "dense_split_k")
+    with _WORKSPACES_LOCK:
+        scratch = _WORKSPACES.get(key)
+        if scratch is None or scratch.numel() < need:
+            if scratch is not None:
+                _RETIRED_WORKSPACES.append(scratch)
+            scratch = torch.empty(need, dtype=torch.uint8, device=device)
+            _WORKSPACES[key] = scratch
+    return int(scratch.data_ptr()), int(scratch.numel())
 
 
 def launch_generated_kernel(
@@ -401,21 +525,14 @@ def launch_generated_kernel(
     LaunchShape(m, n, k).validate_for(kernel)
     _validate_scale_shapes(kernel, m=m, n=n, k=k, a_scale=a_scale, b_scale=b_scale)
 
-    variant = make_variant(
-        dtype=kernel.a_dtype,
-        layout=kernel.layout,
-        scale=kernel.scale,
-        epilogue=kernel.epilogue,
-        out_dtype=OUT_F32 if want_dtype is torch.float32 else OUT_BF16,
-        split_k=kernel.tile.split_k,
-        path=path,
-        group_m=0,  # the library picks the raster width per kernel form; the registry's gm label is descriptive
-        schedule=kernel.schedule,
-    )
+    variant = variant_for_kernel(kernel, out_dtype=OUT_F32 if want_dtype is torch.float32 else OUT_BF16, path=path)
+    stream_handle = _stream_handle(torch, a, stream)
+    workspace_ptr, workspace_bytes = dense_workspace(variant, m=m, n=n, k=k, device=a.device, stream_handle=stream_handle,
+                                                     library_path=library_path)
     launch_dense(
         variant,
         device_index=_device_index(a),
-        stream_handle=_stream_handle(torch, a, stream),
+        stream_handle=stream_handle,
         a_ptr=a.data_ptr(),
         b_ptr=b.data_ptr(),
         a_scale_ptr=a_scale.data_ptr(),
@@ -424,6 +541,8 @@ def launch_generated_kernel(
         m=m,
         n=n,
         k=k,
+        workspace_ptr=workspace_ptr,
+        workspace_bytes=workspace_bytes,
         library_path=library_path,
     )
     return c
@@ -508,17 +627,21 @@ def launch_ragged_fwd_kernel(
     )
     sizes = (int(rows), int(cols), int(k_packed), int(scale_cols), int(group_info.num_tasks), groups, int(config.block_m))
     device_count = getattr(group_info, "device_num_tasks", None)
+    device_overflow = getattr(group_info, "device_overflow", None)
     if device_count is not None:
         # tasks built on the device: num_tasks is the capacity of the arrays, the real count stays on the GPU
         rc = library.b200_int4_gemms_launch_ragged_fwd_device_tasks(
             ctypes.byref(record), _device_index(lhs), _stream_handle(torch, lhs, stream), *operands, *task_arrays,
-            ctypes.c_void_p(device_count.data_ptr()), ctypes.c_void_p(out.data_ptr()), *sizes)
+            ctypes.c_void_p(device_count.data_ptr()),
+            ctypes.c_void_p(device_overflow.data_ptr() if device_overflow is not None else 0),
+            ctypes.c_void_p(out.data_ptr()), *sizes)
     else:
         rc = library.b200_int4_gemms_launch_ragged_fwd(
             ctypes.byref(record), _device_index(lhs), _stream_handle(torch, lhs, stream), *operands, *task_arrays,
             ctypes.c_void_p(out.data_ptr()), *sizes)
     if rc != 0:
         raise RuntimeError(_library_last_error(library))
+    _warn_if_cuda_core_path(library, f"a grouped forward dot (layout {layout.value})", path)
     return out
 
 
@@ -555,8 +678,10 @@ def launch_ragged_bwd_kernel(
     if library_path is None and root is not None:
         library_path = native_library_path(root=root)
     library = load_dispatch_library(library_path)
+    pair_tiles = getattr(config, "pair_tiles", None)
     record = make_variant(
         dtype=OperandDType.INT4, layout=layout, scale=scale, epilogue=Epilogue.NONE, out_dtype=OUT_F32, path=path,
+        cta_group=CTA_GROUP_AUTO if pair_tiles is None else (CTA_GROUP_PAIR if pair_tiles else CTA_GROUP_SINGLE),
     )
     groups = int(lhs.shape[0])
     if groups == 0 or rows == 0 or cols == 0:
@@ -570,6 +695,7 @@ def launch_ragged_bwd_kernel(
     )
     if rc != 0:
         raise RuntimeError(_library_last_error(library))
+    _warn_if_cuda_core_path(library, f"a grouped backward dot (layout {layout.value})", path)
     return out
 
 

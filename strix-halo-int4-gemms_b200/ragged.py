@@ -45,7 +45,7 @@ class RaggedDotConfig:
     align_tile: int = 8
     group_size_tasks: int = 1
     enable_even_k_fast_path: bool = True
-    num_warps: int = 10
+    num_warps: int = 14   # TMA + MMA + 4 epilogue + 8 unpack warps of the per-channel kernel
     num_stages: int = 3
     # None: 128-row tasks are widened to 256 rows (CTA pairs) when the groups are large enough and
     # the kernel supports it for the call; False: never; True: whenever the kernel supports it.
@@ -73,15 +73,19 @@ class RaggedBwdDotConfig:
 
     ``split_k`` is accepted for compatibility.  Every output tile is reduced by a single CTA
     in a fixed order, so results are deterministic and identical for every ``split_k``.
+    ``pair_tiles``: None lets the library run 256-row tiles on CTA pairs when M is a multiple of 256
+    and a paired kernel exists, False keeps one CTA per 128-row tile, True asks for pairs (one CTA
+    per tile where no paired kernel applies).  Results are bit-identical either way.
     """
 
     block_m: int = 128
     block_n: int = 256
     block_k: int = 128
     split_k: int = 1
-    num_warps: int = 10
-    num_stages: int = 3
+    num_warps: int = 20   # TMA / MMA warpgroup + 8 epilogue + 8 unpack warps of the K-masked kernel
+    num_stages: int = 2
     enable_even_k_fast_path: bool = True
+    pair_tiles: bool | None = None
 
     def __post_init__(self) -> None:
         if min(self.block_m, self.block_n, self.block_k) <= 0:
@@ -109,6 +113,10 @@ class RaggedGroupInfo:
     # (``num_tasks`` is then the capacity of the arrays) and a flag that is 1 when the capacity was too small
     device_num_tasks: Any | None = None
     device_overflow: Any | None = None
+    # the block height and alignment the tasks were cut with (None for records built by older callers);
+    # ragged_dot_int4 launches prebuilt tasks with this height, whatever its config says
+    tile: int | None = None
+    align_tile: int | None = None
 
 
 def _torch() -> Any:
@@ -206,7 +214,7 @@ def calculate_group_info(
     def blank(length: int, num_tasks: int, *, zero: bool) -> RaggedGroupInfo:
         make = torch.zeros if zero else torch.empty
         fields = [make((length,), **i64) for _ in range(6)]
-        return RaggedGroupInfo(*fields, num_tasks=num_tasks)
+        return RaggedGroupInfo(*fields, num_tasks=num_tasks, tile=int(tile), align_tile=int(align_tile))
 
     if groups == 0:
         return blank(tid_size or 0, 0, zero=True)
@@ -244,6 +252,8 @@ def calculate_group_info(
         start_within_block=keep(actual_start - block_start),
         actual_size=keep((actual_end - actual_start).clamp_min(0)),
         num_tasks=num_tasks,
+        tile=int(tile),
+        align_tile=int(align_tile),
     )
 
 
@@ -421,7 +431,11 @@ def ragged_dot_int4(
 
     ``group_info`` (not in the reference) lets a caller who reuses the same ``group_sizes`` pass
     the prebuilt task arrays and skip the two host synchronisations of validation and task
-    building.
+    building.  The tasks run with the block height they were built with (``group_info.tile``).  For
+    tasks built on the device nothing about them is read on the host: the kernel clamps task bounds to
+    the operand, and a task list that overflowed its arrays is reported after the fact through
+    ``native.device_status()`` (code 3) and ``group_info.device_overflow`` - rows of the tasks that did
+    not fit stay unwritten, so size ``max_tasks`` by the documented bound.
     """
     layout = _check_layout(layout)
     torch = _torch()
@@ -449,6 +463,15 @@ def ragged_dot_int4(
         scale.mode is ScaleMode.PER_CHANNEL or (scale.subchannel_size or 0) >= 128)
     if config.block_m > 128 and not pair_capable:
         raise ValueError("tasks of more than 128 rows need layout NN and per-channel scales or K-groups of at least 128")
+    if group_info is not None and group_info.tile is not None and group_info.tile != config.block_m:
+        # prebuilt tasks carry their own height: a launch with another one would skip rows of every block
+        if config.block_m != RaggedDotConfig().block_m:
+            raise ValueError(
+                f"group_info was built with tile={group_info.tile} but config.block_m={config.block_m}; "
+                "build the tasks with the block height of the config (or leave block_m at its default)")
+        if group_info.tile > 128 and not pair_capable:
+            raise ValueError("tasks of more than 128 rows need layout NN and per-channel scales or K-groups of at least 128")
+        config = replace(config, block_m=int(group_info.tile))
     if group_info is None and config.block_m == 128 and pair_capable and config.pair_tasks is not False:
         if config.pair_tasks is True or rows >= PAIR_MIN_MEAN_GROUP_ROWS * groups:
             if PAIR_TASK_ROWS % config.align_tile == 0:
@@ -683,7 +706,7 @@ def calculate_group_info_on_device(
     return RaggedGroupInfo(
         group_id=gid, block_start=bstart, actual_start=astart, actual_end=aend,
         start_within_block=astart - bstart, actual_size=aend - astart, num_tasks=max(capacity, 1),
-        device_num_tasks=count, device_overflow=overflow,
+        device_num_tasks=count, device_overflow=overflow, tile=int(tile), align_tile=int(align_tile),
     )
 
 

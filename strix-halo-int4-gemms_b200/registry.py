@@ -2,15 +2,22 @@
 
 Same surface as the reference's ``registry.py`` (``KernelRegistry.register/get/all/select/
 select_reference/with_status`` :254-349, ``default_registry`` :352, ``seed_tile_configs`` :112,
-``iter_supported_kernel_metadata`` :202) with the variant matrix re-keyed to this library:
+``iter_supported_kernel_metadata`` :202) with the variant matrix re-keyed to what this library can
+launch differently.  An entry names, besides its cell (operand type, scale spec, epilogue, layout):
 
-    2 operand types x 5 scale specs x 3 layouts x 2 schedules x 88 tile records = 5280 entries
+* the launch form (``KernelSchedule``): ``STANDARD`` = the library's own choice for the shape,
+  ``PERSISTENT`` = one CTA per 128-row tile, ``PERSISTENT_2CTA`` = a CTA pair per 256-row tile
+  (only for the cells that have a paired kernel), ``TILE_PER_CTA`` = one CTA per tile without the
+  persistent grid;
+* the raster width ``group_size_m`` handed to the launch (0 = the library's default for the form);
+* the split-K factor (plain epilogue only, and only where the library has the partial-sum kernel);
+* the shape multiples it accepts (``block_m``, ``block_n``, ``block_k``).
 
-A tile record names the shape multiples it is registered for (rows 128/64/32/16, columns
-256/128, K step 32), the split-K factor (plain epilogue only), and whether K must be a
-multiple of ``block_k * split_k`` (``evenk``) or not (``maskk``).  Selection keeps the
-reference's rule: among even-K entries whose multiples divide the shape, take the one with
-the best measured TOPS, ties broken by the largest ``block_m * block_n``.
+``STANDARD`` entries also come with smaller row multiples (64 / 32 / 16 rows, 128 columns): the same
+launch, accepted for shapes that leave the last tile partly empty.  Selection keeps the reference's
+rule: among even-K entries of the requested schedule whose multiples divide the shape, take the one
+with the best measured TOPS, ties broken by the largest ``block_m * block_n``.  Masked-K entries
+(``even_k=False``: any K) are listed for ``explicit_mm`` as in the reference.
 """
 from __future__ import annotations
 
@@ -38,12 +45,44 @@ from .metadata import (
 )
 from .template_config import LaunchShape, is_tile_multiple_shape
 
-ROW_MULTIPLES = (128, 64, 32, 16)
+ROW_MULTIPLES = (128, 64, 32, 16)   # STANDARD entries: the 128-row tile and the row multiples it masks down to
 COLUMN_MULTIPLES = (256, 128)
-SWIGLU_COLUMN_MULTIPLES = (128,)  # one tile = 128 up columns + the matching 128 gate columns
-K_STEP = 32                       # one tcgen05.mma kind::i8 instruction reduces 32 K values
-RASTER_GROUP_M = 8
+SWIGLU_COLUMN_MULTIPLES = (128,)    # one tile = 128 up columns + the matching 128 gate columns
+K_STEP = 32                         # one tcgen05.mma kind::i8 instruction reduces 32 K values
+PAIR_ROWS = 256                     # output rows of a CTA pair's tile
+# raster widths (row tiles walked before the next column tile) registered per forced form; the first one is
+# what the library itself uses for the form
+RASTER_WIDTHS = {KernelSchedule.PERSISTENT: (8, 32), KernelSchedule.PERSISTENT_2CTA: (16, 8), KernelSchedule.TILE_PER_CTA: (8,)}
 DEVICE_KERNEL = "b200::gemm_i8_tcgen05_kernel"
+SCHEDULES = (KernelSchedule.STANDARD, KernelSchedule.PERSISTENT, KernelSchedule.PERSISTENT_2CTA, KernelSchedule.TILE_PER_CTA)
+
+
+def has_pair_kernel(dtype: OperandDType, scale: ScaleSpec, epilogue: Epilogue, layout: GemmLayout) -> bool:
+    """Whether the library holds a CTA-pair instantiation for the cell (bf16 output; csrc/tc_table.h)."""
+    sub = scale.mode is ScaleMode.SUBCHANNEL
+    if sub and (scale.subchannel_size or 0) < 128:
+        return False  # paired kernels hand the accumulator over per 128-deep K block
+    if layout is GemmLayout.NN:
+        return True
+    if sub or epilogue is Epilogue.SWIGLU:
+        return False
+    if layout is GemmLayout.NT:
+        return epilogue is Epilogue.NONE or dtype is OperandDType.INT8
+    if layout is GemmLayout.TN:
+        return dtype is OperandDType.INT4 and epilogue is Epilogue.NONE
+    return False
+
+
+def has_split_k_kernel(dtype: OperandDType, scale: ScaleSpec, layout: GemmLayout, *, pair: bool = False) -> bool:
+    """Whether the library holds the partial-sum kernel a split-K launch of the cell needs: raw s32
+    accumulators for per-channel scales (layouts NN and NT), fp32 partial sums for int4 subchannel scales."""
+    if scale.mode is ScaleMode.PER_CHANNEL:
+        return layout is GemmLayout.NN or (layout is GemmLayout.NT and not pair)
+    if dtype is not OperandDType.INT4:
+        return False
+    if pair:
+        return layout is GemmLayout.NN and (scale.subchannel_size or 0) >= 128
+    return layout in (GemmLayout.NN, GemmLayout.NT)
 
 
 def cta_warps(dtype: OperandDType, scale: ScaleSpec) -> int:
@@ -54,7 +93,10 @@ def cta_warps(dtype: OperandDType, scale: ScaleSpec) -> int:
     return 2 + 4 + (8 if dtype is OperandDType.INT4 else 0)
 
 
-def pipeline_stages(dtype: OperandDType) -> int:
+def pipeline_stages(dtype: OperandDType, schedule: KernelSchedule = KernelSchedule.STANDARD) -> int:
+    """Depth of the int8 operand pipeline in shared memory: a CTA of a pair holds one block of B, so more fit."""
+    if schedule is KernelSchedule.PERSISTENT_2CTA:
+        return 4 if dtype is OperandDType.INT4 else 6
     return 3 if dtype is OperandDType.INT4 else 4
 
 
@@ -63,22 +105,35 @@ def seed_tile_configs(
     *,
     epilogue: Epilogue | None = None,
     scale: ScaleSpec | None = None,
+    schedule: KernelSchedule = KernelSchedule.STANDARD,
+    layout: GemmLayout = GemmLayout.NN,
 ) -> tuple[TileConfig, ...]:
-    """Tile records registered for one (dtype, scale, epilogue) cell of the matrix."""
+    """Tile records registered for one (dtype, scale, epilogue, layout) cell and launch form."""
     if dtype not in (OperandDType.INT4, OperandDType.INT8):
         raise ValueError(f"unsupported dtype: {dtype}")
     scale = scale if scale is not None else ScaleSpec(ScaleMode.PER_CHANNEL)
     epilogue = epilogue if epilogue is not None else Epilogue.NONE
-    columns = SWIGLU_COLUMN_MULTIPLES if epilogue is Epilogue.SWIGLU else COLUMN_MULTIPLES
-    splits = SUPPORTED_SPLIT_K if epilogue is Epilogue.NONE else (1,)
+    pair = schedule is KernelSchedule.PERSISTENT_2CTA
+    if pair and not has_pair_kernel(dtype, scale, epilogue, layout):
+        return ()
+    swiglu = epilogue is Epilogue.SWIGLU
+    splits = tuple(
+        split for split in (SUPPORTED_SPLIT_K if epilogue is Epilogue.NONE else (1,))
+        if split == 1 or (schedule is not KernelSchedule.TILE_PER_CTA and has_split_k_kernel(dtype, scale, layout, pair=pair))
+    )
+    if schedule is KernelSchedule.STANDARD:
+        shapes = [(rows, cols, 0) for cols in (SWIGLU_COLUMN_MULTIPLES if swiglu else COLUMN_MULTIPLES) for rows in ROW_MULTIPLES]
+    else:
+        rows = PAIR_ROWS if pair else 128
+        shapes = [(rows, 128 if swiglu else 256, width) for width in RASTER_WIDTHS[schedule]]
     warps = cta_warps(dtype, scale)
-    stages = pipeline_stages(dtype)
+    stages = pipeline_stages(dtype, schedule)
     return tuple(
         TileConfig(
             block_m=rows,
             block_n=cols,
             block_k=K_STEP,
-            group_size_m=RASTER_GROUP_M,
+            group_size_m=width,
             num_warps=warps,
             num_stages=stages,
             waves_per_eu=0,
@@ -86,9 +141,8 @@ def seed_tile_configs(
             split_k=split_k,
         )
         for split_k in splits
-        for cols in columns
         for even_k in (True, False)
-        for rows in ROW_MULTIPLES
+        for rows, cols, width in shapes
     )
 
 
@@ -123,14 +177,21 @@ def iter_supported_kernel_metadata(
 ) -> Iterator[KernelMetadata]:
     """Every registered variant; ``tiles`` replaces the seed tile list of every cell."""
     forced = None if tiles is None else tuple(tiles)
-    for schedule in (KernelSchedule.STANDARD, KernelSchedule.PERSISTENT):
+    for schedule in SCHEDULES:
         for dtype in (OperandDType.INT4, OperandDType.INT8):
             for scale in supported_scale_specs():
                 for epilogue in (Epilogue.NONE, Epilogue.RELU2, Epilogue.SWIGLU):
-                    cell = forced if forced is not None else seed_tile_configs(dtype, epilogue=epilogue, scale=scale)
                     for layout in SUPPORTED_GEMM_LAYOUTS:
+                        cell = forced if forced is not None else seed_tile_configs(
+                            dtype, epilogue=epilogue, scale=scale, schedule=schedule, layout=layout)
                         for tile in cell:
                             yield _describe(dtype, scale, epilogue, tile, layout, schedule)
+
+
+def launch_signature(kernel: KernelMetadata) -> tuple:
+    """What distinguishes one entry's launch from another's within a cell: entries with equal signatures run
+    the same kernel with the same parameters (they differ only in the shapes they accept)."""
+    return (kernel.schedule, kernel.tile.group_size_m, kernel.tile.split_k)
 
 
 _CellKey = tuple[OperandDType, ScaleSpec, Epilogue, GemmLayout, KernelSchedule]

@@ -74,8 +74,11 @@ def assert_close_rms(got: np.ndarray, want: np.ndarray, *, rtol=1e-2, atol_rms=1
 # ----------------------------------------------------------------------------------------------
 # GPU side: calls through the C ABI (ctypes) with arbitrary shapes
 # ----------------------------------------------------------------------------------------------
-def abi_dense(pkg, case, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue="none", out="bf16", path=0, schedule="persistent", cta_group=0):
-    """One dense launch through ``b200_int4_gemms_launch_dense``; returns the CUDA output tensor."""
+def abi_dense(pkg, case, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue="none", out="bf16", path=0, schedule="persistent", cta_group=0,
+              order="reference"):
+    """One dense launch through ``b200_int4_gemms_launch_dense``; returns the CUDA output tensor.  ``order``: the
+    subchannel accumulation order, "reference" (every rounding of the reference math: what the bit-equality checks
+    use) or "fused" (the library's default)."""
     from strix_halo_int4_gemms_b200 import native
 
     out_dtype = {"bf16": torch.bfloat16, "f32": torch.float32, "s32": torch.int32}[out]
@@ -86,8 +89,11 @@ def abi_dense(pkg, case, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue=
     variant = native.make_variant(
         dtype=pkg.OperandDType(dtype), layout=getattr(pkg.GemmLayout, layout.upper()), scale=scale_spec(pkg, sub),
         epilogue=pkg.Epilogue(epilogue), out_dtype=code, path=path,
-        schedule=pkg.KernelSchedule.STANDARD if schedule == "standard" else pkg.KernelSchedule.PERSISTENT,
+        # "persistent": the library's persistent grid with the CTA form given by cta_group (0 = its own choice);
+        # "tile_per_cta": one CTA per output tile
+        schedule=pkg.KernelSchedule.TILE_PER_CTA if schedule == "tile_per_cta" else pkg.KernelSchedule.STANDARD,
         cta_group=cta_group,
+        accumulate_order=native.ACCUMULATE_REFERENCE if order == "reference" else native.ACCUMULATE_FUSED,
     )
     native.launch_dense(
         variant, device_index=0, stream_handle=torch.cuda.current_stream().cuda_stream,
@@ -100,11 +106,16 @@ def abi_dense(pkg, case, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue=
     return c
 
 
-def check_dense(pkg, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue="none", out="bf16", path=0, seed=0, exact=None, schedule="persistent", cta_group=0):
+def check_dense(pkg, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue="none", out="bf16", path=0, seed=0, exact=None, schedule="persistent", cta_group=0,
+                order="reference"):
     """Run one dense case on the GPU and compare with the oracle.  ``exact`` defaults to bit
-    equality for everything except SwiGLU (whose exp() is implementation-defined to an ulp)."""
+    equality for everything except SwiGLU (whose exp() is implementation-defined to an ulp) and
+    the fused subchannel accumulation order (one rounding fewer per K-group than the reference)."""
     case = dense_case(pkg, m=m, n=n, k=k, dtype=dtype, layout=layout, sub=sub, epilogue=epilogue, seed=seed)
-    got = abi_dense(pkg, case, m=m, n=n, k=k, dtype=dtype, layout=layout, sub=sub, epilogue=epilogue, out=out, path=path, schedule=schedule, cta_group=cta_group)
+    got = abi_dense(pkg, case, m=m, n=n, k=k, dtype=dtype, layout=layout, sub=sub, epilogue=epilogue, out=out, path=path, schedule=schedule,
+                    cta_group=cta_group, order=order)
+    if exact is None and order == "fused" and sub:
+        exact = False
     if out == "s32":
         want = oracle.int32_accumulators(case["a"].numpy(), case["b"].numpy(), int4=dtype == "int4", layout=layout)
         np.testing.assert_array_equal(got.cpu().numpy(), want)

@@ -19,13 +19,24 @@ def _pc(pkg):
     return pkg.ScaleSpec(pkg.ScaleMode.PER_CHANNEL)
 
 
-def test_candidates_are_the_entries_that_accept_the_shape(pkg):
+def test_candidates_are_launches_that_differ(pkg):
+    from strix_halo_int4_gemms_b200.registry import launch_signature
+
     found = pkg.find_autotune_candidates(m=256, n=512, k=256, dtype=pkg.OperandDType.INT4, scale=_pc(pkg), epilogue=pkg.Epilogue.NONE)
-    # rows 128/64/32/16 x columns 256/128 x split 1/2/4/8, even-K only
-    assert len(found) == 4 * 2 * 4
-    assert all(k.tile.even_k and k.schedule is pkg.KernelSchedule.STANDARD for k in found)
+    # library's choice x split 1/2/4/8; one CTA per tile x raster 8/32 x split; CTA pairs x raster 16/8 x split; tile per CTA
+    assert len(found) == 4 + 2 * 4 + 2 * 4 + 1 == 21
+    assert len({launch_signature(k) for k in found}) == len(found)      # no two candidates run the same launch
+    assert all(k.tile.even_k for k in found)
+    assert {k.schedule for k in found} == set(pkg.KernelSchedule)
+    standard = pkg.find_autotune_candidates(m=256, n=512, k=256, dtype=pkg.OperandDType.INT4, scale=_pc(pkg), epilogue=pkg.Epilogue.NONE,
+                                            schedule=pkg.KernelSchedule.STANDARD)
+    assert [k.tile.split_k for k in standard] == [1, 2, 4, 8]
+    assert all((k.tile.block_m, k.tile.block_n) == (128, 256) for k in standard)   # largest multiples that divide the shape
+    # M = 128: nothing for CTA pairs (256-row tiles)
+    skinny = pkg.find_autotune_candidates(m=128, n=1024, k=64, dtype=pkg.OperandDType.INT4, scale=_pc(pkg), epilogue=pkg.Epilogue.NONE)
+    assert pkg.KernelSchedule.PERSISTENT_2CTA not in {k.schedule for k in skinny}
     odd = pkg.find_autotune_candidates(m=48, n=128, k=96, dtype=pkg.OperandDType.INT4, scale=_pc(pkg), epilogue=pkg.Epilogue.RELU2)
-    assert {(k.tile.block_m, k.tile.block_n) for k in odd} == {(16, 128)}
+    assert {(k.tile.block_m, k.tile.block_n, k.schedule) for k in odd} == {(16, 128, pkg.KernelSchedule.STANDARD)}
     assert pkg.generated_shape_for_kernel(found[0]) is None
 
 
@@ -37,9 +48,9 @@ def test_autotune_picks_best_successful_record_and_appends_to_db(pkg, tmp_path):
         seen.append(kernel.kernel_id)
         assert tuned == shape
         ms = 1.0 + 0.01 * len(seen)
-        if kernel.tile.block_m == 64 and kernel.tile.block_n == 128 and kernel.tile.split_k == 1:
+        if kernel.schedule is pkg.KernelSchedule.PERSISTENT_2CTA and kernel.tile.group_size_m == 8 and kernel.tile.split_k == 1:
             ms = 0.25
-        ok = not (kernel.tile.block_m == 16 and kernel.tile.split_k == 8)
+        ok = not (kernel.schedule is pkg.KernelSchedule.PERSISTENT and kernel.tile.split_k == 8)
         return BenchmarkRecord(kernel.kernel_id, tuned, ms, tops_for_runtime(tuned, ms) if ok else 1e9, 7, 25, success=ok)
 
     path = tmp_path / "db.json"
@@ -47,15 +58,15 @@ def test_autotune_picks_best_successful_record_and_appends_to_db(pkg, tmp_path):
     BenchmarkDatabase([old]).save(path)
     result = pkg.autotune(m=256, n=512, k=256, dtype=pkg.OperandDType.INT4, scale=_pc(pkg), epilogue=pkg.Epilogue.NONE,
                           benchmark_db_path=path, benchmark_runner=runner)
-    assert len(result.records) == len(result.candidates) == 32 == len(seen)
-    assert result.best_kernel.tile.block_m == 64 and result.best_kernel.tile.block_n == 128
+    assert len(result.records) == len(result.candidates) == 21 == len(seen)
+    assert result.best_kernel.schedule is pkg.KernelSchedule.PERSISTENT_2CTA and result.best_kernel.tile.group_size_m == 8
     assert result.best_record.runtime_ms == 0.25 and result.shape == shape
     stored = BenchmarkDatabase.load(path).records()
-    assert stored[0] == old and len(stored) == 33
+    assert stored[0] == old and len(stored) == 22
 
 
 def test_autotune_errors(pkg):
-    with pytest.raises(LookupError, match=r"no pregenerated kernels match dtype=int4, layout=nn, scale=pc, epilogue=none, schedule=standard, shape=\(17, 512, 256\)"):
+    with pytest.raises(LookupError, match=r"no pregenerated kernels match dtype=int4, layout=nn, scale=pc, epilogue=none, schedule=any, shape=\(17, 512, 256\)"):
         pkg.autotune(m=17, n=512, k=256, dtype=pkg.OperandDType.INT4, scale=_pc(pkg), epilogue=pkg.Epilogue.NONE, benchmark_runner=lambda k, s: None)
     failing = lambda kernel, shape: BenchmarkRecord(kernel.kernel_id, shape, 1.0, 1.0, 1, 1, success=False)
     with pytest.raises(RuntimeError, match="no successful benchmark records"):
@@ -71,11 +82,14 @@ def test_validation_tolerances(pkg):
 
 def test_default_ragged_candidates(pkg):
     fwd = pkg.default_ragged_dot_candidates(RaggedDotMode.FWD)
-    assert all(isinstance(c.config, pkg.RaggedDotConfig) and c.config.block_m <= 128 for c in fwd)
-    assert fwd[0].kernel_id == "ragged_dot_int4_fwd_nn_pc_bm128_bn256_bk128_gst1_w10_s3"
+    assert all(isinstance(c.config, pkg.RaggedDotConfig) and c.config.pair_tasks is False for c in fwd)
+    assert [c.config.block_m for c in fwd] == [256, 128, 64, 32]        # CTA-pair tasks first, then single-CTA heights
+    assert fwd[1].kernel_id == "ragged_dot_int4_fwd_nn_pc_bm128_bn256_bk128_gst1_w14_s3"
+    tn = pkg.default_ragged_dot_candidates(RaggedDotMode.FWD, layout=pkg.GemmLayout.TN)
+    assert max(c.config.block_m for c in tn) == 128                      # no paired kernel for a transposed lhs
     bwd = pkg.default_ragged_dot_candidates(RaggedDotMode.BWD, layout=pkg.GemmLayout.TN, split_ks=(1, 4))
     assert [c.config.split_k for c in bwd] == [1, 4]
-    assert bwd[1].kernel_id == "ragged_dot_int4_bwd_tn_pc_bm128_bn256_bk128_w10_s3_sk4"
+    assert bwd[1].kernel_id == "ragged_dot_int4_bwd_tn_pc_bm128_bn256_bk128_w20_s2_sk4"
     with pytest.raises(TypeError, match="mode must be a RaggedDotMode"):
         pkg.default_ragged_dot_candidates("fwd")
 
@@ -87,7 +101,7 @@ def test_ragged_autotune_bookkeeping(pkg, tmp_path):
         calls.append(candidate.kernel_id)
         if candidate.config.block_m == 32:
             raise RuntimeError("boom")
-        ms = 2.0 if candidate.config.block_m == 128 and candidate.config.group_size_tasks == 1 else 1.0
+        ms = 2.0 if candidate.config.block_m == 128 else 1.0
         return BenchmarkRecord(candidate.kernel_id, shape, ms, tops_for_runtime(shape, ms), 5, 25)
 
     result = pkg.autotune_ragged_dot(mode=RaggedDotMode.FWD, m=1000, n=256, k=128, groups=3, benchmark_runner=runner,

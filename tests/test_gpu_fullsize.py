@@ -27,7 +27,7 @@ def _random_bytes(shape, seed, *, int8=False):
     return torch.randint(0, 256, shape, generator=g, device="cuda", dtype=torch.uint8)
 
 
-def _launch(pkg, a, b, sa, sb, *, m, n, k, dtype="int4", sub=0, epilogue="none", out="bf16"):
+def _launch(pkg, a, b, sa, sb, *, m, n, k, dtype="int4", sub=0, epilogue="none", out="bf16", order="reference", path=None):
     from strix_halo_int4_gemms_b200 import native
     from helpers import scale_spec
 
@@ -35,7 +35,8 @@ def _launch(pkg, a, b, sa, sb, *, m, n, k, dtype="int4", sub=0, epilogue="none",
     code = {"bf16": native.OUT_BF16, "f32": native.OUT_F32, "s32": native.OUT_S32}[out]
     c = torch.empty((m, n), device="cuda", dtype=out_dtype)
     variant = native.make_variant(dtype=pkg.OperandDType(dtype), layout=pkg.GemmLayout.NN, scale=scale_spec(pkg, sub),
-                                  epilogue=pkg.Epilogue(epilogue), out_dtype=code, path=native.PATH_TCGEN05)
+                                  epilogue=pkg.Epilogue(epilogue), out_dtype=code, path=native.PATH_TCGEN05 if path is None else path,
+                                  accumulate_order=native.ACCUMULATE_REFERENCE if order == "reference" else native.ACCUMULATE_FUSED)
     native.launch_dense(variant, device_index=0, stream_handle=torch.cuda.current_stream().cuda_stream, a_ptr=a.data_ptr(), b_ptr=b.data_ptr(),
                         a_scale_ptr=sa.data_ptr(), b_scale_ptr=sb.data_ptr(), c_ptr=c.data_ptr(), m=m, n=n, k=k)
     torch.cuda.synchronize()
@@ -121,6 +122,33 @@ def test_config4_int4_sc256_fused_swiglu(pkg):
     want = oracle.reference_mm(a[rows.cuda()].cpu().numpy(), b[:, :4096].cpu().numpy(), int4=True, a_scale_bits=bf16_bits(sa[rows.cuda()]),
                                b_scale_bits=bf16_bits(sb[:, :4096].contiguous()), subchannel=256)
     np.testing.assert_array_equal(as_f32(plain[rows.cuda()]), want)
+    # the library's default (fused) accumulation order against the reference order, EVERY element, on the GPU:
+    # the bf16 outputs may differ by one unit in the last place where the fp32 sums straddle a rounding boundary
+    fused = _launch(pkg, a, b, sa, sb, m=m, n=d, k=k, sub=256, epilogue="swiglu", order="fused")
+    diff = (fused.float() - out.float()).abs()
+    bound = 1e-2 * out.float().abs() + 1e-2 * out.float().pow(2).mean().sqrt()
+    assert bool((diff <= bound).all())
+    assert float((fused == out).float().mean()) > 0.95
+    sampled = as_f32(fused[rows.cuda()])
+    want_swiglu = oracle.reference_mm(a[rows.cuda()].cpu().numpy(), b.cpu().numpy(), int4=True, a_scale_bits=bf16_bits(sa[rows.cuda()]),
+                                      b_scale_bits=bf16_bits(sb), subchannel=256, epilogue="swiglu")
+    assert_close_rms(sampled, want_swiglu, what="config 4, fused order")
+
+
+def test_config4_whole_output_against_the_cuda_core_kernel(pkg):
+    """Every element of a config-4-shaped product (a 1024-row slice of M, all 14336 columns): the tensor-core kernel in
+    the reference order against the CUDA-core kernel, which the small cases pin to the oracle.  Only exp() may differ."""
+    from strix_halo_int4_gemms_b200 import native
+
+    m, k, d = 1024, 4096, 14336
+    a, b = _random_bytes((m, k // 2), 20), _random_bytes((k // 2, 2 * d), 21)
+    sa, sb = _scales((m, k // 256), 22).cuda(), _scales((k // 256, 2 * d), 23).cuda()
+    plain_tc = _launch(pkg, a, b, sa, sb, m=m, n=2 * d, k=k, sub=256)
+    plain_cc = _launch(pkg, a, b, sa, sb, m=m, n=2 * d, k=k, sub=256, path=native.PATH_SIMT)
+    assert torch.equal(plain_tc, plain_cc)                       # [up | gate] before the activation: bit for bit
+    fused_tc = _launch(pkg, a, b, sa, sb, m=m, n=d, k=k, sub=256, epilogue="swiglu")
+    fused_cc = _launch(pkg, a, b, sa, sb, m=m, n=d, k=k, sub=256, epilogue="swiglu", path=native.PATH_SIMT)
+    assert float((fused_tc == fused_cc).float().mean()) > 0.999  # same instruction sequence on both; bf16 rounding hides the rest
 
 
 def _config5_group_sizes():

@@ -80,6 +80,37 @@ def test_group_info_capacity_overflow_is_reported(pkg):
     assert int(info.device_overflow.item()) == 1 and int(info.device_num_tasks.item()) == 4
 
 
+def test_forward_reports_an_overflowed_task_list_and_clamps_task_bounds(pkg):
+    """A task array that is too small leaves rows unwritten: the forward kernel says so through the status word
+    (code 3, detail = tasks kept) instead of dropping tasks silently; rows of the tasks that fit are right."""
+    from strix_halo_int4_gemms_b200 import native
+
+    sizes = [300, 300, 300]
+    data = make_ragged_fwd_inputs(m=900, n=256, k=256, group_sizes=sizes, layout=pkg.GemmLayout.NN, scale=scale_spec(pkg, 0), seed=5)
+    dev = {name: data[name].cuda() for name in ("lhs", "rhs", "a_scale", "b_scale", "group_sizes")}
+    info = pkg.calculate_group_info_on_device(dev["group_sizes"], 128, total_rows=900, max_tasks=4)
+    assert info.tile == 128
+    out = torch.full((900, 256), float("nan"), device="cuda", dtype=torch.bfloat16)
+    native.reset_device_status(0)
+    pkg.ragged_dot_int4(dev["lhs"], dev["rhs"], dev["group_sizes"], a_scale=dev["a_scale"], b_scale=dev["b_scale"], group_info=info, out=out)
+    torch.cuda.synchronize()
+    status, (kept, _site, _) = native.device_status(0)
+    assert status == 3 and kept == 4
+    native.reset_device_status(0)
+    want = oracle.ragged_dot_fwd(data["lhs"].numpy(), data["rhs"].numpy(), sizes, bf16_bits(data["a_scale"]), bf16_bits(data["b_scale"]), layout="nn")
+    got = as_f32(out)
+    np.testing.assert_array_equal(got[:384], want[:384])        # group 0 (3 tasks) and the first task of group 1
+    assert np.isnan(got[512:]).all()                             # the rest was never written
+    # group sizes that claim more rows than the operand has: bounds are clamped on the device, nothing is written past row 900
+    big = torch.tensor([300, 300, 400], dtype=torch.int64).cuda()
+    info = pkg.calculate_group_info_on_device(big, 128, total_rows=1000)
+    guard = torch.full((1024, 256), float("nan"), device="cuda", dtype=torch.bfloat16)
+    pkg.ragged_dot_int4(dev["lhs"], dev["rhs"], big, a_scale=dev["a_scale"], b_scale=dev["b_scale"], group_info=info, out=guard[:900])
+    torch.cuda.synchronize()
+    assert native.device_status(0)[0] == 0
+    assert torch.isnan(guard[900:]).all() and not torch.isnan(guard[:900]).any()
+
+
 @pytest.mark.parametrize("sub,block_m", [(0, 128), (0, 256), (128, 256), (32, 64)])
 def test_forward_with_device_built_tasks(pkg, sub, block_m):
     """No host synchronisation between group_sizes and the output: tasks and their count stay on the GPU."""

@@ -149,14 +149,16 @@ def _bwd(pkg, sizes, m, n, *, layout="tn", sub=0, seed=0, k_capacity=None, confi
 
 
 @pytest.mark.parametrize("layout", ["tn", "nn"])
-def test_backward_on_cta_pairs_and_on_single_ctas(pkg, layout, monkeypatch):
+def test_backward_on_cta_pairs_and_on_single_ctas(pkg, layout):
     """M = 512 is two 256-row pair tiles per group; the per-channel backward kernels exist in both forms and
-    the binding's environment switch pins either: both must reproduce the oracle."""
+    RaggedBwdDotConfig.pair_tiles pins either: both must reproduce the oracle."""
+    from strix_halo_int4_gemms_b200 import native
+
     sizes = [17, 0, 300, 128, 255, 512, 1]
-    for forced in ("2", "1"):
-        monkeypatch.setenv("B200_INT4_GEMMS_CTA_GROUP", forced)
-        out, want = _bwd(pkg, sizes, 512, 1408, layout=layout, k_capacity=512, seed=41)
-        np.testing.assert_array_equal(out.cpu().numpy(), want, err_msg=f"cta_group {forced}")
+    for forced, path in ((True, native.LAUNCHED_TCGEN05_PAIR), (False, native.LAUNCHED_TCGEN05), (None, native.LAUNCHED_TCGEN05_PAIR)):
+        out, want = _bwd(pkg, sizes, 512, 1408, layout=layout, k_capacity=512, seed=41, config=pkg.RaggedBwdDotConfig(pair_tiles=forced))
+        assert native.last_launch_path() == path
+        np.testing.assert_array_equal(out.cpu().numpy(), want, err_msg=f"pair_tiles {forced}")
 
 
 @pytest.mark.parametrize("layout", ["tn", "nn", "nt", "tt"])

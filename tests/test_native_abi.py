@@ -29,7 +29,13 @@ def test_library_exports_every_declared_symbol(pkg, native_lib):
 
 
 def test_variant_record_matches_header(pkg):
-    from strix_halo_int4_gemms_b200.native import GemmVariant
+    from strix_halo_int4_gemms_b200.native import DensePlan, GemmVariant
+
+    plan = re.search(r"typedef struct b200_dense_plan \{(.*?)\}", HEADER.read_text(), flags=re.S).group(1)
+    plan = re.sub(r"/\*.*?\*/", "", plan, flags=re.S)
+    plan_fields = re.findall(r"int32_t\s+(\w+)(?:\[(\d+)\])?;", plan)
+    assert [f[0] for f in plan_fields] == [name for name, _ in DensePlan._fields_]
+    assert ctypes.sizeof(DensePlan) == 4 * sum(int(n or 1) for _, n in plan_fields) == 32
 
     body = re.search(r"typedef struct b200_gemm_variant \{(.*?)\}", HEADER.read_text(), flags=re.S).group(1)
     body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
@@ -66,6 +72,21 @@ def test_bad_arguments_fail_with_a_message(pkg, native_lib):
     assert dense(good, ptrs=(16, 16, 16, 16, 16), shape=(0, 256, 64)) == (1, "m, n and k must be positive")
     bad = native.make_variant(dtype=pkg.OperandDType.INT4, layout=pkg.GemmLayout.NN, scale=pc, epilogue=pkg.Epilogue.RELU2, out_dtype=native.OUT_F32, split_k=2)
     assert dense(bad, ptrs=(16, 16, 16, 16, 16)) == (1, "split_k > 1 needs epilogue NONE and float32 output")
+    # the registry's launch forms map onto the variant record
+    pair = native.make_variant(dtype=pkg.OperandDType.INT4, layout=pkg.GemmLayout.NN, scale=pc, epilogue=pkg.Epilogue.NONE,
+                               out_dtype=native.OUT_BF16, schedule=pkg.KernelSchedule.PERSISTENT_2CTA, group_m=8)
+    assert (pair.schedule, pair.cta_group, pair.group_m) == (native.SCHEDULE_PERSISTENT, native.CTA_GROUP_PAIR, 8)
+    assert (good.schedule, good.cta_group) == (native.SCHEDULE_PERSISTENT, native.CTA_GROUP_AUTO)
+    plain = native.make_variant(dtype=pkg.OperandDType.INT4, layout=pkg.GemmLayout.NN, scale=pc, epilogue=pkg.Epilogue.NONE,
+                                out_dtype=native.OUT_BF16, schedule=pkg.KernelSchedule.TILE_PER_CTA)
+    assert (plain.schedule, plain.cta_group) == (native.SCHEDULE_TILE_PER_CTA, native.CTA_GROUP_SINGLE)
+    split = native.make_variant(dtype=pkg.OperandDType.INT4, layout=pkg.GemmLayout.NN, scale=pc, epilogue=pkg.Epilogue.NONE, out_dtype=native.OUT_F32, split_k=4)
+    need = lib.b200_int4_gemms_dense_workspace_bytes(ctypes.byref(split), 128, 256, 1024)
+    assert need == 4 * 128 * 256 * 4
+    assert lib.b200_int4_gemms_dense_workspace_bytes(ctypes.byref(split), 128, 256, 256) == 2 * 128 * 256 * 4   # two K blocks: two slices
+    assert lib.b200_int4_gemms_dense_workspace_bytes(ctypes.byref(split), 128, 256, 64) == 0                    # one K block: no split
+    assert lib.b200_int4_gemms_dense_workspace_bytes(ctypes.byref(good), 128, 256, 1024) == 0
+    assert lib.b200_int4_gemms_last_launch_path() == native.LAUNCHED_NOTHING
     bad = native.make_variant(dtype=pkg.OperandDType.INT4, layout=pkg.GemmLayout.NN, scale=pc, epilogue=pkg.Epilogue.NONE, out_dtype=native.OUT_BF16)
     bad.subchannel, bad.scale_mode = 48, 1
     assert dense(bad, ptrs=(16, 16, 16, 16, 16)) == (1, "variant.subchannel must be 32, 64, 128 or 256")
@@ -101,12 +122,17 @@ def test_launcher_validation_before_any_device_work(pkg):
         dtype=pkg.OperandDType.INT4, scale=pkg.ScaleSpec(pkg.ScaleMode.PER_CHANNEL), epilogue=pkg.Epilogue.NONE, m=4096, n=4096, k=4096
     )
     assert block_size(k) == 448  # 2 + 4 + 8 warps: TMA, MMA, epilogue, unpack
-    assert launch_grid(k, 4096, 4096) == (512, 1, 1)
-    persistent = pkg.default_registry.select(
-        dtype=pkg.OperandDType.INT4, scale=pkg.ScaleSpec(pkg.ScaleMode.PER_CHANNEL), epilogue=pkg.Epilogue.NONE,
-        m=4096, n=4096, k=4096, schedule=pkg.KernelSchedule.PERSISTENT,
-    )
-    assert launch_grid(persistent, 4096, 4096) == (148, 1, 1)
+    assert launch_grid(k, 4096, 4096) == (148, 1, 1)
+
+    def form(schedule):
+        return pkg.default_registry.select(
+            dtype=pkg.OperandDType.INT4, scale=pkg.ScaleSpec(pkg.ScaleMode.PER_CHANNEL), epilogue=pkg.Epilogue.NONE,
+            m=4096, n=4096, k=4096, schedule=schedule)
+
+    assert launch_grid(form(pkg.KernelSchedule.PERSISTENT), 4096, 4096) == (148, 1, 1)
+    assert launch_grid(form(pkg.KernelSchedule.PERSISTENT_2CTA), 4096, 4096) == (148, 1, 1)   # 74 pairs
+    assert launch_grid(form(pkg.KernelSchedule.PERSISTENT_2CTA), 512, 512) == (8, 1, 1)       # 4 tiles of 256 x 256
+    assert launch_grid(form(pkg.KernelSchedule.TILE_PER_CTA), 4096, 4096) == (512, 1, 1)
     a = torch.zeros((128, 32), dtype=torch.uint8)
     b = torch.zeros((32, 256), dtype=torch.uint8)
     if not torch.cuda.is_available():

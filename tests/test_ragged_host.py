@@ -102,11 +102,11 @@ def test_config_validation_and_ids(pkg):
         pkg.RaggedBwdDotConfig(split_k=0)
     pc = pkg.ScaleSpec(pkg.ScaleMode.PER_CHANNEL)
     assert ragged_kernel_id(mode="fwd", layout=pkg.GemmLayout.NN, scale=pc, config=pkg.RaggedDotConfig(), variant="evenk") == (
-        "sm_100a_ragged_int4_fwd_nn_pc_evenk_bfloat16_bm128_bn256_bk128_gst1_w10_s3"
+        "sm_100a_ragged_int4_fwd_nn_pc_evenk_bfloat16_bm128_bn256_bk128_gst1_w14_s3"
     )
     assert ragged_kernel_id(mode="bwd", layout=pkg.GemmLayout.TN, scale=pkg.ScaleSpec(pkg.ScaleMode.SUBCHANNEL, 32),
                             config=pkg.RaggedBwdDotConfig(), variant="maskk") == (
-        "sm_100a_ragged_int4_bwd_tn_sc32_maskk_float32_bm128_bn256_bk128_w10_s3_sk1"
+        "sm_100a_ragged_int4_bwd_tn_sc32_maskk_float32_bm128_bn256_bk128_w20_s2_sk1"
     )
     with pytest.raises(ValueError, match="ragged mode"):
         ragged_kernel_id(mode="x", layout=pkg.GemmLayout.NN, scale=pc, config=pkg.RaggedDotConfig(), variant="evenk")
@@ -123,3 +123,23 @@ def test_ragged_api_rejects_cpu_tensors_and_bad_layout(pkg):
             pkg.ragged_dot_int4(lhs, rhs, gs)
         with pytest.raises(ValueError, match="lhs must be a CUDA tensor"):
             pkg.ragged_dot_int4_bwd(rhs, rhs, gs)
+
+
+def test_group_info_records_its_tile_and_a_mismatched_config_is_refused(pkg):
+    """Prebuilt tasks run with the height they were cut with; a config that names another height is an error
+    (launching 256-row tasks as 128-row ones would leave half of every block unwritten)."""
+    import torch
+
+    from strix_halo_int4_gemms_b200.ragged import RaggedGroupInfo
+
+    info = pkg.calculate_group_info(torch.tensor([300, 0, 200]), 256, align_tile=8)
+    assert (info.tile, info.align_tile) == (256, 8)
+    assert pkg.calculate_group_info(torch.tensor([], dtype=torch.int64), 64).tile == 64
+    legacy = RaggedGroupInfo(*(torch.zeros(0, dtype=torch.int64) for _ in range(6)), num_tasks=0)
+    assert legacy.tile is None
+    if torch.cuda.is_available():
+        lhs = torch.zeros((500, 64), dtype=torch.uint8, device="cuda")
+        rhs = torch.zeros((3, 64, 256), dtype=torch.uint8, device="cuda")
+        sizes = torch.tensor([300, 0, 200], device="cuda")
+        with pytest.raises(ValueError, match="group_info was built with tile=256 but config.block_m=64"):
+            pkg.ragged_dot_int4(lhs, rhs, sizes, config=pkg.RaggedDotConfig(block_m=64), group_info=info)

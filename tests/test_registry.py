@@ -2,14 +2,40 @@
 import pytest
 
 
-def test_matrix_size_and_unique_ids(pkg):
+def test_matrix_and_unique_ids(pkg):
+    from collections import Counter
+
     kernels = pkg.default_registry.all()
-    # 2 schedules x 2 dtypes x 5 scale specs x 3 layouts x (64 plain + 16 relu2 + 8 swiglu tile records)
-    assert len(kernels) == 2 * 2 * 5 * 3 * 88 == 5280
+    per_form = Counter(k.schedule for k in kernels)
+    assert set(per_form) == set(pkg.KernelSchedule)
+    # the library's own choice comes with every shape multiple; forced forms with their raster widths only
+    assert per_form[pkg.KernelSchedule.STANDARD] > per_form[pkg.KernelSchedule.PERSISTENT] > per_form[pkg.KernelSchedule.PERSISTENT_2CTA]
     assert len({k.kernel_id for k in kernels}) == len(kernels)
     assert all(k.arch == "sm_100a" and k.acc_dtype == "int32" and k.scale_dtype == "bfloat16" for k in kernels)
     assert {k.layout for k in kernels} == set(pkg.SUPPORTED_GEMM_LAYOUTS)
     assert pkg.GemmLayout.TT not in {k.layout for k in kernels}
+    for k in kernels:
+        if k.schedule is pkg.KernelSchedule.PERSISTENT_2CTA:
+            assert k.tile.block_m == 256 and k.tile.group_size_m in (16, 8)
+            assert not (k.scale.mode is pkg.ScaleMode.SUBCHANNEL and k.scale.subchannel_size < 128)
+        elif k.schedule is pkg.KernelSchedule.STANDARD:
+            assert k.tile.group_size_m == 0          # raster width left to the library
+        else:
+            assert k.tile.block_m == 128 and k.tile.group_size_m > 0
+
+
+def test_forced_forms_exist_only_where_the_library_has_the_kernel(pkg):
+    from strix_halo_int4_gemms_b200.registry import has_pair_kernel, has_split_k_kernel
+
+    pc, sc256, sc64 = pkg.ScaleSpec(pkg.ScaleMode.PER_CHANNEL), pkg.ScaleSpec(pkg.ScaleMode.SUBCHANNEL, 256), pkg.ScaleSpec(pkg.ScaleMode.SUBCHANNEL, 64)
+    i4, i8 = pkg.OperandDType.INT4, pkg.OperandDType.INT8
+    nn, nt, tn = pkg.GemmLayout.NN, pkg.GemmLayout.NT, pkg.GemmLayout.TN
+    assert has_pair_kernel(i4, sc256, pkg.Epilogue.SWIGLU, nn) and has_pair_kernel(i8, pc, pkg.Epilogue.RELU2, nt)
+    assert not has_pair_kernel(i4, sc64, pkg.Epilogue.NONE, nn) and not has_pair_kernel(i8, pc, pkg.Epilogue.NONE, tn)
+    assert has_split_k_kernel(i4, pc, nn, pair=True) and has_split_k_kernel(i8, pc, nt) and has_split_k_kernel(i4, sc64, nt)
+    assert not has_split_k_kernel(i4, pc, tn) and not has_split_k_kernel(i8, sc256, nn) and not has_split_k_kernel(i4, pc, nt, pair=True)
+    splits = {k.tile.split_k for k in pkg.default_registry.all() if k.layout is tn}
+    assert splits == {1}
 
 
 def test_activations_have_no_split_k_and_split_k_means_float32(pkg):
@@ -55,7 +81,12 @@ def _select(pkg, **kw):
 def test_selection_prefers_largest_registered_multiples(pkg):
     k = _select(pkg, m=4096, n=4096, k=4096)
     assert (k.tile.block_m, k.tile.block_n, k.tile.split_k, k.tile.even_k) == (128, 256, 1, True)
-    assert k.kernel_id == "sm_100a_int4xint4_nn_pc_none_bm128_bn256_bk32_gm8_w14_s3_weu0_sk1_evenk"
+    assert k.kernel_id == "sm_100a_int4xint4_nn_pc_none_bm128_bn256_bk32_gm0_w14_s3_weu0_sk1_evenk"
+    assert k.schedule is pkg.KernelSchedule.STANDARD      # the default form: the library pairs CTAs itself when that pays
+    pair = _select(pkg, m=4096, n=4096, k=4096, schedule=pkg.KernelSchedule.PERSISTENT_2CTA)
+    assert (pair.tile.block_m, pair.tile.group_size_m, pair.tile.num_stages) == (256, 16, 4) and "_persistent_2cta_" in pair.kernel_id
+    with pytest.raises(LookupError):
+        _select(pkg, m=128, n=1024, k=64, schedule=pkg.KernelSchedule.PERSISTENT_2CTA)   # a pair's tile has 256 rows
     assert _select(pkg, m=128, n=1024, k=64).tile.block_m == 128          # the quick-start shape
     small = _select(pkg, m=48, n=384, k=96)
     assert (small.tile.block_m, small.tile.block_n) == (16, 128)
