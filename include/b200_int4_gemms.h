@@ -69,6 +69,11 @@ enum { B200_CTA_GROUP_AUTO = 0, B200_CTA_GROUP_SINGLE = 1, B200_CTA_GROUP_PAIR =
  * Grouped (ragged) launches always use the reference order. */
 enum { B200_ACCUMULATE_FUSED = 0, B200_ACCUMULATE_REFERENCE = 1 };
 
+/* Where the unpacked A operand of an int4 CTA-pair kernel lives between the unpack warps and the tensor core.
+ * AUTO: in TMEM where the library has that kernel (per-channel scales, A stored [M, Kb]): a third less traffic
+ * through the shared-memory pipe that bounds these kernels.  SMEM: always shared memory.  Bit-identical results. */
+enum { B200_A_OPERAND_AUTO = 0, B200_A_OPERAND_SMEM = 1 };
+
 typedef struct b200_gemm_variant {
   int32_t dtype;      /* B200_DTYPE_*      */
   int32_t layout;     /* B200_LAYOUT_*     */
@@ -83,7 +88,8 @@ typedef struct b200_gemm_variant {
   int32_t schedule;   /* B200_SCHEDULE_*   */
   int32_t cta_group;  /* B200_CTA_GROUP_*: SMs per output tile of the tensor-core kernel */
   int32_t accumulate_order; /* B200_ACCUMULATE_*: subchannel dense launches only */
-  int32_t reserved[4];
+  int32_t a_operand;  /* B200_A_OPERAND_* */
+  int32_t reserved[3];
 } b200_gemm_variant;
 
 /* Replaces amd_strix_halo_kernels_dispatch_version (dispatch.cpp:206). */

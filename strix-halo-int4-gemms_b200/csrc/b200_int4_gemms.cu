@@ -122,13 +122,13 @@ struct TcLaunch {
   bool int4, a_mn, b_mn, mask_k;
   int scale, epi, out;
   bool pair = false;     // CTA-pair kernel (clusters of two, 256-row tiles)
-  bool fast_sc = false;  // subchannel kernels: fused accumulation order
+  int flavor = FLAVOR_PLAIN;  // FLAVOR_FUSED_SC: fused subchannel order; FLAVOR_TMEM_A: A operand through TMEM
 };
 
 const TcKernelInfo* tc_find(const TcLaunch& l) {
   for (const TcKernelInfo& k : tc_kernels()) {
     if (k.int4 == l.int4 && k.a_mn == l.a_mn && k.b_mn == l.b_mn && k.scale == l.scale && k.epi == l.epi &&
-        k.out == l.out && k.mask_k == l.mask_k && k.pair == l.pair && k.fast_sc == l.fast_sc)
+        k.out == l.out && k.mask_k == l.mask_k && k.pair == l.pair && k.flavor == l.flavor)
       return &k;
   }
   return nullptr;
@@ -271,6 +271,7 @@ int check_variant(const b200_gemm_variant* v) {
   if (v->cta_group < B200_CTA_GROUP_AUTO || v->cta_group > B200_CTA_GROUP_PAIR) return fail("variant.cta_group is unknown");
   if (v->accumulate_order != B200_ACCUMULATE_FUSED && v->accumulate_order != B200_ACCUMULATE_REFERENCE)
     return fail("variant.accumulate_order is unknown");
+  if (v->a_operand != B200_A_OPERAND_AUTO && v->a_operand != B200_A_OPERAND_SMEM) return fail("variant.a_operand is unknown");
   return 0;
 }
 
@@ -393,14 +394,16 @@ int plan_dense(const b200_gemm_variant* v, const DeviceState* dev, const void* a
   // roundings (or the variant has no kernel in the fused order, e.g. K-groups of 32 / 64 would gain nothing)
   if (sc_mode == SCALE_SC && v->accumulate_order == B200_ACCUMULATE_FUSED) {
     TcLaunch fused = tl;
-    fused.fast_sc = true;
+    fused.flavor = FLAVOR_FUSED_SC;
     if (tc_has(fused)) tl = fused;
   }
   bool tc_ok = tc_has(tl) && (a == nullptr || aligned16(a)) && (b == nullptr || aligned16(b));
   tc_ok = tc_ok && ((a_t ? m : kb) % 16 == 0) && ((b_t ? kb : b_cols) % 16 == 0);  // TMA needs 16-byte pitches
+  // fused SwiGLU reads the gate block at column n of a B stored [Kb, 2n]: a TMA x coordinate, multiples of 16 bytes
+  if (swiglu && !b_t && n % 16 != 0) tc_ok = false;
   if (v->path == B200_PATH_SIMT) tc_ok = false;
   if (v->path == B200_PATH_TCGEN05 && !tc_ok)
-    return fail("the tcgen05 kernel needs 16-byte aligned operands, operand pitches that are multiples of 16 bytes, and a kernel instantiated for the variant");
+    return fail("the tcgen05 kernel needs 16-byte aligned operands, operand pitches that are multiples of 16 bytes (for a fused SwiGLU over B [Kb, 2n]: n a multiple of 16), and a kernel instantiated for the variant");
   if (!tc_ok && pl.slices > 1)
     return fail("split_k > 1 runs on the tensor-core kernel only (layouts NN / NT per-channel, NN subchannel; 16-byte aligned operands and pitches)");
   pl.tensor_core = tc_ok;
@@ -420,6 +423,12 @@ int plan_dense(const b200_gemm_variant* v, const DeviceState* dev, const void* a
     const bool want = v->cta_group == B200_CTA_GROUP_PAIR ||
                       (v->cta_group == B200_CTA_GROUP_AUTO && m > BM && 87 * pair_waves <= 100 * single_waves);
     if (want && sc_ok && dev->max_pair_clusters > 0 && tc_has(pair)) tl = pair;
+    // per-channel int4 pairs with a row-major A: the kernel that keeps the unpacked A operand in TMEM
+    if (tl.pair && v->a_operand != B200_A_OPERAND_SMEM) {
+      TcLaunch through_tmem = tl;
+      through_tmem.flavor = FLAVOR_TMEM_A;
+      if (tc_has(through_tmem)) tl = through_tmem;
+    }
     pl.kernel = tl;
     pl.tile_rows = tl.pair ? 2 * BM : BM;
     pl.tiles_m = (m + pl.tile_rows - 1) / pl.tile_rows;
@@ -542,7 +551,10 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
     if (a_t) {
       if (int rc = make_map_2d(&ta, a, m, kb, m, NBLK, BK / 2, 0, "A"); rc != 0) return rc;
     } else {
-      if (int rc = make_map_2d(&ta, a, kb, m, kb, BK / 2, BM, 0, "A"); rc != 0) return rc;
+      // A through TMEM: a thread of the unpack warps reads one 64-byte row of the staging tile, so TMA writes the tile
+      // with the 64-byte swizzle
+      const int a_swizzle = pl.kernel.flavor == FLAVOR_TMEM_A ? 64 : 0;
+      if (int rc = make_map_2d(&ta, a, kb, m, kb, BK / 2, BM, a_swizzle, "A"); rc != 0) return rc;
     }
     if (b_t) {
       if (int rc = make_map_2d(&tb, b, kb, b_cols, kb, BK / 2, NBLK, 0, "B"); rc != 0) return rc;
@@ -683,8 +695,13 @@ int launch_ragged_fwd_impl(
     return launch_simt(sp, block_rows, num_tasks, stream);
   }
 
+  if (tl.pair && v->a_operand != B200_A_OPERAND_SMEM) {
+    TcLaunch through_tmem = tl;
+    through_tmem.flavor = FLAVOR_TMEM_A;
+    if (tc_has(through_tmem)) tl = through_tmem;
+  }
   CUtensorMap ta, tb;
-  if (int rc = make_map_2d(&ta, lhs, k_packed, m, k_packed, BK / 2, BM, 0, "lhs"); rc != 0) return rc;
+  if (int rc = make_map_2d(&ta, lhs, k_packed, m, k_packed, BK / 2, BM, tl.flavor == FLAVOR_TMEM_A ? 64 : 0, "lhs"); rc != 0) return rc;
   if (b_t) {
     if (int rc = make_map_2d(&tb, rhs, k_packed, static_cast<uint64_t>(groups) * n, k_packed, BK / 2, NBLK, 0, "rhs"); rc != 0)
       return rc;

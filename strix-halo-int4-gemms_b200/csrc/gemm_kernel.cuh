@@ -213,8 +213,28 @@ __device__ __forceinline__ void expand_word(uint32_t w, uint32_t& lo, uint32_t& 
   hi = w & 0xF0F0F0F0u;
 }
 
-template <bool kInt4, bool kAMn, bool kBMn, int kScale, int kEpi, int kOut, bool kMaskK, bool k2Cta = false>
+// Kernel flavours (mutually exclusive refinements of an instantiation):
+//   FLAVOR_FUSED_SC  subchannel kernels: the fused order of roundings of the per-K-group accumulation (see the kernel)
+//   FLAVOR_TMEM_A    per-channel int4 CTA-pair kernels with a row-major A: the unpacked A operand goes to TMEM
+//                    (tcgen05.st by the unpack warps, tcgen05.mma with a TMEM A operand) instead of shared memory
+enum : int { FLAVOR_PLAIN = 0, FLAVOR_FUSED_SC = 1, FLAVOR_TMEM_A = 2 };
+
+template <bool kInt4, bool kAMn, bool kBMn, int kScale, int kEpi, int kOut, bool kMaskK, bool k2Cta = false, int kFlavor = FLAVOR_PLAIN>
 struct KernelTraits {
+  static constexpr bool kFastSc = kFlavor == FLAVOR_FUSED_SC;
+  // A through TMEM.  The int4 kernels are bound by the shared-memory data pipe: per 128-deep K block a CTA of a
+  // pair writes 16 KB of unpacked A to shared memory and the tensor core reads it back.  With A in TMEM neither
+  // crosses that pipe (a third of its traffic).  TMEM then holds ONE 256-column accumulator (the epilogue of a
+  // tile no longer overlaps the next tile's MMAs) and seven 32-column A stages; the deeper operand pipeline
+  // (seven stages filled during the epilogue) wins most of that overlap back.
+  static constexpr bool kTmemA = kFlavor == FLAVOR_TMEM_A;
+  static_assert(!kTmemA || (kInt4 && !kAMn && k2Cta && kScale == SCALE_PC && !kMaskK),
+                "A through TMEM: per-channel int4 CTA-pair kernels with a row-major A");
+  static constexpr int kAccBufs = kTmemA ? 1 : 2;          // accumulator buffers of 256 TMEM columns
+  static constexpr int kTmemAStage0 = 256;                 // first TMEM column of the A stages (32 columns each)
+  // Eight unpack warps beside the eight epilogue warps of a subchannel kernel were tried (640 threads: 168 registers
+  // for the epilogue, 56 for the unpack warps): the spills made it a third slower than four unpack warps.
+  static constexpr bool kWideSc = false;
   // K-masked kernels serve the grouped backward pass: short reductions (a group's tokens) and large fp32
   // tiles.  Their epilogue is the long pole, so it gets eight warps (two per TMEM lane quarter, half of the
   // columns each) and one of the operand stages as output staging.
@@ -222,15 +242,15 @@ struct KernelTraits {
   // Kernels with eight epilogue warps re-balance registers between roles with setmaxnreg, which works on
   // warpgroups (4 consecutive warps): warps 0..3 = TMA, MMA and two idle warps, 4..11 = epilogue, then unpack
   // (4 warps next to the subchannel epilogue, whose running sums need 200 registers; 8 warps otherwise).
-  static constexpr bool kRegBalance = (kScale == SCALE_SC) || kShortK;
-  static constexpr int kUnpackWarps = kInt4 ? ((kScale == SCALE_SC) ? 4 : 8) : 0;
+  static constexpr bool kRegBalance = (kScale == SCALE_SC) || kShortK || kTmemA;
+  static constexpr int kUnpackWarps = kInt4 ? ((kScale == SCALE_SC && !kWideSc) ? 4 : 8) : 0;
   static constexpr int kEpiWarps = kRegBalance ? 8 : 4;
   static constexpr int kEpiWarp0 = kRegBalance ? 4 : 2;
   static constexpr int kUnpackWarp0 = kEpiWarp0 + kEpiWarps;
   static constexpr int kThreads = (kUnpackWarp0 + kUnpackWarps) * 32;
-  static constexpr int kRegsLight = (kScale == SCALE_SC) ? 32 : 40;    // TMA / MMA warpgroup (subchannel: every register counts)
-  static constexpr int kRegsUnpack = 80;
-  static constexpr int kRegsEpilogue = (kScale == SCALE_SC) ? 200 : 136;  // subchannel: 128 running sums + room to interleave
+  static constexpr int kRegsLight = (kWideSc || kTmemA) ? 24 : (kScale == SCALE_SC) ? 32 : 40;    // TMA / MMA warpgroup (subchannel: every register counts)
+  static constexpr int kRegsUnpack = kWideSc ? 56 : kTmemA ? 72 : 80;
+  static constexpr int kRegsEpilogue = kWideSc ? 168 : (kScale == SCALE_SC) ? 200 : 136;  // subchannel: 128 running sums + room to interleave
   // The most registers per thread the kernel can be launched with (what the compiler may use before the
   // re-balance).  setmaxnreg.dec must not name more than a warp currently has, setmaxnreg.inc not less: a
   // role whose target is at or above this cap raises its count, one below it lowers it, and the host checks
@@ -242,12 +262,13 @@ struct KernelTraits {
   // A CTA of a pair holds one 128-wide block of B (the MMA reads the other one from the peer), so
   // its stages are a third smaller and more of them fit.
   static constexpr int kBBlocks = k2Cta ? 1 : 2;
-  static constexpr int kStages = kShortK ? (k2Cta ? 3 : 2)
+  static constexpr int kStages = kTmemA ? 7
+                                 : kShortK ? (k2Cta ? 3 : 2)
                                  : kInt4 ? (k2Cta ? 4 : 3)
                                          : (k2Cta ? 6 : 4);  // int8 UMMA stages
   static constexpr int kPkStages =
-      kInt4 ? (k2Cta ? (kShortK ? 3 : 4) : 2) : 0; // packed staging stages
-  static constexpr int kA8Bytes = BM * BK;                  // 16 KB
+      kTmemA ? 4 : kInt4 ? (k2Cta ? (kShortK ? 3 : 4) : 2) : 0; // packed staging stages
+  static constexpr int kA8Bytes = kTmemA ? 0 : BM * BK;     // 16 KB (none: A lives in TMEM)
   static constexpr int kB8Bytes = kBBlocks * NBLK * BK;     // 32 KB (pair: 16 KB)
   static constexpr int kStageBytes = kA8Bytes + kB8Bytes;
   static constexpr int kPkABytes = BM * BK / 2;             // 8 KB
@@ -271,20 +292,25 @@ struct KernelTraits {
   static_assert(kSmemBytes <= 232448, "over the 227 KB of shared memory a CTA can have");
 };
 
-// kFastSc (subchannel kernels only): the order of roundings of the per-K-group accumulation.
+// FLAVOR_FUSED_SC (kFastSc, subchannel kernels only): the order of roundings of the per-K-group accumulation.
 //   false: out += (f32(acc_g) * sa_g) * sb_g with every rounding of the reference (api.py:316-324): bit-identical;
 //   true : out = fma(f32(acc_g) * sa_g, sb_g, out): the last multiply and the add share one rounding, and the
 //          int -> float step costs nothing because the accumulators start from a bias in TMEM (see the epilogue).
 //          Two instructions per element and K-group instead of four; results differ from the reference in the
 //          last bits of the fp32 running sum, far inside the bf16 output tolerance.
-template <bool kInt4, bool kAMn, bool kBMn, int kScale, int kEpi, int kOut, bool kMaskK, bool k2Cta = false, bool kFastSc = false>
-__global__ void __launch_bounds__(KernelTraits<kInt4, kAMn, kBMn, kScale, kEpi, kOut, kMaskK, k2Cta>::kThreads, 1)
+template <bool kInt4, bool kAMn, bool kBMn, int kScale, int kEpi, int kOut, bool kMaskK, bool k2Cta = false, int kFlavor = FLAVOR_PLAIN>
+__global__ void __launch_bounds__(KernelTraits<kInt4, kAMn, kBMn, kScale, kEpi, kOut, kMaskK, k2Cta, kFlavor>::kThreads, 1)
 gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b,
                        const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
-  using T = KernelTraits<kInt4, kAMn, kBMn, kScale, kEpi, kOut, kMaskK, k2Cta>;
+  using T = KernelTraits<kInt4, kAMn, kBMn, kScale, kEpi, kOut, kMaskK, k2Cta, kFlavor>;
+  constexpr bool kFastSc = T::kFastSc;
+  constexpr bool kTmemA = T::kTmemA;
   static_assert(kBMn || !kMaskK, "K masking is applied to an MN-major B operand");
   static_assert(!kFastSc || kScale == SCALE_SC, "the fused accumulation order belongs to the subchannel kernels");
+  // accumulator buffer and barrier phase of the grp-th accumulator hand-over
+  auto acc_buf = [](int grp) { return grp % T::kAccBufs; };
+  auto acc_phase = [](int grp) -> uint32_t { return static_cast<uint32_t>((grp / T::kAccBufs) & 1); };
   constexpr int S = T::kStages;
   constexpr int PS = T::kPkStages;
 
@@ -487,8 +513,8 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int total_mma = (w.k_len + 31) / 32;  // K=32 steps that hold real data
       if constexpr (kScale == SCALE_PC) {
         if (w.num_kb == 0) continue;
-        const int b = grp & 1;
-        if (!__all_sync(0xFFFFFFFFu, wait_acc_empty(b, ((grp >> 1) & 1) ^ 1u))) { ok = false; break; }
+        const int b = acc_buf(grp);
+        if (!__all_sync(0xFFFFFFFFu, wait_acc_empty(b, acc_phase(grp) ^ 1u))) { ok = false; break; }
         for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
@@ -500,9 +526,14 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const int left = total_mma - kb * (BK / 32);
 #pragma unroll
             for (int k = 0; k < BK / 32; ++k) {
-              if (k < left)
-                mma(tmem_base + b * BN, make_desc(a_lo + k * kAStep), make_desc(b_lo + k * kBStep),
-                    (kb | k) != 0 ? 1u : 0u);
+              if (k < left) {
+                if constexpr (kTmemA)
+                  umma_i8_pair_tmem_a(tmem_base + b * BN, tmem_base + T::kTmemAStage0 + s * 32 + k * 8,
+                                      make_desc(b_lo + k * kBStep), idesc, (kb | k) != 0 ? 1u : 0u);
+                else
+                  mma(tmem_base + b * BN, make_desc(a_lo + k * kAStep), make_desc(b_lo + k * kBStep),
+                      (kb | k) != 0 ? 1u : 0u);
+              }
             }
             commit(empty_bar(s));
 #ifndef B200_TEST_DROP_ACC_FULL_SIGNAL
@@ -668,8 +699,8 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         int b = 0;
         if (!zero_tile) {
-          b = grp & 1;
-          if (!__all_sync(0xFFFFFFFFu, mbar_wait(acc_full_bar(b), (grp >> 1) & 1, ctx, 30))) { ok = false; break; }
+          b = acc_buf(grp);
+          if (!__all_sync(0xFFFFFFFFu, mbar_wait(acc_full_bar(b), acc_phase(grp), ctx, 30))) { ok = false; break; }
           tc_fence_after_sync();
         }
         // TMA store path: the warp's 32 rows must all be rows this tile owns (rows past the end of a
@@ -1072,9 +1103,58 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if constexpr (T::kUnpackRaises) reg_alloc<T::kRegsUnpack>();
       else reg_dealloc<T::kRegsUnpack>();
     }
+    if constexpr (kTmemA) {
+      // A through TMEM: the first four unpack warps own A, the other four B (below).  Warp w may touch TMEM lanes
+      // 32 (w % 4) .. + 31, and lane = row of A: a thread expands the 64 packed bytes of ITS row of the K block
+      // (four 16-byte loads from the staging tile, which TMA wrote with the 64-byte swizzle so that rows 64 bytes
+      // apart do not collide on banks) into 32 words of int8 and stores them to the stage's 32 TMEM columns.
+      // Packed chunk c (bytes 16c .. 16c+15) gives K slots 32c .. 32c+15 (low nibbles) and 32c+16 .. 32c+31 (high
+      // nibbles), the same order the B operand uses; a 32-bit TMEM column holds four consecutive slots.
+      if (warp < T::kUnpackWarp0 + 4) {
+        const int row = (warp & 3) * 32 + lane;
+        const uint32_t a_lane = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t src_row = row * 64;
+        const uint32_t sw = (row >> 1) & 3;
+        int it = 0;
+        bool ok = true;
+        for (int t = tile0; t < num_tiles && ok; t += tile_step) {
+          const TileWork w = decode_tile<kAMn, k2Cta>(p, t, cta_rank);
+          for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
+            const int ps = it % PS;
+            const uint32_t pph = (it / PS) & 1;
+            const int s = it % S;
+            const uint32_t ph = (it / S) & 1;
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(pk_full_bar(ps), pph, ctx, 42))) { ok = false; break; }
+            const uint8_t* pk_a = smem_gen + S * T::kStageBytes + ps * T::kPkStageBytes;
+            uint4 x[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) x[c] = *reinterpret_cast<const uint4*>(pk_a + src_row + ((c ^ sw) << 4));
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(empty_bar(s), ph ^ 1u, ctx, 43))) { ok = false; break; }
+            tc_fence_after_sync();
+            uint32_t r[32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              expand_word(x[c].x, r[8 * c + 0], r[8 * c + 4]);
+              expand_word(x[c].y, r[8 * c + 1], r[8 * c + 5]);
+              expand_word(x[c].z, r[8 * c + 2], r[8 * c + 6]);
+              expand_word(x[c].w, r[8 * c + 3], r[8 * c + 7]);
+            }
+            tmem_st_32x32b_x32(tmem_base + a_lane + T::kTmemAStage0 + s * 32, r);
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+              mbar_arrive(full_bar(s));
+              mbar_arrive(pk_empty_bar(ps));
+            }
+          }
+        }
+      }
+    }
     if constexpr (kInt4) {
-      constexpr int UT = T::kUnpackWarps * 32;           // unpack threads: 128 or 256
-      const int ut = threadIdx.x - T::kUnpackWarp0 * 32;
+      if (!kTmemA || warp >= T::kUnpackWarp0 + 4) {
+      constexpr int UT = kTmemA ? 128 : T::kUnpackWarps * 32;           // unpack threads of this role: 128 or 256
+      const int ut = threadIdx.x - (T::kUnpackWarp0 + (kTmemA ? 4 : 0)) * 32;
       // Every item is one 16-byte load of packed data (32 nibbles) that becomes two 16-byte
       // chunks of int8.  Per-thread offsets are fixed; successive passes add a constant.
       //
@@ -1113,17 +1193,19 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           // B items are handled in batches of at most 4 to bound the registers holding raw data
           constexpr int kBItems = (k2Cta ? 512 : 1024) / UT;  // one or two 128-wide blocks of B
           constexpr int kBBatch = kBItems < 4 ? kBItems : 4;
-          uint4 xa[512 / UT];
+          uint4 xa[kTmemA ? 1 : 512 / UT];
           uint4 xb[kBBatch];  // K-major B: packed tile [256 rows][64 B], same item scheme as K-major A
           auto load_b = [&](int j) -> uint4 {
             if constexpr (kBMn && k2Cta) return *reinterpret_cast<const uint4*>(pk_b + m_src0 + j * (kMRowsPerPass * 128));
             else if constexpr (kBMn) return *reinterpret_cast<const uint4*>(pk_b + b_src0 + j * (kBRowsPerPass * 128));
             else return *reinterpret_cast<const uint4*>(pk_b + a_src0 + j * (kARowsPerPass * 64));
           };
+          if constexpr (!kTmemA) {
 #pragma unroll
-          for (int j = 0; j < 512 / UT; ++j) {
-            if constexpr (!kAMn) xa[j] = *reinterpret_cast<const uint4*>(pk_a + a_src0 + j * (kARowsPerPass * 64));
-            else xa[j] = *reinterpret_cast<const uint4*>(pk_a + m_src0 + j * (kMRowsPerPass * 128));
+            for (int j = 0; j < 512 / UT; ++j) {
+              if constexpr (!kAMn) xa[j] = *reinterpret_cast<const uint4*>(pk_a + a_src0 + j * (kARowsPerPass * 64));
+              else xa[j] = *reinterpret_cast<const uint4*>(pk_a + m_src0 + j * (kMRowsPerPass * 128));
+            }
           }
 #pragma unroll
           for (int j = 0; j < kBBatch; ++j) xb[j] = load_b(j);
@@ -1131,7 +1213,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           uint8_t* a8 = smem_gen + s * T::kStageBytes;
           uint8_t* b8 = a8 + T::kA8Bytes;
 #pragma unroll
-          for (int j = 0; j < 512 / UT; ++j) {
+          for (int j = 0; j < (kTmemA ? 0 : 512 / UT); ++j) {
             uint4 lo, hi;
             expand_word(xa[j].x, lo.x, hi.x);
             expand_word(xa[j].y, lo.y, hi.y);
@@ -1195,6 +1277,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
       }
+      }  // B role (or the only unpack role)
     }
   }
 

@@ -268,6 +268,19 @@ __device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t a_desc, u
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same with the A operand read from TMEM instead of shared memory: [a_tmem] addresses lanes = rows of this
+// CTA's 128 rows of A and 8 columns per K = 32 step (four int8 values of consecutive k per 32-bit column).
+__device__ __forceinline__ void umma_i8_pair_tmem_a(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                                    uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], [%1], %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive (count 1) on the mbarrier at this shared-memory offset in BOTH CTAs of the pair once every
 // MMA issued so far by this thread has completed.  (A barrier signal, not a data load.)
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {

@@ -10,9 +10,9 @@
 namespace b200 {
 namespace {
 
-template <bool I4, bool AMN, bool BMN, int SC, int EP, int OT, bool MK, bool PR, bool FS>
+template <bool I4, bool AMN, bool BMN, int SC, int EP, int OT, bool MK, bool PR, int FL>
 TcKernelInfo describe() {
-  using T = KernelTraits<I4, AMN, BMN, SC, EP, OT, MK, PR>;
+  using T = KernelTraits<I4, AMN, BMN, SC, EP, OT, MK, PR, FL>;
   TcKernelInfo info{};
   info.int4 = I4;
   info.a_mn = AMN;
@@ -22,8 +22,8 @@ TcKernelInfo describe() {
   info.out = OT;
   info.mask_k = MK;
   info.pair = PR;
-  info.fast_sc = FS;
-  info.fn = reinterpret_cast<const void*>(&gemm_i8_tcgen05_kernel<I4, AMN, BMN, SC, EP, OT, MK, PR, FS>);
+  info.flavor = FL;
+  info.fn = reinterpret_cast<const void*>(&gemm_i8_tcgen05_kernel<I4, AMN, BMN, SC, EP, OT, MK, PR, FL>);
   info.threads = T::kThreads;
   info.smem_bytes = T::kSmemBytes;
   info.reg_pool_needed = T::kRegPoolNeeded;
@@ -40,8 +40,8 @@ TcKernelInfo describe() {
 template <int kPart>
 void register_part(std::vector<TcKernelInfo>& out) {
   constexpr int kBase = __COUNTER__ + 1;
-#define X(I4, AMN, BMN, SC, EP, OT, MK, PR, FS) \
-  if constexpr ((__COUNTER__ - kBase) % kTcParts == kPart) out.push_back(describe<I4, AMN, BMN, SC, EP, OT, MK, PR, FS>());
+#define X(I4, AMN, BMN, SC, EP, OT, MK, PR, FL) \
+  if constexpr ((__COUNTER__ - kBase) % kTcParts == kPart) out.push_back(describe<I4, AMN, BMN, SC, EP, OT, MK, PR, FL>());
   B200_FOR_EACH_TC_KERNEL(X)
 #undef X
 }

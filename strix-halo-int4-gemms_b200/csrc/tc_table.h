@@ -15,7 +15,7 @@ struct TcKernelInfo {
   bool int4, a_mn, b_mn;
   int scale, epi, out;
   bool mask_k, pair;
-  bool fast_sc;  // subchannel kernels: the fused accumulation order (see gemm_i8_tcgen05_kernel)
+  int flavor;    // FLAVOR_* of gemm_kernel.cuh
   // how to launch it
   const void* fn;
   int threads;
@@ -27,105 +27,112 @@ struct TcKernelInfo {
   bool unpack_raises;
 };
 
-//   int4   A-MN   B-MN   scale     epilogue    out       maskK  pair   fused subchannel order
+//   int4   A-MN   B-MN   scale     epilogue    out       maskK  pair   flavour
 #define B200_FOR_EACH_TC_KERNEL(X)                                       \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, false, false)      \
-  X(true, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, false, false)     \
-  X(true, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false, false)    \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, false, false, false)       \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, false, false)       \
-  X(true, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false, false)      \
-  X(true, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, false)     \
-  X(true, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, false)    \
-  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, false, false, false)       \
-  X(true, true, true, SCALE_PC, EPI_NONE, OUT_BF16, false, false, false)       \
-  X(true, true, true, SCALE_PC, EPI_NONE, OUT_F32, false, false, false)        \
-  X(true, true, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false, false)       \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, true, false, false)        \
-  X(true, true, true, SCALE_PC, EPI_NONE, OUT_F32, true, false, false)         \
-  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, true, false, false)        \
-  X(true, true, true, SCALE_SC, EPI_NONE, OUT_F32, true, false, false)         \
-  X(true, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, false, false)     \
-  X(true, false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false, false, false)    \
-  X(true, false, false, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false, false)   \
-  X(true, false, false, SCALE_PC, EPI_NONE, OUT_F32, false, false, false)      \
-  X(true, false, false, SCALE_PC, EPI_NONE, OUT_S32, false, false, false)      \
-  X(true, false, false, SCALE_SC, EPI_NONE, OUT_BF16, false, false, false)     \
-  X(true, false, false, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, false)    \
-  X(true, false, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, false)   \
-  X(true, false, false, SCALE_SC, EPI_NONE, OUT_F32, false, false, false)      \
-  X(false, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, false, false)     \
-  X(false, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, false, false)    \
-  X(false, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false, false)   \
-  X(false, false, true, SCALE_PC, EPI_NONE, OUT_F32, false, false, false)      \
-  X(false, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, false, false)      \
-  X(false, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false, false)     \
-  X(false, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, false)    \
-  X(false, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, false)   \
-  X(false, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, false, false)    \
-  X(false, false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false, false, false)   \
-  X(false, false, false, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false, false)  \
-  X(false, false, false, SCALE_PC, EPI_NONE, OUT_F32, false, false, false)     \
-  X(false, false, false, SCALE_PC, EPI_NONE, OUT_S32, false, false, false)     \
-  X(false, false, false, SCALE_SC, EPI_NONE, OUT_BF16, false, false, false)    \
-  X(false, false, false, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, false)   \
-  X(false, false, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, false)  \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, false, FLAVOR_PLAIN)      \
+  X(true, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_PLAIN)     \
+  X(true, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_PLAIN)    \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, false, false, FLAVOR_PLAIN)       \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, false, FLAVOR_PLAIN)       \
+  X(true, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false, FLAVOR_PLAIN)      \
+  X(true, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_PLAIN)     \
+  X(true, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_PLAIN)    \
+  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, false, false, FLAVOR_PLAIN)       \
+  X(true, true, true, SCALE_PC, EPI_NONE, OUT_BF16, false, false, FLAVOR_PLAIN)       \
+  X(true, true, true, SCALE_PC, EPI_NONE, OUT_F32, false, false, FLAVOR_PLAIN)        \
+  X(true, true, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false, FLAVOR_PLAIN)       \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, true, false, FLAVOR_PLAIN)        \
+  X(true, true, true, SCALE_PC, EPI_NONE, OUT_F32, true, false, FLAVOR_PLAIN)         \
+  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, true, false, FLAVOR_PLAIN)        \
+  X(true, true, true, SCALE_SC, EPI_NONE, OUT_F32, true, false, FLAVOR_PLAIN)         \
+  X(true, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, false, FLAVOR_PLAIN)     \
+  X(true, false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_PLAIN)    \
+  X(true, false, false, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_PLAIN)   \
+  X(true, false, false, SCALE_PC, EPI_NONE, OUT_F32, false, false, FLAVOR_PLAIN)      \
+  X(true, false, false, SCALE_PC, EPI_NONE, OUT_S32, false, false, FLAVOR_PLAIN)      \
+  X(true, false, false, SCALE_SC, EPI_NONE, OUT_BF16, false, false, FLAVOR_PLAIN)     \
+  X(true, false, false, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_PLAIN)    \
+  X(true, false, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_PLAIN)   \
+  X(true, false, false, SCALE_SC, EPI_NONE, OUT_F32, false, false, FLAVOR_PLAIN)      \
+  X(false, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, false, FLAVOR_PLAIN)     \
+  X(false, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_PLAIN)    \
+  X(false, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_PLAIN)   \
+  X(false, false, true, SCALE_PC, EPI_NONE, OUT_F32, false, false, FLAVOR_PLAIN)      \
+  X(false, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, false, FLAVOR_PLAIN)      \
+  X(false, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false, FLAVOR_PLAIN)     \
+  X(false, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_PLAIN)    \
+  X(false, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_PLAIN)   \
+  X(false, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, false, FLAVOR_PLAIN)    \
+  X(false, false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_PLAIN)   \
+  X(false, false, false, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_PLAIN)  \
+  X(false, false, false, SCALE_PC, EPI_NONE, OUT_F32, false, false, FLAVOR_PLAIN)     \
+  X(false, false, false, SCALE_PC, EPI_NONE, OUT_S32, false, false, FLAVOR_PLAIN)     \
+  X(false, false, false, SCALE_SC, EPI_NONE, OUT_BF16, false, false, FLAVOR_PLAIN)    \
+  X(false, false, false, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_PLAIN)   \
+  X(false, false, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_PLAIN)  \
   /* layout TT: A [Kb, M] with B [N, Kb] */                              \
-  X(true, true, false, SCALE_PC, EPI_NONE, OUT_BF16, false, false, false)      \
-  X(true, true, false, SCALE_PC, EPI_NONE, OUT_F32, false, false, false)       \
-  X(true, true, false, SCALE_SC, EPI_NONE, OUT_BF16, false, false, false)      \
-  X(false, true, true, SCALE_PC, EPI_NONE, OUT_BF16, false, false, false)      \
-  X(false, true, false, SCALE_PC, EPI_NONE, OUT_BF16, false, false, false)     \
+  X(true, true, false, SCALE_PC, EPI_NONE, OUT_BF16, false, false, FLAVOR_PLAIN)      \
+  X(true, true, false, SCALE_PC, EPI_NONE, OUT_F32, false, false, FLAVOR_PLAIN)       \
+  X(true, true, false, SCALE_SC, EPI_NONE, OUT_BF16, false, false, FLAVOR_PLAIN)      \
+  X(false, true, true, SCALE_PC, EPI_NONE, OUT_BF16, false, false, FLAVOR_PLAIN)      \
+  X(false, true, false, SCALE_PC, EPI_NONE, OUT_BF16, false, false, FLAVOR_PLAIN)     \
   /* CTA pairs (cta_group::2): 256 x 256 output tiles over two SMs */   \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true, false)       \
-  X(true, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, true, false)      \
-  X(true, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, true, false)     \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, false, true, false)        \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, true, false)        \
-  X(true, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, true, false)       \
-  X(true, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, true, false)     \
-  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, false, true, false)        \
-  X(true, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, true, false)      \
-  X(false, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true, false)      \
-  X(false, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, true, false)     \
-  X(false, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, true, false)    \
-  X(false, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, true, false)       \
-  X(false, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, true, false)      \
-  X(false, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, true, false)     \
-  X(false, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, true, false)    \
-  X(false, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, true, false)     \
-  X(false, false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false, true, false)    \
-  X(true, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, true, false)      \
-  X(true, true, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true, false)        \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true, FLAVOR_PLAIN)       \
+  X(true, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, true, FLAVOR_PLAIN)      \
+  X(true, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, true, FLAVOR_PLAIN)     \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, false, true, FLAVOR_PLAIN)        \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, true, FLAVOR_PLAIN)        \
+  X(true, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, true, FLAVOR_PLAIN)       \
+  X(true, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, true, FLAVOR_PLAIN)     \
+  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, false, true, FLAVOR_PLAIN)        \
+  X(true, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, true, FLAVOR_PLAIN)      \
+  X(false, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true, FLAVOR_PLAIN)      \
+  X(false, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, true, FLAVOR_PLAIN)     \
+  X(false, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, true, FLAVOR_PLAIN)    \
+  X(false, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, true, FLAVOR_PLAIN)       \
+  X(false, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, true, FLAVOR_PLAIN)      \
+  X(false, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, true, FLAVOR_PLAIN)     \
+  X(false, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, true, FLAVOR_PLAIN)    \
+  X(false, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, true, FLAVOR_PLAIN)     \
+  X(false, false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false, true, FLAVOR_PLAIN)    \
+  X(true, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, true, FLAVOR_PLAIN)      \
+  X(true, true, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true, FLAVOR_PLAIN)        \
   /* grouped backward on CTA pairs */                                    \
-  X(true, true, true, SCALE_PC, EPI_NONE, OUT_F32, true, true, false)          \
-  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, true, true, false)         \
-  X(true, true, true, SCALE_SC, EPI_NONE, OUT_F32, true, true, false)          \
-  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, true, true, false)      \
+  X(true, true, true, SCALE_PC, EPI_NONE, OUT_F32, true, true, FLAVOR_PLAIN)          \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, true, true, FLAVOR_PLAIN)         \
+  X(true, true, true, SCALE_SC, EPI_NONE, OUT_F32, true, true, FLAVOR_PLAIN)          \
+  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, true, true, FLAVOR_PLAIN)      \
   /* subchannel kernels in the fused accumulation order (the default of dense launches) */ \
-  X(true, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false, true)    \
-  X(true, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, true)   \
-  X(true, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, true)  \
-  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, false, false, true)     \
-  X(true, true, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false, true)     \
-  X(true, false, false, SCALE_SC, EPI_NONE, OUT_BF16, false, false, true)   \
-  X(true, false, false, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, true)  \
-  X(true, false, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, true) \
-  X(true, false, false, SCALE_SC, EPI_NONE, OUT_F32, false, false, true)    \
-  X(false, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false, true)   \
-  X(false, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, true)  \
-  X(false, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, true) \
-  X(false, false, false, SCALE_SC, EPI_NONE, OUT_BF16, false, false, true)  \
-  X(false, false, false, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, true) \
-  X(false, false, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, true) \
-  X(true, true, false, SCALE_SC, EPI_NONE, OUT_BF16, false, false, true)    \
-  X(true, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, true, true)     \
-  X(true, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, true, true)    \
-  X(true, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, true, true)   \
-  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, false, true, true)      \
-  X(false, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, true, true)    \
-  X(false, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, true, true)   \
-  X(false, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, true, true)
+  X(true, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false, FLAVOR_FUSED_SC)    \
+  X(true, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_FUSED_SC)   \
+  X(true, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_FUSED_SC)  \
+  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, false, false, FLAVOR_FUSED_SC)     \
+  X(true, true, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false, FLAVOR_FUSED_SC)     \
+  X(true, false, false, SCALE_SC, EPI_NONE, OUT_BF16, false, false, FLAVOR_FUSED_SC)   \
+  X(true, false, false, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_FUSED_SC)  \
+  X(true, false, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_FUSED_SC) \
+  X(true, false, false, SCALE_SC, EPI_NONE, OUT_F32, false, false, FLAVOR_FUSED_SC)    \
+  X(false, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false, FLAVOR_FUSED_SC)   \
+  X(false, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_FUSED_SC)  \
+  X(false, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_FUSED_SC) \
+  X(false, false, false, SCALE_SC, EPI_NONE, OUT_BF16, false, false, FLAVOR_FUSED_SC)  \
+  X(false, false, false, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_FUSED_SC) \
+  X(false, false, false, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_FUSED_SC) \
+  X(true, true, false, SCALE_SC, EPI_NONE, OUT_BF16, false, false, FLAVOR_FUSED_SC)    \
+  X(true, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, true, FLAVOR_FUSED_SC)     \
+  X(true, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, true, FLAVOR_FUSED_SC)    \
+  X(true, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, true, FLAVOR_FUSED_SC)   \
+  X(true, false, true, SCALE_SC, EPI_NONE, OUT_F32, false, true, FLAVOR_FUSED_SC)      \
+  X(false, false, true, SCALE_SC, EPI_NONE, OUT_BF16, false, true, FLAVOR_FUSED_SC)    \
+  X(false, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, true, FLAVOR_FUSED_SC)   \
+  X(false, false, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, true, FLAVOR_FUSED_SC) \
+  /* per-channel int4 CTA-pair kernels with the A operand in TMEM (the default where they exist) */ \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true, FLAVOR_TMEM_A)    \
+  X(true, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, true, FLAVOR_TMEM_A)   \
+  X(true, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, true, FLAVOR_TMEM_A)  \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, false, true, FLAVOR_TMEM_A)     \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, true, FLAVOR_TMEM_A)     \
+  X(true, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, true, FLAVOR_TMEM_A)
 
 constexpr int kTcParts = 8;  // translation units the list above is spread over (entry i goes to part i % kTcParts)
 

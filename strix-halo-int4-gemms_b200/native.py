@@ -32,6 +32,7 @@ SCHEDULE_PERSISTENT, SCHEDULE_TILE_PER_CTA = 0, 1
 CTA_GROUP_AUTO, CTA_GROUP_SINGLE, CTA_GROUP_PAIR = 0, 1, 2
 LAUNCHED_NOTHING, LAUNCHED_TCGEN05, LAUNCHED_TCGEN05_PAIR, LAUNCHED_SIMT = 0, 1, 2, 3
 ACCUMULATE_FUSED, ACCUMULATE_REFERENCE = 0, 1
+A_OPERAND_AUTO, A_OPERAND_SMEM = 0, 1
 
 # Order of roundings of subchannel dense launches made through the registry / public API: "fused" (default; the
 # last multiply and the add of each K-group share one rounding) or "reference" (every rounding of the reference's
@@ -98,7 +99,8 @@ class GemmVariant(ctypes.Structure):
         ("schedule", ctypes.c_int32),
         ("cta_group", ctypes.c_int32),
         ("accumulate_order", ctypes.c_int32),
-        ("reserved", ctypes.c_int32 * 4),
+        ("a_operand", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 3),
     ]
 
 
@@ -362,6 +364,7 @@ def make_variant(
     schedule: KernelSchedule = KernelSchedule.STANDARD,
     cta_group: int | None = None,
     accumulate_order: int | None = None,
+    a_operand: int = A_OPERAND_AUTO,
 ) -> GemmVariant:
     """The C variant record of one launch.  ``schedule`` is the registry's launch form; ``cta_group``
     (CTA_GROUP_*) overrides the form's CTA choice when given."""
@@ -378,6 +381,7 @@ def make_variant(
     variant.schedule, form_cta_group = SCHEDULE_LAUNCH[schedule]
     variant.cta_group = int(form_cta_group if cta_group is None else cta_group)
     variant.accumulate_order = int(_ACCUMULATION_ORDER if accumulate_order is None else accumulate_order)
+    variant.a_operand = int(a_operand)
     return variant
 
 

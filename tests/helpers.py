@@ -75,7 +75,7 @@ def assert_close_rms(got: np.ndarray, want: np.ndarray, *, rtol=1e-2, atol_rms=1
 # GPU side: calls through the C ABI (ctypes) with arbitrary shapes
 # ----------------------------------------------------------------------------------------------
 def abi_dense(pkg, case, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue="none", out="bf16", path=0, schedule="persistent", cta_group=0,
-              order="reference"):
+              order="reference", a_operand=0):
     """One dense launch through ``b200_int4_gemms_launch_dense``; returns the CUDA output tensor.  ``order``: the
     subchannel accumulation order, "reference" (every rounding of the reference math: what the bit-equality checks
     use) or "fused" (the library's default)."""
@@ -94,6 +94,7 @@ def abi_dense(pkg, case, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue=
         schedule=pkg.KernelSchedule.TILE_PER_CTA if schedule == "tile_per_cta" else pkg.KernelSchedule.STANDARD,
         cta_group=cta_group,
         accumulate_order=native.ACCUMULATE_REFERENCE if order == "reference" else native.ACCUMULATE_FUSED,
+        a_operand=a_operand,
     )
     native.launch_dense(
         variant, device_index=0, stream_handle=torch.cuda.current_stream().cuda_stream,

@@ -221,6 +221,48 @@ def test_fused_order_other_layouts(pkg):
     check_dense(pkg, m=256, n=512, k=1024, dtype="int8", layout="nt", sub=256, epilogue="relu2", order="fused", seed=4)
 
 
+@pytest.mark.parametrize("layout", ["nn", "nt"])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 128), (512, 768, 1024), (384, 520 // 8 * 8 + 8, 2176), (1024, 2048, 4096), (4096, 512, 96)])
+def test_a_operand_through_tmem_equals_shared_memory_and_the_oracle(pkg, layout, m, n, k):
+    """Per-channel int4 CTA pairs keep the unpacked A operand in TMEM by default; b200_gemm_variant.a_operand pins
+    shared memory.  Same integers either way: raw accumulators and scaled outputs must be bit-identical, over more
+    K blocks than the seven TMEM stages, partial tiles in M and N, and a K that ends inside a K block."""
+    from strix_halo_int4_gemms_b200 import native
+
+    case = dense_case(pkg, m=m, n=n, k=k, layout=layout, seed=m + n + k)
+    outs = ("s32", "bf16") if layout == "nn" else ("bf16",)
+    for out in outs:
+        tmem = abi_dense(pkg, case, m=m, n=n, k=k, layout=layout, out=out, path=TCGEN05, cta_group=PAIR, a_operand=native.A_OPERAND_AUTO)
+        smem = abi_dense(pkg, case, m=m, n=n, k=k, layout=layout, out=out, path=TCGEN05, cta_group=PAIR, a_operand=native.A_OPERAND_SMEM)
+        assert torch.equal(tmem, smem), out
+        if out == "s32":
+            np.testing.assert_array_equal(tmem.cpu().numpy(), oracle.int32_accumulators(case["a"].numpy(), case["b"].numpy(), int4=True, layout=layout))
+        else:
+            np.testing.assert_array_equal(as_f32(tmem), oracle_dense(case, layout=layout))
+    if layout == "nn":
+        for epilogue in ("relu2", "swiglu"):
+            nn = n // 32 * 16 if epilogue == "swiglu" else n      # D a multiple of 16: the gate block starts on a TMA boundary
+            ecase = dense_case(pkg, m=m, n=nn, k=k, epilogue=epilogue, seed=k)
+            a = abi_dense(pkg, ecase, m=m, n=nn, k=k, epilogue=epilogue, path=TCGEN05, cta_group=PAIR, a_operand=native.A_OPERAND_AUTO)
+            b = abi_dense(pkg, ecase, m=m, n=nn, k=k, epilogue=epilogue, path=TCGEN05, cta_group=PAIR, a_operand=native.A_OPERAND_SMEM)
+            assert torch.equal(a, b), epilogue
+
+
+def test_swiglu_with_an_unaligned_gate_offset_leaves_the_tensor_core_path(pkg):
+    """D = 264: the gate half of B [Kb, 2D] starts at byte column 264, which no TMA load can start at.  The library
+    must notice on the host (a launch would raise an illegal-instruction fault): AUTO takes the CUDA-core kernel,
+    forcing the tensor-core path is refused."""
+    from strix_halo_int4_gemms_b200 import native
+
+    m, d, k = 128, 264, 256
+    case = dense_case(pkg, m=m, n=d, k=k, epilogue="swiglu", seed=2)
+    got = abi_dense(pkg, case, m=m, n=d, k=k, epilogue="swiglu")
+    assert native.last_launch_path() == native.LAUNCHED_SIMT
+    assert_close_rms(as_f32(got), oracle_dense(case, epilogue="swiglu"), what="swiglu D=264")
+    with pytest.raises(RuntimeError, match="n a multiple of 16"):
+        abi_dense(pkg, case, m=m, n=d, k=k, epilogue="swiglu", path=TCGEN05)
+
+
 def test_runs_are_deterministic(pkg):
     case = dense_case(pkg, m=512, n=768, k=1024, sub=256, seed=21)
     first = abi_dense(pkg, case, m=512, n=768, k=1024, sub=256, out="f32")
