@@ -371,14 +371,22 @@ def make_pass(ctx: Ctx, w, problems):
         scale = pkg.ScaleSpec(pkg.ScaleMode.SUBCHANNEL, w["sub"]) if w["sub"] else pc
         variant = native.make_variant(dtype=pkg.OperandDType(w["dtype"]), layout=pkg.GemmLayout.NN, scale=scale,
                                       epilogue=pkg.Epilogue(w["epilogue"]), out_dtype=native.OUT_BF16)
+        # the scratch the library asks for (partial sums of the balanced tail); one buffer: the launches of a pass run in
+        # stream order
+        scratch = max(int(native.load_dispatch_library().b200_int4_gemms_dense_workspace_bytes(
+            __import__("ctypes").byref(variant), w["m"], p["n"], w["k"])) for p in problems)
+        workspace = torch.zeros(max(scratch, 16), dtype=torch.uint8, device=ctx.device)  # flag words start out zero
         args = [dict(a_ptr=p["a"].data_ptr(), b_ptr=p["b"].data_ptr(), a_scale_ptr=p["a_scale"].data_ptr(),
-                     b_scale_ptr=p["b_scale"].data_ptr(), c_ptr=p["out"].data_ptr(), n=p["n"]) for p in problems]
+                     b_scale_ptr=p["b_scale"].data_ptr(), c_ptr=p["out"].data_ptr(), n=p["n"],
+                     workspace_ptr=workspace.data_ptr() if scratch else 0, workspace_bytes=scratch) for p in problems]
+        run_keepalive = workspace
 
         def run():
             for ptrs in args:
                 # the stream is looked up per call: under CUDA-graph capture the current stream is the capturing one
                 native.launch_dense(variant, device_index=device_index, stream_handle=torch.cuda.current_stream().cuda_stream,
                                     m=w["m"], k=w["k"], **ptrs)
+        run.workspace = run_keepalive   # keeps the scratch alive as long as the callable
         return run, len(problems)
     if w["kind"] == "ragged_fwd":
         # the task height ragged_dot_int4 itself picks for groups this large: 256-row tasks on pairs of SMs

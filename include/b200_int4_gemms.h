@@ -70,9 +70,20 @@ enum { B200_CTA_GROUP_AUTO = 0, B200_CTA_GROUP_SINGLE = 1, B200_CTA_GROUP_PAIR =
 enum { B200_ACCUMULATE_FUSED = 0, B200_ACCUMULATE_REFERENCE = 1 };
 
 /* Where the unpacked A operand of an int4 CTA-pair kernel lives between the unpack warps and the tensor core.
- * AUTO: in TMEM where the library has that kernel (per-channel scales, A stored [M, Kb]): a third less traffic
- * through the shared-memory pipe that bounds these kernels.  SMEM: always shared memory.  Bit-identical results. */
-enum { B200_A_OPERAND_AUTO = 0, B200_A_OPERAND_SMEM = 1 };
+ * TMEM (per-channel scales, A stored [M, Kb]): a third less traffic through the shared-memory pipe, but a single
+ * accumulator buffer, so the epilogue of a tile is not hidden behind the next tile's MMAs.  AUTO picks TMEM for
+ * long reductions (K >= 6144), shared memory otherwise; SMEM / TMEM force one (TMEM falls back to shared memory
+ * where no such kernel exists).  Bit-identical results. */
+enum { B200_A_OPERAND_AUTO = 0, B200_A_OPERAND_SMEM = 1, B200_A_OPERAND_TMEM = 2 };
+
+/* Balanced tail of dense per-channel launches.  When the last wave of the persistent grid fills at most half of the
+ * CTAs (CTA pairs), its tiles can be cut along K into 2 .. 4 parts that run side by side; one part owns the tile and
+ * starts from (or, without a full wave before it, ends by adding) the other parts' exact s32 partial sums, which
+ * travel through the workspace b200_int4_gemms_dense_workspace_bytes asks for: bit-identical results, no atomics on
+ * data.  AUTO uses it for launches without a full wave whose parts keep at least 32 K blocks (few tiles, long
+ * reductions: up to 1.4 x faster); ALWAYS also where full waves precede the tail (parts of at least 4 K blocks; at
+ * 4096^3 the measured gain was within noise); OFF: whole tiles only.  Without a workspace whole tiles are scheduled. */
+enum { B200_TAIL_AUTO = 0, B200_TAIL_OFF = 1, B200_TAIL_ALWAYS = 2 };
 
 typedef struct b200_gemm_variant {
   int32_t dtype;      /* B200_DTYPE_*      */
@@ -89,7 +100,8 @@ typedef struct b200_gemm_variant {
   int32_t cta_group;  /* B200_CTA_GROUP_*: SMs per output tile of the tensor-core kernel */
   int32_t accumulate_order; /* B200_ACCUMULATE_*: subchannel dense launches only */
   int32_t a_operand;  /* B200_A_OPERAND_* */
-  int32_t reserved[3];
+  int32_t tail_balance; /* B200_TAIL_* */
+  int32_t reserved[2];
 } b200_gemm_variant;
 
 /* Replaces amd_strix_halo_kernels_dispatch_version (dispatch.cpp:206). */
@@ -122,8 +134,13 @@ int b200_int4_gemms_reset_device_status(int device_index);
  *   a_scale    bf16 [m] (per-channel) or [m, ceil(k/S)] (subchannel)
  *   b_scale    bf16 [cols] or [ceil(k/S), cols], cols = n (2*n for SWIGLU)
  *   c          [m, n] in variant->out_dtype
- *   workspace  device scratch of at least b200_int4_gemms_dense_workspace_bytes(...) bytes,
- *              may be NULL when that is 0
+ *   workspace  device scratch (16-byte aligned) of b200_int4_gemms_dense_workspace_bytes(...) bytes: required
+ *              for split_k > 1; optional otherwise (the balanced tail of B200_TAIL_AUTO is used only when it is
+ *              there).  Launches that share a workspace must not overlap in time.  The first 4 KB hold flag words
+ *              that must be zero before a launch and are left zero by it: the library clears them itself the first
+ *              time it sees a workspace (address, size, device), so pass freshly allocated memory as it is; after
+ *              freeing a workspace, or after a kernel reported a failed wait, call
+ *              b200_int4_gemms_reset_device_status, which also makes the library clear the flag words again
  *   m, n, k    logical sizes (k counts int4 values, not bytes) */
 int b200_int4_gemms_launch_dense(const b200_gemm_variant* variant, int device_index,
                                  uintptr_t stream_handle, const void* a, const void* b,
@@ -158,7 +175,8 @@ typedef struct b200_dense_plan {
   int32_t tile_cols; /* 256, or 128 for SwiGLU (up + gate) */
   int32_t group_m;   /* raster width in row tiles */
   int32_t split_k;   /* slices actually used */
-  int32_t reserved[2];
+  int32_t tail_units; /* > 0: the balanced tail is used, over this many CTAs (pairs), given a workspace */
+  int32_t reserved[1];
 } b200_dense_plan;
 int b200_int4_gemms_plan_dense(const b200_gemm_variant* variant, int device_index, int32_t m, int32_t n,
                                int32_t k, b200_dense_plan* plan);

@@ -271,7 +271,8 @@ int check_variant(const b200_gemm_variant* v) {
   if (v->cta_group < B200_CTA_GROUP_AUTO || v->cta_group > B200_CTA_GROUP_PAIR) return fail("variant.cta_group is unknown");
   if (v->accumulate_order != B200_ACCUMULATE_FUSED && v->accumulate_order != B200_ACCUMULATE_REFERENCE)
     return fail("variant.accumulate_order is unknown");
-  if (v->a_operand != B200_A_OPERAND_AUTO && v->a_operand != B200_A_OPERAND_SMEM) return fail("variant.a_operand is unknown");
+  if (v->a_operand < B200_A_OPERAND_AUTO || v->a_operand > B200_A_OPERAND_TMEM) return fail("variant.a_operand is unknown");
+  if (v->tail_balance < B200_TAIL_AUTO || v->tail_balance > B200_TAIL_ALWAYS) return fail("variant.tail_balance is unknown");
   return 0;
 }
 
@@ -285,6 +286,33 @@ int launch_simt(const SimtParams& sp, int rows_per_z, int z, cudaStream_t stream
   return 0;
 }
 
+// The flag words of a balanced-tail workspace must be zero before its first launch; the kernels leave them zero.  The
+// library clears them when it first sees a workspace (address, size, device) and remembers the last few it has seen,
+// so that back-to-back launches do not carry a memset between them.
+struct SeenWorkspace {
+  const void* ptr = nullptr;
+  size_t bytes = 0;
+  int device = -1;
+};
+constexpr int kSeenWorkspaces = 32;
+SeenWorkspace g_seen_workspaces[kSeenWorkspaces];
+int g_seen_next = 0;
+std::mutex g_seen_mutex;
+
+void forget_workspaces(int device) {
+  std::lock_guard<std::mutex> lock(g_seen_mutex);
+  for (SeenWorkspace& w : g_seen_workspaces)
+    if (w.device == device) w = SeenWorkspace{};
+}
+
+bool workspace_seen_before(const void* ptr, size_t bytes, int device) {
+  std::lock_guard<std::mutex> lock(g_seen_mutex);
+  for (const SeenWorkspace& w : g_seen_workspaces)
+    if (w.ptr == ptr && w.bytes == bytes && w.device == device) return true;
+  g_seen_workspaces[g_seen_next] = SeenWorkspace{ptr, bytes, device};
+  g_seen_next = (g_seen_next + 1) % kSeenWorkspaces;
+  return false;
+}
 }  // namespace
 
 extern "C" int b200_int4_gemms_dispatch_version(void) { return 1; }
@@ -335,6 +363,7 @@ extern "C" int b200_int4_gemms_device_status(int device_index, int32_t* detail) 
 
 extern "C" int b200_int4_gemms_reset_device_status(int device_index) {
   if (device_index < 0 || device_index >= kMaxDevices) return 1;
+  forget_workspaces(device_index);  // a kernel that gave up may have left flag words set: clear them at the next launch
   DeviceState& st = g_devices[device_index];
   if (st.ready && st.status_host != nullptr) std::memset(st.status_host, 0, 4 * sizeof(int));
   return 0;
@@ -354,7 +383,19 @@ struct DensePlan {
   int slices = 1;        // effective split-K factor (<= variant.split_k)
   int k_per_slice = 0;
   bool integer_partials = false;
+  int tail_units = 0;    // > 0: balanced tail over this many scheduling units (needs the workspace)
+  int tail_split = 0, tail_waves = 0, tail_rest = 0;
 };
+
+// Workspace of the balanced tail: one partial-sum slot of 2 x 128 x 256 s32 per scheduling unit, then the flags.
+constexpr size_t kTailSlotBytes = 2u * BM * BN * sizeof(int);
+// Layout: the flag words first (a fixed 4 KB, enough for kTailMaxUnits units, so that they sit in the same place
+// whatever kernel form uses the workspace next), then one partial-sum slot per unit.
+constexpr size_t kTailFlagBytes = 4096;
+size_t tail_workspace_bytes(int units) { return kTailFlagBytes + static_cast<size_t>(units) * kTailSlotBytes; }
+
+constexpr int kTailMaxUnits = 160;  // an upper bound on the SMs of a device, for sizing a workspace without one
+static_assert(kTailMaxUnits * 4 * sizeof(int) <= 4096, "flag words of every unit fit the fixed flag area");
 
 int effective_slices(int k, int unit, int requested, int* k_per_slice) {
   const int units = (k + unit - 1) / unit;
@@ -366,7 +407,7 @@ int effective_slices(int k, int unit, int requested, int* k_per_slice) {
 
 // `a`, `b`, `c` only decide alignment; nullptr means "assume aligned".
 int plan_dense(const b200_gemm_variant* v, const DeviceState* dev, const void* a, const void* b, int32_t m,
-               int32_t n, int32_t k, DensePlan* plan) {
+               int32_t n, int32_t k, size_t have_workspace_bytes, DensePlan* plan) {
   const bool int4 = v->dtype == B200_DTYPE_INT4;
   const bool swiglu = v->epilogue == B200_EPILOGUE_SWIGLU;
   const int b_cols = swiglu ? 2 * n : n;
@@ -423,12 +464,6 @@ int plan_dense(const b200_gemm_variant* v, const DeviceState* dev, const void* a
     const bool want = v->cta_group == B200_CTA_GROUP_PAIR ||
                       (v->cta_group == B200_CTA_GROUP_AUTO && m > BM && 87 * pair_waves <= 100 * single_waves);
     if (want && sc_ok && dev->max_pair_clusters > 0 && tc_has(pair)) tl = pair;
-    // per-channel int4 pairs with a row-major A: the kernel that keeps the unpacked A operand in TMEM
-    if (tl.pair && v->a_operand != B200_A_OPERAND_SMEM) {
-      TcLaunch through_tmem = tl;
-      through_tmem.flavor = FLAVOR_TMEM_A;
-      if (tc_has(through_tmem)) tl = through_tmem;
-    }
     pl.kernel = tl;
     pl.tile_rows = tl.pair ? 2 * BM : BM;
     pl.tiles_m = (m + pl.tile_rows - 1) / pl.tile_rows;
@@ -440,6 +475,44 @@ int plan_dense(const b200_gemm_variant* v, const DeviceState* dev, const void* a
     const int max_units = tl.pair ? dev->max_pair_clusters : dev->sm_count;  // tiles in flight
     pl.grid = (num_tiles < max_units ? num_tiles : max_units) * cta_per_tile;
     if (v->schedule == B200_SCHEDULE_TILE_PER_CTA) pl.grid = num_tiles * cta_per_tile;
+    // Balanced tail: the tiles of a last wave that fills at most half of the units are cut along K into 2 .. 4 parts
+    // that run side by side (per-channel scales: the partial sums that cross units are exact integers, so the result
+    // does not change).  Worth it while one wave is a visible share of the run; needs the caller's workspace.
+    const int kb_per_tile = (k + BK - 1) / BK;
+    const int rest = num_tiles % max_units, waves = num_tiles / max_units;
+    // AUTO keeps to launches without a full wave (few tiles, long reductions), where the gain is large; with full
+    // waves before the tail the measured gain at 4096^3 was within noise for CTA pairs, so that takes ALWAYS.
+    const bool tail_wanted = v->tail_balance == B200_TAIL_ALWAYS || (v->tail_balance == B200_TAIL_AUTO && waves == 0);
+    if (tail_wanted && v->schedule == B200_SCHEDULE_PERSISTENT && sc_mode == SCALE_PC && pl.slices == 1 &&
+        rest > 0 && waves <= 4 && have_workspace_bytes >= tail_workspace_bytes(max_units)) {
+      // With a full wave before it the owner part starts from the other parts' sum, loaded while earlier tiles run:
+      // parts of at least 4 K blocks pay.  Without one (fewer tiles than units) the parts run side by side and the
+      // sums are added after the MMAs, a few serial trips to L2: only long reductions (32 K blocks per part) pay.
+      const int min_part = waves > 0 ? 4 : 32;
+      int split = max_units / rest;
+      if (split > 4) split = 4;
+      while (split >= 2 && kb_per_tile / split < min_part) --split;
+      TcLaunch with_tail = tl;
+      with_tail.flavor = FLAVOR_TAIL;
+      if (split >= 2 && tl.flavor == FLAVOR_PLAIN && tc_has(with_tail)) {
+        tl = with_tail;
+        pl.kernel = tl;
+        pl.tail_units = waves > 0 ? max_units : split * rest;  // no full wave: only the units that hold a part
+        pl.tail_split = split;
+        pl.tail_waves = waves;
+        pl.tail_rest = rest;
+        pl.grid = pl.tail_units * cta_per_tile;
+      }
+    }
+    // per-channel int4 pairs with a row-major A: the kernel that keeps the unpacked A operand in TMEM
+    // (one accumulator buffer: the epilogue of a tile is not hidden behind the next tile's MMAs, which the saved
+    // shared-memory traffic outweighs from about 48 K blocks per tile on: +9 % at K = 8192, even at K = 4096)
+    if (pl.tail_units == 0 && tl.pair && (v->a_operand == B200_A_OPERAND_TMEM || (v->a_operand == B200_A_OPERAND_AUTO && k >= 48 * BK))) {
+      TcLaunch through_tmem = tl;
+      through_tmem.flavor = FLAVOR_TMEM_A;
+      if (tc_has(through_tmem)) tl = through_tmem;
+    }
+    pl.kernel = tl;
   } else {
     pl.tiles_m = (m + 3) / 4;  // the CUDA-core kernel: 4 rows x 64 columns per block
     pl.tiles_n = (n + 63) / 64;
@@ -457,7 +530,16 @@ extern "C" int b200_int4_gemms_last_launch_path(void) { return g_last_path; }
 
 extern "C" size_t b200_int4_gemms_dense_workspace_bytes(const b200_gemm_variant* variant, int32_t m,
                                                         int32_t n, int32_t k) {
-  if (variant == nullptr || variant->split_k <= 1 || m <= 0 || n <= 0 || k <= 0) return 0;
+  if (variant == nullptr || m <= 0 || n <= 0 || k <= 0) return 0;
+  if (variant->split_k <= 1) {
+    // what the balanced tail would use if the launch qualifies for it (optional: without it whole tiles are scheduled)
+    const long long tiles = static_cast<long long>((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+    const bool base = variant->scale_mode == B200_SCALE_PER_CHANNEL && variant->schedule == B200_SCHEDULE_PERSISTENT &&
+                      variant->path != B200_PATH_SIMT;
+    const bool may_balance = base && ((variant->tail_balance == B200_TAIL_ALWAYS && k >= 8 * BK) ||
+                                      (variant->tail_balance == B200_TAIL_AUTO && tiles < kTailMaxUnits && k >= 64 * BK));
+    return may_balance ? tail_workspace_bytes(kTailMaxUnits) : 0;
+  }
   const int sc = variant->scale_mode == B200_SCALE_SUBCHANNEL ? variant->subchannel : 0;
   int per = 0;
   const int slices = effective_slices(k, sc > BK ? sc : BK, variant->split_k, &per);
@@ -474,7 +556,7 @@ extern "C" int b200_int4_gemms_plan_dense(const b200_gemm_variant* v, int device
   DeviceState* dev = nullptr;
   if (int rc = ensure_device(device_index, &dev); rc != 0) return rc;
   DensePlan pl;
-  if (int rc = plan_dense(v, dev, nullptr, nullptr, m, n, k, &pl); rc != 0) return rc;
+  if (int rc = plan_dense(v, dev, nullptr, nullptr, m, n, k, static_cast<size_t>(-1), &pl); rc != 0) return rc;
   std::memset(out, 0, sizeof(*out));
   out->path = !pl.tensor_core ? B200_LAUNCHED_SIMT : (pl.kernel.pair ? B200_LAUNCHED_TCGEN05_PAIR : B200_LAUNCHED_TCGEN05);
   out->grid = pl.grid;
@@ -482,6 +564,7 @@ extern "C" int b200_int4_gemms_plan_dense(const b200_gemm_variant* v, int device
   out->tile_cols = pl.tensor_core ? pl.tile_cols : 64;
   out->group_m = pl.tensor_core ? pl.group_m : 0;
   out->split_k = pl.slices;
+  out->tail_units = pl.tail_units;
   return 0;
 }
 
@@ -512,7 +595,8 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
   const int scale_cols = sc_mode == SCALE_SC ? (k + v->subchannel - 1) / v->subchannel : 1;
 
   DensePlan pl;
-  if (int rc = plan_dense(v, dev, a, b, m, n, k, &pl); rc != 0) return rc;
+  const size_t usable_workspace = (workspace != nullptr && aligned16(workspace)) ? workspace_bytes : 0;
+  if (int rc = plan_dense(v, dev, a, b, m, n, k, usable_workspace, &pl); rc != 0) return rc;
 
   if (!pl.tensor_core) {
     SimtParams sp{};
@@ -595,6 +679,19 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
   p.b_scale = static_cast<const __nv_bfloat16*>(b_scale);
   p.out = split ? workspace : c;
   p.status = dev->status_dev;
+  if (pl.tail_units > 0) {
+    p.tail_units = pl.tail_units;
+    p.tail_split = pl.tail_split;
+    p.tail_waves = pl.tail_waves;
+    p.tail_rest = pl.tail_rest;
+    p.tail_kb_per_tile = (k + BK - 1) / BK;
+    p.tail_flags = static_cast<int*>(workspace);
+    p.tail_partials = reinterpret_cast<int*>(static_cast<char*>(workspace) + kTailFlagBytes);
+    if (!workspace_seen_before(workspace, workspace_bytes, device_index)) {
+      cudaError_t err = cudaMemsetAsync(p.tail_flags, 0, kTailFlagBytes, stream);
+      if (err != cudaSuccess) return fail_cuda("cudaMemsetAsync(balanced-tail flags)", err);
+    }
+  }
   CUtensorMap tc;
   std::memset(&tc, 0, sizeof(tc));
   if (!split) {
@@ -695,7 +792,7 @@ int launch_ragged_fwd_impl(
     return launch_simt(sp, block_rows, num_tasks, stream);
   }
 
-  if (tl.pair && v->a_operand != B200_A_OPERAND_SMEM) {
+  if (tl.pair && (v->a_operand == B200_A_OPERAND_TMEM || (v->a_operand == B200_A_OPERAND_AUTO && k >= 48 * BK))) {
     TcLaunch through_tmem = tl;
     through_tmem.flavor = FLAVOR_TMEM_A;
     if (tc_has(through_tmem)) tl = through_tmem;

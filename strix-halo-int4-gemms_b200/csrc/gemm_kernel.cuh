@@ -64,6 +64,19 @@ struct GemmParams {
   // result to out + s * M * ldc (a [k_slices, M, N] workspace); a second kernel adds the slices in a fixed order
   int k_slices;          // 1: no split
   int k_per_slice;       // multiple of BK (and of the K-group length)
+  // balanced tail (dense, per-channel).  Whole tiles go round-robin over the scheduling units (CTA pairs or CTAs) for
+  // the full waves; the tail_rest tiles of the last, partly filled wave are cut along K into tail_split parts that run
+  // on different units at the same time.  Part 0 is the tile's owner: it is the LAST segment of units 0 .. rest-1 and
+  // starts from the sum of the other parts (exact s32 partial sums), which units p * rest + j (part p of rest tile j)
+  // produce as their FIRST segment, store to tail_partials and announce in tail_flags.
+  int tail_units;        // 0: off; else the number of scheduling units of the launch
+  int tail_split;        // parts per rest tile (2 .. 4)
+  int tail_waves;        // full waves of whole tiles
+  int tail_rest;         // tiles of the last wave
+  int tail_kb_per_tile;
+  int* tail_partials;    // [units][2 ranks][128][256] s32
+  int* tail_flags;       // [units][2 ranks][2]: epilogue warps that have written their part, and readers that have seen
+                         // it; zero before the first launch on a workspace, and again at the end of every launch
   // ragged
   int num_groups;
   int rows_per_group_a;  // rows of the stacked A map per group (bwd)
@@ -94,6 +107,8 @@ struct TileWork {
   int k_len;         // reduction length of this tile (bwd: group_sizes[g])
   int k_valid;       // number of valid k (masking, bwd); INT_MAX otherwise
   int k_first;       // first valid k (1 when a flat group starts on the odd token of a byte, else 0)
+  int part;          // balanced tail: PART_WHOLE, PART_OWNER (part 0 + the other parts' partial sums), PART_PRODUCER
+  int part_slot;     // partial-sum slot written (producer: its own unit)
   int out_row0;      // output row of tile row 0
   int row_lo, row_hi;// valid output rows [lo, hi)
   long long out_off; // element offset added to out (bwd: g*M*N)
@@ -102,21 +117,44 @@ struct TileWork {
   long long sb_off;  // element offset of this tile's b_scale base
 };
 
-// `rank` is the CTA's rank in its pair (always 0 for single-CTA kernels).  A pair works on 256 rows of
+enum : int { PART_WHOLE = 0, PART_OWNER = 1, PART_PRODUCER = 2 };
+
+// `rank` is the CTA's rank in its pair (always 0 for single-CTA kernels); `unit` the scheduling unit (cluster or CTA)
+// index, used by the balanced-tail schedule, in which `t` counts the unit's own segments.  A pair works on 256 rows of
 // output: rank r owns rows [128 r, 128 r + 128) of them, and p.tiles_m counts 256-row tiles.
-template <bool kAMn, bool k2Cta>
-__device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t, int rank) {
+template <bool kAMn, bool k2Cta, bool kTail = false>
+__device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t, int rank, int unit) {
   constexpr int RM = k2Cta ? 2 * BM : BM;  // output rows per scheduled tile
   const int rank_rows = k2Cta ? rank * BM : 0;
   TileWork w;
   w.k_valid = 0x7FFFFFFF;
   w.k_first = 0;
   w.kb0 = 0;
+  w.part = PART_WHOLE;
+  w.part_slot = 0;
   w.out_off = 0;
   w.out_row_base = 0;
   w.sa_off = 0;
   w.sb_off = 0;
   if (p.mode == MODE_DENSE) {
+    // balanced tail: segment t of this unit (a producer part first, whole tiles, an owner part last)
+    int seg_kb0 = 0, seg_kb1 = 0;
+    if (kTail && p.tail_units > 0) {
+      const int kbt = p.tail_kb_per_tile;
+      const bool producer = unit >= p.tail_rest && unit < p.tail_split * p.tail_rest;
+      const int wave = producer ? t - 1 : t;
+      seg_kb1 = kbt;
+      if (wave >= 0 && wave < p.tail_waves) {
+        t = wave * p.tail_units + unit;
+      } else {
+        const int part = producer ? unit / p.tail_rest : 0;
+        t = p.tail_waves * p.tail_units + unit % p.tail_rest;
+        seg_kb0 = part * kbt / p.tail_split;
+        seg_kb1 = (part + 1) * kbt / p.tail_split;
+        w.part = producer ? PART_PRODUCER : PART_OWNER;
+        w.part_slot = unit;
+      }
+    }
     // split-K: the slice is the slowest index of the tile list
     int slice = 0;
     if (p.k_slices > 1) {
@@ -149,6 +187,10 @@ __device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t, int 
         w.sa_off = static_cast<long long>(slice) * groups_per_slice;
         w.sb_off = static_cast<long long>(slice) * groups_per_slice * p.lds_b;
       }
+    }
+    if (kTail && p.tail_units > 0) {
+      w.kb0 = seg_kb0;
+      w.k_len = min(p.K, seg_kb1 * BK) - seg_kb0 * BK;
     }
     w.num_kb = (w.k_len + BK - 1) / BK;
     w.out_row0 = mt * RM + rank_rows;
@@ -213,11 +255,48 @@ __device__ __forceinline__ void expand_word(uint32_t w, uint32_t& lo, uint32_t& 
   hi = w & 0xF0F0F0F0u;
 }
 
+// Balanced tail: adds the other parts' partial sums (chunks [c_begin, c_end) of 32 columns, this thread's row) into the
+// accumulator buffer at `acc` (TMEM address of the warp's lanes, column 0 of the buffer).  `keep_own`: the buffer
+// already holds this unit's own sum (added to), else it is overwritten.  Slot layout: 16-byte piece i of chunk c of
+// row r at int4 index ((c * 8 + i) * 128 + r), so that a warp's 32 rows move 512 contiguous bytes per instruction.
+// Kept out of line: it runs once per launch and unit, and its registers must not weigh on the epilogue proper.
+static __device__ __noinline__ void tail_sum_into_tmem(uint32_t acc, const int4* first_part, long long part_stride, int parts,
+                                                int c_begin, int c_end, bool keep_own) {
+  for (int c = c_begin; c < c_end; ++c) {
+    uint32_t r[32];
+    if (keep_own) {
+      tmem_ld_32x32b_x32(acc + 32 * c, r);
+      tmem_ld_wait();
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) r[i] = 0u;
+    }
+    for (int part = 0; part < parts; ++part) {
+      const int4* src = first_part + part * part_stride;
+      int4 x[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = __ldcg(src + (c * 8 + i) * BM);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        r[4 * i] += static_cast<uint32_t>(x[i].x);
+        r[4 * i + 1] += static_cast<uint32_t>(x[i].y);
+        r[4 * i + 2] += static_cast<uint32_t>(x[i].z);
+        r[4 * i + 3] += static_cast<uint32_t>(x[i].w);
+      }
+    }
+    tmem_st_32x32b_x32(acc + 32 * c, r);
+  }
+  tmem_st_wait();
+}
+
 // Kernel flavours (mutually exclusive refinements of an instantiation):
 //   FLAVOR_FUSED_SC  subchannel kernels: the fused order of roundings of the per-K-group accumulation (see the kernel)
 //   FLAVOR_TMEM_A    per-channel int4 CTA-pair kernels with a row-major A: the unpacked A operand goes to TMEM
 //                    (tcgen05.st by the unpack warps, tcgen05.mma with a TMEM A operand) instead of shared memory
-enum : int { FLAVOR_PLAIN = 0, FLAVOR_FUSED_SC = 1, FLAVOR_TMEM_A = 2 };
+//   FLAVOR_TAIL      per-channel kernels that can run the balanced tail (GemmParams::tail_units): the code for parts of
+//                    tiles and their partial sums is compiled into these instantiations only, so that it does not
+//                    weigh on the register allocation of the plain kernels
+enum : int { FLAVOR_PLAIN = 0, FLAVOR_FUSED_SC = 1, FLAVOR_TMEM_A = 2, FLAVOR_TAIL = 3 };
 
 template <bool kInt4, bool kAMn, bool kBMn, int kScale, int kEpi, int kOut, bool kMaskK, bool k2Cta = false, int kFlavor = FLAVOR_PLAIN>
 struct KernelTraits {
@@ -230,6 +309,8 @@ struct KernelTraits {
   static constexpr bool kTmemA = kFlavor == FLAVOR_TMEM_A;
   static_assert(!kTmemA || (kInt4 && !kAMn && k2Cta && kScale == SCALE_PC && !kMaskK),
                 "A through TMEM: per-channel int4 CTA-pair kernels with a row-major A");
+  static constexpr bool kTail = kFlavor == FLAVOR_TAIL;
+  static_assert(!kTail || (kScale == SCALE_PC && !kMaskK), "the balanced tail belongs to the dense per-channel kernels");
   static constexpr int kAccBufs = kTmemA ? 1 : 2;          // accumulator buffers of 256 TMEM columns
   static constexpr int kTmemAStage0 = 256;                 // first TMEM column of the A stages (32 columns each)
   // Eight unpack warps beside the eight epilogue warps of a subchannel kernel were tried (640 threads: 168 registers
@@ -306,6 +387,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   using T = KernelTraits<kInt4, kAMn, kBMn, kScale, kEpi, kOut, kMaskK, k2Cta, kFlavor>;
   constexpr bool kFastSc = T::kFastSc;
   constexpr bool kTmemA = T::kTmemA;
+  constexpr bool kTail = T::kTail;
   static_assert(kBMn || !kMaskK, "K masking is applied to an MN-major B operand");
   static_assert(!kFastSc || kScale == SCALE_SC, "the fused accumulation order belongs to the subchannel kernels");
   // accumulator buffer and barrier phase of the grp-th accumulator hand-over
@@ -332,14 +414,22 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (32 + b); };
   auto acc_empty_bar = [&](int b) { return bar_base + 8u * (34 + b); };
   auto peer_full_bar = [&](int s) { return bar_base + 8u * (36 + s); };  // leader CTA of a pair only
+  const uint32_t preload_bar = bar_base + 8u * 45;  // balanced tail: the owner segment's accumulator holds its neighbour's partial sum
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * 44);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 8 * 44 + 4);
   // CTA pairs: the cluster is the scheduling unit; the leader (rank 0) issues the MMAs for both.
   const int cta_rank = k2Cta ? static_cast<int>(cluster_ctarank()) : 0;
-  const int tile0 = k2Cta ? static_cast<int>(cluster_id_x()) : static_cast<int>(blockIdx.x);
-  const int tile_step = k2Cta ? static_cast<int>(cluster_count_x()) : static_cast<int>(gridDim.x);
+  const int unit = k2Cta ? static_cast<int>(cluster_id_x()) : static_cast<int>(blockIdx.x);
+  int tile0 = unit;
+  int tile_step = k2Cta ? static_cast<int>(cluster_count_x()) : static_cast<int>(gridDim.x);
   // grouped forward with tasks built on the device: the task count is read here, not passed by the host
-  const int num_tiles = p.num_tasks_dev != nullptr ? min(*p.num_tasks_dev, p.tiles_m) * p.tiles_n : p.num_tiles;
+  int num_tiles = p.num_tasks_dev != nullptr ? min(*p.num_tasks_dev, p.tiles_m) * p.tiles_n : p.num_tiles;
+  if (kTail && p.tail_units > 0) {
+    // balanced tail: the roles walk this unit's segments
+    tile0 = 0;
+    tile_step = 1;
+    num_tiles = p.tail_waves + (unit < p.tail_split * p.tail_rest ? 1 : 0);
+  }
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -372,6 +462,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       mbar_init(acc_full_bar(b), 1);
       mbar_init(acc_empty_bar(b), (k2Cta ? 2 : 1) * T::kEpiWarps);  // pair: both CTAs' epilogue warps
     }
+    mbar_init(preload_bar, (k2Cta ? 2 : 1) * T::kEpiWarps);
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
@@ -404,7 +495,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int it = 0;
       bool ok = true;
       for (int t = tile0; t < num_tiles && ok; t += tile_step) {
-        const TileWork w = decode_tile<kAMn, k2Cta>(p, t, cta_rank);
+        const TileWork w = decode_tile<kAMn, k2Cta, kTail>(p, t, cta_rank, unit);
         for (int kbl = 0; kbl < w.num_kb; ++kbl, ++it) {
           const int kb = kbl + w.kb0;  // K block of the whole reduction (a split-K slice starts past 0)
           if constexpr (kInt4) {
@@ -484,7 +575,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int it = 0;
       bool ok = true;
       for (int t = tile0; t < num_tiles && ok; t += tile_step) {
-        const TileWork w = decode_tile<kAMn, k2Cta>(p, t, cta_rank);
+        const TileWork w = decode_tile<kAMn, k2Cta, kTail>(p, t, cta_rank, unit);
         for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
@@ -509,12 +600,19 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int grp = 0;  // accumulator hand-over counter (one per K-group)
     bool ok = true;
     for (int t = tile0; t < num_tiles && ok; t += tile_step) {
-      const TileWork w = decode_tile<kAMn, k2Cta>(p, t, cta_rank);
+      const TileWork w = decode_tile<kAMn, k2Cta, kTail>(p, t, cta_rank, unit);
       const int total_mma = (w.k_len + 31) / 32;  // K=32 steps that hold real data
       if constexpr (kScale == SCALE_PC) {
         if (w.num_kb == 0) continue;
         const int b = acc_buf(grp);
         if (!__all_sync(0xFFFFFFFFu, wait_acc_empty(b, acc_phase(grp) ^ 1u))) { ok = false; break; }
+        // balanced tail: the epilogue warps have put the neighbour's partial sum into this buffer (a unit owns at
+        // most one such tile, so the barrier is used once); the MMAs add onto it
+        const uint32_t onto = (kTail && w.part == PART_OWNER && p.tail_waves > 0) ? 1u : 0u;
+        if (onto != 0u) {
+          if (!__all_sync(0xFFFFFFFFu, mbar_wait(preload_bar, 0u, ctx, 24))) { ok = false; break; }
+          tc_fence_after_sync();
+        }
         for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
@@ -529,10 +627,10 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               if (k < left) {
                 if constexpr (kTmemA)
                   umma_i8_pair_tmem_a(tmem_base + b * BN, tmem_base + T::kTmemAStage0 + s * 32 + k * 8,
-                                      make_desc(b_lo + k * kBStep), idesc, (kb | k) != 0 ? 1u : 0u);
+                                      make_desc(b_lo + k * kBStep), idesc, ((kb | k) != 0 ? 1u : 0u) | onto);
                 else
                   mma(tmem_base + b * BN, make_desc(a_lo + k * kAStep), make_desc(b_lo + k * kBStep),
-                      (kb | k) != 0 ? 1u : 0u);
+                      ((kb | k) != 0 ? 1u : 0u) | onto);
               }
             }
             commit(empty_bar(s));
@@ -630,6 +728,58 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     };
     int store_count = 0;  // TMA stores issued by this warp (selects the staging slot)
     bool ok = true;
+    // Balanced tail: the segment this unit owns together with its right-hand neighbour (always its last one), and the
+    // segment after whose read-out this warp writes the neighbour's partial sum into the accumulator buffer that the
+    // owner segment will use (the buffer's previous user; < 0: nobody used it before, preload before the first tile).
+    int owner_seg = -1;
+    if constexpr (kTail) {
+      if (p.tail_units > 0 && p.tail_waves > 0 && unit < p.tail_rest) owner_seg = num_tiles - 1;
+    }
+    const int preload_after = owner_seg - T::kAccBufs;
+    // Slot layout: 16-byte piece i of chunk c of row r at int4 index ((c * 8 + i) * 128 + r): a warp's 32 rows read or
+    // write 512 contiguous bytes per instruction.  Producer and owner are the same kernel, so they agree on it.
+    // Waits until every other part of this unit's rest tile has been written; false when the wait was abandoned.
+    // The flags return to zero inside the launch, so that the next launch on the same workspace needs no memset
+    // between kernels: every warp that has seen a flag complete counts itself in the word beside it, and the last of
+    // the unit's epilogue warps to do so clears both.
+    auto partners_ready = [&]() -> bool {
+      bool got = true;
+      if (lane == 0) {
+        for (int part = 1; part < p.tail_split && got; ++part) {
+          int* flag = p.tail_flags + ((part * p.tail_rest + unit) * 2 + cta_rank) * 2;
+          got = flag_wait(flag, T::kEpiWarps, ctx, 32);
+          if (got && atomicAdd(flag + 1, 1) == T::kEpiWarps - 1) {
+            flag[1] = 0;
+            __threadfence();
+            flag[0] = 0;
+          }
+        }
+      }
+      return __all_sync(0xFFFFFFFFu, got);
+    };
+    // this thread's row of the first other part's slot, and the distance (in int4) from one part's slot to the next
+    const int4* first_part = reinterpret_cast<const int4*>(p.tail_partials) +
+                             static_cast<long long>((p.tail_rest + unit) * 2 + cta_rank) * (BM * BN / 4) + row_in_tile;
+    const long long part_stride = static_cast<long long>(p.tail_rest) * 2 * (BM * BN / 4);
+    constexpr int kRawChunks = 8 / (T::kEpiWarps / 4);
+    // With a full wave before it, the owner part starts from the other parts' sum: this warp writes its share of the
+    // sum into the accumulator buffer the owner part will use, right after it has read that buffer's previous tile.
+    auto preload_partner = [&]() -> bool {
+      const int b = acc_buf(owner_seg);
+      if (!partners_ready()) return false;
+      tail_sum_into_tmem(tmem_base + lane_addr + b * BN, first_part, part_stride, p.tail_split - 1, half * kRawChunks,
+                         (half + 1) * kRawChunks, false);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (k2Cta) mbar_arrive_cluster(map_to_cta(preload_bar, 0));
+        else mbar_arrive(preload_bar);
+      }
+      return true;
+    };
+    if constexpr (kTail) {
+      if (owner_seg >= 0 && preload_after < 0) ok = preload_partner();
+    }
     // Fused order.  For |x| <= 2^22 the float with bit pattern 0x4B400000 + x is exactly 1.5 * 2^23 + x.  The
     // accumulators therefore start from the integer 0x4B400000 instead of 0 (the tensor core adds the products onto
     // whatever TMEM holds): what comes back from TMEM is already the float 1.5 * 2^23 + acc, no conversion, no
@@ -660,7 +810,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     //   subchannel, 8 warps : plain -> [128*half, +128); SwiGLU -> up [64*half,+64) with gate 128+[64*half,+64)
     constexpr int kOwnCols = (kScale == SCALE_SC) ? 128 : 256;
     for (int t = tile0; t < num_tiles && ok; t += tile_step) {
-      const TileWork w = decode_tile<kAMn, k2Cta>(p, t, cta_rank);
+      const TileWork w = decode_tile<kAMn, k2Cta, kTail>(p, t, cta_rank, unit);
       const int row = w.out_row0 + row_in_tile;
       const bool row_ok = (row >= w.row_lo) && (row < w.row_hi);
       const long long sa_row = w.sa_off + static_cast<long long>(row) * (kScale == SCALE_SC ? p.scale_cols : 1);
@@ -703,6 +853,32 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (!__all_sync(0xFFFFFFFFu, mbar_wait(acc_full_bar(b), acc_phase(grp), ctx, 30))) { ok = false; break; }
           tc_fence_after_sync();
         }
+        // Balanced tail.  A producer segment ends here: its raw accumulators (the exact s32 sums of the tile's last
+        // K blocks) go to the partial-sum slot, 128 bytes per thread and chunk, and each warp announces its share.
+        // Balanced tail.  A producer segment ends here: its raw accumulators (the exact s32 sums of the tile's last
+        // K blocks) go to this unit's partial-sum slot and each warp announces its share.
+        if (kTail && w.part == PART_PRODUCER) {
+          int4* dst = reinterpret_cast<int4*>(p.tail_partials) + static_cast<long long>(w.part_slot * 2 + cta_rank) * (BM * BN / 4) + row_in_tile;
+          uint32_t r[32];
+#pragma unroll 1
+          for (int c = half * kRawChunks; c < (half + 1) * kRawChunks; ++c) {
+            tmem_ld_32x32b_x32(tmem_base + lane_addr + b * BN + 32 * c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              __stcg(dst + (c * 8 + i) * BM, make_int4(static_cast<int>(r[4 * i]), static_cast<int>(r[4 * i + 1]),
+                                                       static_cast<int>(r[4 * i + 2]), static_cast<int>(r[4 * i + 3])));
+          }
+          if (kTail && t == preload_after && !preload_partner()) { ok = false; break; }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) release_acc(b);
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) atomicAdd(p.tail_flags + (w.part_slot * 2 + cta_rank) * 2, 1);
+          ++grp;
+          continue;
+        }
         // TMA store path: the warp's 32 rows must all be rows this tile owns (rows past the end of a
         // dense output are clipped by the tensor map itself)
         const int wrow0 = w.out_row0 + q * 32;
@@ -711,8 +887,16 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t acc_addr = tmem_base + lane_addr + b * BN;
 
         // one 32-column chunk: scale, activation, store
+        // no full wave before the owner part (fewer tiles than units): the other parts run at the same time, so their
+        // sums are added here, after the MMAs, instead of being preloaded
+        if (kTail && w.part == PART_OWNER && p.tail_waves == 0) {
+          if (!partners_ready()) { ok = false; break; }
+          tail_sum_into_tmem(tmem_base + lane_addr + b * BN, first_part, part_stride, p.tail_split - 1, half * kRawChunks,
+                             (half + 1) * kRawChunks, true);
+        }
         auto process = [&](uint32_t (&r)[32], int c) {
           const int col0 = w.n0 + 32 * c;  // output column of this chunk
+
           if constexpr (kOut == OUT_S32) {
             if (row_ok) {
 #pragma unroll
@@ -742,6 +926,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               uint32_t g[32];
               tmem_ld_32x32b_x32(acc_addr + NBLK + 32 * c, g);
               tmem_ld_wait();
+
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
                 int a = static_cast<int>(g[i]);
@@ -888,14 +1073,26 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (!zero_tile) {
             tmem_ld_wait();
             tmem_ld_fence(rb);
-            if (c + 2 < c_first + kOutChunks) tmem_ld_32x32b_x32(acc_addr + 32 * (c + 2), ra);
+            if (c + 2 < c_first + kOutChunks) {
+              tmem_ld_32x32b_x32(acc_addr + 32 * (c + 2), ra);
+            } else if constexpr (kEpi != EPI_SWIGLU) {
+              // the warp's last chunk is in registers: hand the accumulator back before processing it (the SwiGLU
+              // epilogue still reads its gate columns while it processes)
+              if (kTail && t == preload_after && !preload_partner()) ok = false;
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) release_acc(b);
+            }
           }
           process(rb, c + 1);
         }
         if (!zero_tile) {
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) release_acc(b);
+          if constexpr (kEpi == EPI_SWIGLU) {
+            if (kTail && t == preload_after && !preload_partner()) ok = false;
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) release_acc(b);
+          }
           ++grp;
         }
       } else {
@@ -1000,10 +1197,17 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               tmem_ld_wait();
               tmem_ld_fence16(rb);
               tmem_st_fill_32x32b_x16(buf + sc_chunk_col(c + 1), kBiasBits);
-              if (c + 2 < kOwnCols / 16) tmem_ld_32x32b_x16(buf + sc_chunk_col(c + 2), ra);
+              if (c + 2 < kOwnCols / 16) {
+                tmem_ld_32x32b_x16(buf + sc_chunk_col(c + 2), ra);
+              } else {
+                // everything is read and re-armed: hand the buffer back before the last chunk's arithmetic
+                tmem_st_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) release_acc(b);
+              }
               accumulate(rb, c + 1);
             }
-            tmem_st_wait();
           } else {
 #pragma unroll
           for (int c = 0; c < kOwnCols / 16; ++c) {
@@ -1024,10 +1228,10 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               }
             }
           }
-          }
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) release_acc(b);
+          }
         }
         if (!ok) break;
         // activation + store, 32 output columns at a time
@@ -1118,7 +1322,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         int it = 0;
         bool ok = true;
         for (int t = tile0; t < num_tiles && ok; t += tile_step) {
-          const TileWork w = decode_tile<kAMn, k2Cta>(p, t, cta_rank);
+          const TileWork w = decode_tile<kAMn, k2Cta, kTail>(p, t, cta_rank, unit);
           for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
             const int ps = it % PS;
             const uint32_t pph = (it / PS) & 1;
@@ -1180,7 +1384,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int it = 0;
       bool ok = true;
       for (int t = tile0; t < num_tiles && ok; t += tile_step) {
-        const TileWork w = decode_tile<kAMn, k2Cta>(p, t, cta_rank);
+        const TileWork w = decode_tile<kAMn, k2Cta, kTail>(p, t, cta_rank, unit);
         for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
           const int ps = it % PS;
           const uint32_t pph = (it / PS) & 1;

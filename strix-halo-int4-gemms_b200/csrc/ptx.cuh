@@ -105,6 +105,34 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const A
   }
 }
 
+// Bounded wait for a counter in global memory that other CTAs of the same (co-resident, persistent) grid raise.
+// Same contract as mbar_wait: false when the wait was abandoned.
+__device__ __forceinline__ bool flag_wait(const int* flag, int want, const AbortCtx& ctx, int site) {
+  auto peek = [&]() -> int {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    return v;
+  };
+  if (peek() >= want) return true;
+  const unsigned long long t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (peek() >= want) return true;
+    if ((++spins & 0xFFu) == 0u) {
+      if (*ctx.cta_flag) return false;
+      if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+        *ctx.cta_flag = 1;
+        if (ctx.status != nullptr && ctx.status[0] == STATUS_OK) {
+          ctx.status[1] = static_cast<int>(blockIdx.x);
+          ctx.status[2] = site;
+          ctx.status[0] = STATUS_WAIT_TIMEOUT;
+        }
+        return false;
+      }
+    }
+  }
+}
+
 // One lane of a converged warp (the same lane every time within a call site is not guaranteed).
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;

@@ -132,7 +132,24 @@ struct TcKernelInfo {
   X(true, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, true, FLAVOR_TMEM_A)  \
   X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, false, true, FLAVOR_TMEM_A)     \
   X(true, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, true, FLAVOR_TMEM_A)     \
-  X(true, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, true, FLAVOR_TMEM_A)
+  X(true, false, false, SCALE_PC, EPI_NONE, OUT_BF16, false, true, FLAVOR_TMEM_A)   \
+  /* dense per-channel kernels with the balanced tail compiled in */                \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, false, FLAVOR_TAIL)     \
+  X(true, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_TAIL)    \
+  X(true, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_TAIL)   \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, false, false, FLAVOR_TAIL)      \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, false, FLAVOR_TAIL)      \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true, FLAVOR_TAIL)      \
+  X(true, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, true, FLAVOR_TAIL)     \
+  X(true, false, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, true, FLAVOR_TAIL)    \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_F32, false, true, FLAVOR_TAIL)       \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, true, FLAVOR_TAIL)       \
+  X(false, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, false, FLAVOR_TAIL)    \
+  X(false, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_TAIL)   \
+  X(false, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, false, FLAVOR_TAIL)     \
+  X(false, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true, FLAVOR_TAIL)     \
+  X(false, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, true, FLAVOR_TAIL)    \
+  X(false, false, true, SCALE_PC, EPI_NONE, OUT_S32, false, true, FLAVOR_TAIL)
 
 constexpr int kTcParts = 8;  // translation units the list above is spread over (entry i goes to part i % kTcParts)
 

@@ -32,7 +32,8 @@ SCHEDULE_PERSISTENT, SCHEDULE_TILE_PER_CTA = 0, 1
 CTA_GROUP_AUTO, CTA_GROUP_SINGLE, CTA_GROUP_PAIR = 0, 1, 2
 LAUNCHED_NOTHING, LAUNCHED_TCGEN05, LAUNCHED_TCGEN05_PAIR, LAUNCHED_SIMT = 0, 1, 2, 3
 ACCUMULATE_FUSED, ACCUMULATE_REFERENCE = 0, 1
-A_OPERAND_AUTO, A_OPERAND_SMEM = 0, 1
+A_OPERAND_AUTO, A_OPERAND_SMEM, A_OPERAND_TMEM = 0, 1, 2
+TAIL_AUTO, TAIL_OFF, TAIL_ALWAYS = 0, 1, 2
 
 # Order of roundings of subchannel dense launches made through the registry / public API: "fused" (default; the
 # last multiply and the add of each K-group share one rounding) or "reference" (every rounding of the reference's
@@ -100,7 +101,8 @@ class GemmVariant(ctypes.Structure):
         ("cta_group", ctypes.c_int32),
         ("accumulate_order", ctypes.c_int32),
         ("a_operand", ctypes.c_int32),
-        ("reserved", ctypes.c_int32 * 3),
+        ("tail_balance", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 2),
     ]
 
 
@@ -114,7 +116,8 @@ class DensePlan(ctypes.Structure):
         ("tile_cols", ctypes.c_int32),
         ("group_m", ctypes.c_int32),
         ("split_k", ctypes.c_int32),
-        ("reserved", ctypes.c_int32 * 2),
+        ("tail_units", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 1),
     ]
 
     def as_tuple(self) -> tuple[int, int, int, int, int, int]:
@@ -365,6 +368,7 @@ def make_variant(
     cta_group: int | None = None,
     accumulate_order: int | None = None,
     a_operand: int = A_OPERAND_AUTO,
+    tail_balance: int = TAIL_AUTO,
 ) -> GemmVariant:
     """The C variant record of one launch.  ``schedule`` is the registry's launch form; ``cta_group``
     (CTA_GROUP_*) overrides the form's CTA choice when given."""
@@ -382,6 +386,7 @@ def make_variant(
     variant.cta_group = int(form_cta_group if cta_group is None else cta_group)
     variant.accumulate_order = int(_ACCUMULATION_ORDER if accumulate_order is None else accumulate_order)
     variant.a_operand = int(a_operand)
+    variant.tail_balance = int(tail_balance)
     return variant
 
 
@@ -461,8 +466,9 @@ def launch_dense(
 
 def dense_workspace(variant: GemmVariant, *, m: int, n: int, k: int, device: Any, stream_handle: int,
                     library_path: str | Path | None = None) -> tuple[int, int]:
-    """(pointer, bytes) of the split-K scratch for a launch; (0, 0) when the variant needs none.  The buffer is
-    kept per (device, stream): launches that share it run in stream order and so never overlap."""
+    """(pointer, bytes) of the scratch a launch can use (split-K slices, partial sums of the balanced tail); (0, 0)
+    when the variant needs none.  The buffer is kept per (device, stream): launches that share it run in stream
+    order and so never overlap."""
     library = load_dispatch_library(library_path)
     need = int(library.b200_int4_gemms_dense_workspace_bytes(ctypes.byref(variant), int(m), int(n), int(k)))
     if need == 0:
@@ -474,7 +480,7 @@ def dense_workspace(variant: GemmVariant, *, m: int, n: int, k: int, device: Any
         if scratch is None or scratch.numel() < need:
             if scratch is not None:
                 _RETIRED_WORKSPACES.append(scratch)
-            scratch = torch.empty(need, dtype=torch.uint8, device=device)
+            scratch = torch.zeros(need, dtype=torch.uint8, device=device)  # the flag words of the balanced tail start out zero
             _WORKSPACES[key] = scratch
     return int(scratch.data_ptr()), int(scratch.numel())
 
@@ -603,6 +609,7 @@ def launch_ragged_fwd_kernel(
     library_path: str | Path | None = None,
     stream: Any | None = None,
     path: int = PATH_AUTO,
+    a_operand: int = A_OPERAND_AUTO,
 ) -> Any:
     """Grouped forward launch over prebuilt row-block tasks (reference native.py:533-600)."""
     torch = _torch()
@@ -618,7 +625,7 @@ def launch_ragged_fwd_kernel(
     library = load_dispatch_library(library_path)
     record = make_variant(
         dtype=OperandDType.INT4, layout=layout, scale=scale, epilogue=Epilogue.NONE,
-        out_dtype=OUT_F32 if out.dtype is torch.float32 else OUT_BF16, path=path,
+        out_dtype=OUT_F32 if out.dtype is torch.float32 else OUT_BF16, path=path, a_operand=a_operand,
     )
     groups = int(rhs.shape[0])
     task_arrays = (

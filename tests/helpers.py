@@ -75,7 +75,7 @@ def assert_close_rms(got: np.ndarray, want: np.ndarray, *, rtol=1e-2, atol_rms=1
 # GPU side: calls through the C ABI (ctypes) with arbitrary shapes
 # ----------------------------------------------------------------------------------------------
 def abi_dense(pkg, case, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue="none", out="bf16", path=0, schedule="persistent", cta_group=0,
-              order="reference", a_operand=0):
+              order="reference", a_operand=0, tail=None):
     """One dense launch through ``b200_int4_gemms_launch_dense``; returns the CUDA output tensor.  ``order``: the
     subchannel accumulation order, "reference" (every rounding of the reference math: what the bit-equality checks
     use) or "fused" (the library's default)."""
@@ -95,11 +95,18 @@ def abi_dense(pkg, case, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue=
         cta_group=cta_group,
         accumulate_order=native.ACCUMULATE_REFERENCE if order == "reference" else native.ACCUMULATE_FUSED,
         a_operand=a_operand,
+        tail_balance=native.TAIL_OFF if tail is False else (native.TAIL_ALWAYS if tail is True else native.TAIL_AUTO),
     )
+    stream = torch.cuda.current_stream().cuda_stream
+    # tail=True / False: hand the launch the workspace the balanced tail needs and ask for it wherever it applies
+    # (False switches it off in the variant);
+    # None: no workspace, as a caller that does not know about it would launch
+    workspace = native.dense_workspace(variant, m=m, n=n, k=k, device=c.device, stream_handle=stream) if tail is not None else (0, 0)
     native.launch_dense(
-        variant, device_index=0, stream_handle=torch.cuda.current_stream().cuda_stream,
+        variant, device_index=0, stream_handle=stream,
         a_ptr=dev["a"].data_ptr(), b_ptr=dev["b"].data_ptr(), a_scale_ptr=dev["a_scale"].data_ptr(),
         b_scale_ptr=dev["b_scale"].data_ptr(), c_ptr=c.data_ptr(), m=m, n=n, k=k,
+        workspace_ptr=workspace[0], workspace_bytes=workspace[1],
     )
     torch.cuda.synchronize()
     status, detail = native.device_status(0)

@@ -224,15 +224,15 @@ def test_fused_order_other_layouts(pkg):
 @pytest.mark.parametrize("layout", ["nn", "nt"])
 @pytest.mark.parametrize("m,n,k", [(256, 256, 128), (512, 768, 1024), (384, 520 // 8 * 8 + 8, 2176), (1024, 2048, 4096), (4096, 512, 96)])
 def test_a_operand_through_tmem_equals_shared_memory_and_the_oracle(pkg, layout, m, n, k):
-    """Per-channel int4 CTA pairs keep the unpacked A operand in TMEM by default; b200_gemm_variant.a_operand pins
-    shared memory.  Same integers either way: raw accumulators and scaled outputs must be bit-identical, over more
+    """Per-channel int4 CTA pairs can keep the unpacked A operand in TMEM (the library's choice for long reductions);
+    b200_gemm_variant.a_operand pins either.  Same integers either way: raw accumulators and scaled outputs must be bit-identical, over more
     K blocks than the seven TMEM stages, partial tiles in M and N, and a K that ends inside a K block."""
     from strix_halo_int4_gemms_b200 import native
 
     case = dense_case(pkg, m=m, n=n, k=k, layout=layout, seed=m + n + k)
     outs = ("s32", "bf16") if layout == "nn" else ("bf16",)
     for out in outs:
-        tmem = abi_dense(pkg, case, m=m, n=n, k=k, layout=layout, out=out, path=TCGEN05, cta_group=PAIR, a_operand=native.A_OPERAND_AUTO)
+        tmem = abi_dense(pkg, case, m=m, n=n, k=k, layout=layout, out=out, path=TCGEN05, cta_group=PAIR, a_operand=native.A_OPERAND_TMEM)
         smem = abi_dense(pkg, case, m=m, n=n, k=k, layout=layout, out=out, path=TCGEN05, cta_group=PAIR, a_operand=native.A_OPERAND_SMEM)
         assert torch.equal(tmem, smem), out
         if out == "s32":
@@ -243,7 +243,7 @@ def test_a_operand_through_tmem_equals_shared_memory_and_the_oracle(pkg, layout,
         for epilogue in ("relu2", "swiglu"):
             nn = n // 32 * 16 if epilogue == "swiglu" else n      # D a multiple of 16: the gate block starts on a TMA boundary
             ecase = dense_case(pkg, m=m, n=nn, k=k, epilogue=epilogue, seed=k)
-            a = abi_dense(pkg, ecase, m=m, n=nn, k=k, epilogue=epilogue, path=TCGEN05, cta_group=PAIR, a_operand=native.A_OPERAND_AUTO)
+            a = abi_dense(pkg, ecase, m=m, n=nn, k=k, epilogue=epilogue, path=TCGEN05, cta_group=PAIR, a_operand=native.A_OPERAND_TMEM)
             b = abi_dense(pkg, ecase, m=m, n=nn, k=k, epilogue=epilogue, path=TCGEN05, cta_group=PAIR, a_operand=native.A_OPERAND_SMEM)
             assert torch.equal(a, b), epilogue
 

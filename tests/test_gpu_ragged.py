@@ -208,3 +208,27 @@ def test_ragged_autotune_on_device(pkg):
     assert all(r.success for r in res.records) and res.best_record.tops > 0
     res = pkg.autotune_ragged_dot(mode=RaggedDotMode.BWD, m=256, n=256, k=1024, groups=4, layout=pkg.GemmLayout.TN, warmup_ms=1, rep_ms=3, continue_on_error=False)
     assert all(r.success for r in res.records) and res.shape.k == 1024
+
+
+def test_forward_pair_tasks_with_the_lhs_through_tmem(pkg):
+    """256-row tasks on CTA pairs with the unpacked lhs kept in TMEM (the library's own choice only for long K):
+    same bits as with the lhs in shared memory, and as the oracle."""
+    from strix_halo_int4_gemms_b200 import native
+
+    sizes = [300, 0, 256, 7, 129, 512, 1, 255]
+    data = make_ragged_fwd_inputs(m=sum(sizes), n=768, k=1024, group_sizes=sizes, layout=pkg.GemmLayout.NN, scale=scale_spec(pkg, 0), seed=9)
+    dev = {name: data[name].cuda() for name in ("lhs", "rhs", "a_scale", "b_scale", "group_sizes")}
+    cfg = pkg.RaggedDotConfig(block_m=256)
+    info = pkg.calculate_group_info(dev["group_sizes"], 256, align_tile=cfg.align_tile)
+    outs = []
+    for a_operand in (native.A_OPERAND_TMEM, native.A_OPERAND_SMEM):
+        out = torch.full((sum(sizes), 768), float("nan"), device="cuda", dtype=torch.bfloat16)
+        native.launch_ragged_fwd_kernel(dev["lhs"], dev["rhs"], group_info=info, a_scale=dev["a_scale"], b_scale=dev["b_scale"], out=out,
+                                        scale=scale_spec(pkg, 0), config=cfg, layout=pkg.GemmLayout.NN, rows=sum(sizes), cols=768,
+                                        k_packed=512, scale_cols=1, path=native.PATH_TCGEN05, a_operand=a_operand)
+        assert native.last_launch_path() == native.LAUNCHED_TCGEN05_PAIR
+        outs.append(out)
+    _status_clean()
+    assert torch.equal(outs[0], outs[1])
+    want = oracle.ragged_dot_fwd(data["lhs"].numpy(), data["rhs"].numpy(), sizes, bf16_bits(data["a_scale"]), bf16_bits(data["b_scale"]), layout="nn")
+    np.testing.assert_array_equal(as_f32(outs[0]), want)

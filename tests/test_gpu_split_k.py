@@ -57,7 +57,7 @@ def test_split_on_cta_pairs_and_plan(pkg):
     split = native.make_variant(dtype=pkg.OperandDType.INT4, layout=pkg.GemmLayout.NN, scale=pc, epilogue=pkg.Epilogue.NONE,
                                 out_dtype=native.OUT_F32, split_k=8)
     plain = native.make_variant(dtype=pkg.OperandDType.INT4, layout=pkg.GemmLayout.NN, scale=pc, epilogue=pkg.Epilogue.NONE,
-                                out_dtype=native.OUT_F32)
+                                out_dtype=native.OUT_F32, tail_balance=native.TAIL_OFF)
     # a skinny problem: 4 tiles without the split, 32 CTAs with it; a short K gives fewer slices than asked for
     assert native.plan_dense(plain, m=128, n=1024, k=8192).as_tuple()[:2] == (native.LAUNCHED_TCGEN05, 4)
     assert native.plan_dense(split, m=128, n=1024, k=8192).as_tuple() == (native.LAUNCHED_TCGEN05, 32, 128, 256, 8, 8)
@@ -114,25 +114,30 @@ def test_split_k_pays_on_skinny_shapes(pkg):
     case = dense_case(pkg, m=m, n=n, k=k, seed=3)
     dev = {name: case[name].cuda() for name in ("a", "b", "a_scale", "b_scale")}
     out = torch.empty((m, n), device="cuda", dtype=torch.float32)
-    stream = torch.cuda.current_stream().cuda_stream
     times = {}
     for split in (1, 8):
         variant = native.make_variant(dtype=pkg.OperandDType.INT4, layout=pkg.GemmLayout.NN, scale=scale_spec(pkg, 0),
-                                      epilogue=pkg.Epilogue.NONE, out_dtype=native.OUT_F32, split_k=split)
-        ptr, size = native.dense_workspace(variant, m=m, n=n, k=k, device=out.device, stream_handle=stream)
+                                      epilogue=pkg.Epilogue.NONE, out_dtype=native.OUT_F32, split_k=split, tail_balance=native.TAIL_OFF)
+        ptr, size = native.dense_workspace(variant, m=m, n=n, k=k, device=out.device, stream_handle=torch.cuda.current_stream().cuda_stream)
 
         def run():
-            native.launch_dense(variant, device_index=0, stream_handle=stream, a_ptr=dev["a"].data_ptr(), b_ptr=dev["b"].data_ptr(),
+            native.launch_dense(variant, device_index=0, stream_handle=torch.cuda.current_stream().cuda_stream, a_ptr=dev["a"].data_ptr(), b_ptr=dev["b"].data_ptr(),
                                 a_scale_ptr=dev["a_scale"].data_ptr(), b_scale_ptr=dev["b_scale"].data_ptr(), c_ptr=out.data_ptr(),
                                 m=m, n=n, k=k, workspace_ptr=ptr, workspace_bytes=size)
-        for _ in range(5):
+        for _ in range(3):
             run()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()          # GPU time, not the host's launch rate
+        with torch.cuda.graph(graph):
+            for _ in range(20):
+                run()
+        graph.replay()
         torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        for _ in range(50):
-            run()
+        for _ in range(3):
+            graph.replay()
         stop.record()
         stop.synchronize()
-        times[split] = start.elapsed_time(stop) / 50
+        times[split] = start.elapsed_time(stop) / 60
     assert times[8] * 2.0 <= times[1], times
