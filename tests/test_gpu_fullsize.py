@@ -240,3 +240,62 @@ def test_config5_flat_backward_from_forward_format_operands(pkg):
                                     oracle.bf16_bits_to_f32(bf16_bits(sb[g])))
         np.testing.assert_array_equal(out[g].cpu().numpy(), want, err_msg=f"group {g}")
     assert torch.equal(out, pkg.ragged_dot_int4_bwd_flat(lhs, rhs, sizes.cuda(), a_scale=sa, b_scale=sb, static_scratch=True))
+
+
+def test_config2_whole_output_against_the_cuda_core_kernel(pkg):
+    """Every element of the 4096^3 int4 product: the tensor-core kernel (the pair form the defaults choose) against the
+    CUDA-core kernel, which the small cases pin to the oracle bit for bit."""
+    from strix_halo_int4_gemms_b200 import native
+
+    m = n = k = 4096
+    a, b = _random_bytes((m, k // 2), 40), _random_bytes((k // 2, n), 41)
+    sa, sb = _scales((m,), 42).cuda(), _scales((n,), 43).cuda()
+    tc = _launch(pkg, a, b, sa, sb, m=m, n=n, k=k)
+    cc = _launch(pkg, a, b, sa, sb, m=m, n=n, k=k, path=native.PATH_SIMT)
+    assert torch.equal(tc, cc)
+
+
+def test_config5_forward_whole_output_against_the_cuda_core_kernel(pkg):
+    """All 32768 x 1408 outputs of the grouped forward dot on the config-5 size vector, both kernels, bit for bit."""
+    from strix_halo_int4_gemms_b200 import native
+
+    sizes = _config5_group_sizes()
+    rows, k, n, groups = 32768, 2048, 1408, 64
+    lhs, rhs = _random_bytes((rows, k // 2), 50), _random_bytes((groups, k // 2, n), 51)
+    sa, sb = _scales((rows,), 52).cuda(), _scales((groups, n), 53).cuda()
+    config = pkg.RaggedDotConfig(block_m=256)     # the task height the public API picks for this shape
+    info = pkg.calculate_group_info(sizes.cuda(), config.block_m, align_tile=config.align_tile)
+    results = []
+    for path in (native.PATH_TCGEN05, native.PATH_SIMT):
+        out = torch.full((rows, n), float("nan"), device="cuda", dtype=torch.bfloat16)
+        native.launch_ragged_fwd_kernel(lhs, rhs, group_info=info, a_scale=sa, b_scale=sb, out=out, scale=pkg.ScaleSpec(pkg.ScaleMode.PER_CHANNEL),
+                                        config=config, layout=pkg.GemmLayout.NN, rows=rows, cols=n, k_packed=k // 2, scale_cols=1, path=path)
+        torch.cuda.synchronize()
+        assert native.device_status(0)[0] == 0
+        results.append(out)
+    assert torch.equal(pkg.ragged_dot_int4(lhs, rhs, sizes.cuda(), a_scale=sa, b_scale=sb), results[0])   # the default call
+    assert not bool(torch.isnan(results[0]).any())   # every row belongs to a group: every element is written
+    assert torch.equal(results[0], results[1])
+
+
+def test_config5_backward_whole_output_against_the_cuda_core_kernel(pkg):
+    """All 64 x 2048 x 1408 fp32 outputs of the grouped backward dot, both kernels, bit for bit (empty groups: zeros)."""
+    from strix_halo_int4_gemms_b200 import native
+
+    sizes = _config5_group_sizes()
+    groups, m, n = 64, 2048, 1408
+    cap = int(sizes.max())
+    cap += (-cap) % 32
+    lhs, rhs = _random_bytes((groups, cap // 2, m), 60), _random_bytes((groups, cap // 2, n), 61)
+    sa, sb = _scales((groups, m), 62).cuda(), _scales((groups, n), 63).cuda()
+    results = []
+    for path in (native.PATH_TCGEN05, native.PATH_SIMT):
+        out = torch.full((groups, m, n), float("nan"), device="cuda", dtype=torch.float32)
+        native.launch_ragged_bwd_kernel(lhs, rhs, sizes.cuda(), a_scale=sa, b_scale=sb, out=out, scale=pkg.ScaleSpec(pkg.ScaleMode.PER_CHANNEL),
+                                        config=pkg.RaggedBwdDotConfig(), layout=pkg.GemmLayout.TN, rows=m, cols=n, k_packed=cap // 2,
+                                        scale_cols=1, path=path)
+        torch.cuda.synchronize()
+        assert native.device_status(0)[0] == 0
+        results.append(out)
+    assert not bool(torch.isnan(results[0]).any())
+    assert torch.equal(results[0], results[1])
