@@ -660,7 +660,11 @@ def plan_problem(ctx: Ctx, key: str, *, split: str | None, batch_override: int, 
             lo, hi = shard.column_block(w["n"], ctx.world, ctx.rank)
             n_local = hi - lo
         per_problem = dense_bytes(w, n_local)
-        batch = batch_override or min(batch_for(per_problem), 1024)
+        # every rank runs the same number of problems per pass (the smallest shard decides: its sets must still
+        # exceed L2 between reuses)
+        widths = ([hi - lo for lo, hi in (shard.column_block(w["n"], ctx.world, r) for r in range(ctx.world))]
+                  if split == "strong" and ctx.world > 1 else [n_local])
+        batch = batch_override or min(max(batch_for(dense_bytes(w, n)) for n in widths), 1024)
         problems = build_dense_problems(ctx, w, batch, seed=seed, split=split)
         ops = sum(dense_ops(w, p["n"]) for p in problems)
         return w, problems, ops, per_problem, extra
@@ -668,13 +672,17 @@ def plan_problem(ctx: Ctx, key: str, *, split: str | None, batch_override: int, 
     if split == "weak" and ctx.world > 1:
         # expert-parallel, weak scaling: the global problem has 64 * world groups
         sizes = torch.cat([sizes[torch.randperm(64, generator=torch.Generator().manual_seed(r))] for r in range(ctx.world)])
-    plan = shard.assign_groups(sizes.tolist(), ctx.world) if (split and ctx.world > 1) else [list(range(len(sizes)))]
+    # the backward dot writes a [M, N] fp32 slab per group whatever the group's size: groups count as two mean groups' rows
+    slab_rows = 2 * int(sizes.sum()) // max(len(sizes), 1) if w["kind"] == "ragged_bwd" else 0
+    plan = (shard.assign_groups(sizes.tolist(), ctx.world, per_group_cost=slab_rows) if (split and ctx.world > 1)
+            else [list(range(len(sizes)))])
     owned = plan[ctx.rank] if (split and ctx.world > 1) else plan[0]
     if split and ctx.world > 1:
         extra["load_imbalance_max_over_mean"] = shard.load_imbalance(sizes.tolist(), plan)
     rows_local = int(sizes[list(owned)].sum())
     per_problem = ragged_bytes(w, rows_local, len(owned))
-    batch = batch_override or batch_for(per_problem)
+    # the same number of problems per pass on every rank, decided by the rank with the smallest shard
+    batch = batch_override or max(batch_for(ragged_bytes(w, int(sizes[list(groups)].sum()), len(groups))) for groups in plan)
     problems = build_ragged_problems(ctx, w, batch, seed=seed, sizes=sizes, owned=owned)
     w["plan"], w["sizes"] = plan, sizes
     return w, problems, ragged_ops(w, rows_local) * batch, per_problem, extra

@@ -816,9 +816,9 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const long long sa_row = w.sa_off + static_cast<long long>(row) * (kScale == SCALE_SC ? p.scale_cols : 1);
 
       if constexpr (kScale == SCALE_PC) {
-        float sa = 0.f;
+        float sa_pre = 0.f;  // the row's scale; for int4 divided by the 256 the accumulator carries (exact)
         if constexpr (kOut != OUT_S32) {
-          if (row_ok) sa = __bfloat162float(p.a_scale[sa_row]);
+          if (row_ok) sa_pre = __bfloat162float(p.a_scale[sa_row]) * (kInt4 ? (1.0f / 256.0f) : 1.0f);
         }
         const bool zero_tile = (w.num_kb == 0);  // nothing to reduce (empty group): the result is zero
         // Column scales of the tile, once per tile, into this warp's strip of shared memory as fp32
@@ -910,17 +910,24 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               }
             }
           } else {
+            // (f32(acc) * sa) * sb, two roundings, two elements per instruction.  An int4 accumulator holds 256 * sum:
+            // converting it as it is and multiplying by sa / 256 (`sa_pre`) gives the bits of f32(sum) * sa, because a
+            // power of two scales the convert's rounding and the product's exactly.
             float v[32];
+            const float2 sa2 = make_float2(sa_pre, sa_pre);
 #pragma unroll
             for (int i4 = 0; i4 < 8; ++i4) {
               const float4 sb4 = reinterpret_cast<const float4*>(sb_strip)[8 * c + i4];  // broadcast read
-              const float sbv[4] = {sb4.x, sb4.y, sb4.z, sb4.w};
-#pragma unroll
-              for (int k2 = 0; k2 < 4; ++k2) {
-                int a = static_cast<int>(r[4 * i4 + k2]);
-                if constexpr (kInt4) a >>= 8;
-                v[4 * i4 + k2] = __fmul_rn(__fmul_rn(static_cast<float>(a), sa), sbv[k2]);
-              }
+              const float2 lo = __fmul2_rn(__fmul2_rn(make_float2(static_cast<float>(static_cast<int>(r[4 * i4])),
+                                                                  static_cast<float>(static_cast<int>(r[4 * i4 + 1]))), sa2),
+                                           make_float2(sb4.x, sb4.y));
+              const float2 hi = __fmul2_rn(__fmul2_rn(make_float2(static_cast<float>(static_cast<int>(r[4 * i4 + 2])),
+                                                                  static_cast<float>(static_cast<int>(r[4 * i4 + 3]))), sa2),
+                                           make_float2(sb4.z, sb4.w));
+              v[4 * i4] = lo.x;
+              v[4 * i4 + 1] = lo.y;
+              v[4 * i4 + 2] = hi.x;
+              v[4 * i4 + 3] = hi.y;
             }
             if constexpr (kEpi == EPI_SWIGLU) {
               uint32_t g[32];
@@ -929,9 +936,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
-                int a = static_cast<int>(g[i]);
-                if constexpr (kInt4) a >>= 8;
-                const float gate = __fmul_rn(__fmul_rn(static_cast<float>(a), sa), sb_strip[NBLK + 32 * c + i]);
+                const float gate = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(g[i])), sa_pre), sb_strip[NBLK + 32 * c + i]);
                 v[i] = v[i] * (gate / (1.0f + __expf(-gate)));
               }
             } else if constexpr (kEpi == EPI_RELU2) {

@@ -74,21 +74,27 @@ def shard_dense_rhs(
     return b_local, scale_local, (lo, hi)
 
 
-def assign_groups(group_sizes: Sequence[int], world_size: int) -> list[list[int]]:
+def assign_groups(group_sizes: Sequence[int], world_size: int, *, per_group_cost: int = 0) -> list[list[int]]:
     """Greedy largest-first (LPT) assignment of groups to ranks by row count.
+
+    ``per_group_cost`` is a fixed cost per group in units of rows.  The forward dot costs rows only (0); the
+    backward dot writes one ``[M, N]`` fp32 slab per group whatever its size, empty groups included, so its cost per
+    group is mostly that slab: pass the number of rows whose arithmetic takes as long as one slab's write.
 
     Returns, per rank, its group indices in ascending order.  Deterministic: ties go to the lower
     group index first and to the lower rank.
     """
     if world_size <= 0:
         raise ValueError("world_size must be positive")
+    if per_group_cost < 0:
+        raise ValueError("per_group_cost must not be negative")
     order = sorted(range(len(group_sizes)), key=lambda g: (-int(group_sizes[g]), g))
     load = [0] * world_size
     owned: list[list[int]] = [[] for _ in range(world_size)]
     for g in order:
         r = min(range(world_size), key=lambda i: (load[i], i))
         owned[r].append(g)
-        load[r] += int(group_sizes[g])
+        load[r] += int(group_sizes[g]) + per_group_cost
     return [sorted(groups) for groups in owned]
 
 

@@ -117,3 +117,20 @@ def test_lpt_assignment_balances_skewed_groups():
         assert load_imbalance(sizes, plan) <= max(1.02, worst_single + 1e-9)
     contiguous = [list(range(r * 8, r * 8 + 8)) for r in range(8)]
     assert load_imbalance(sizes, assign_groups(sizes, 8)) <= load_imbalance(sizes, contiguous)
+
+
+def test_lpt_assignment_with_a_cost_per_group_spreads_the_groups():
+    """The backward dot pays for every group's output slab: with a cost per group no rank ends up with one huge group
+    while another holds a dozen small ones."""
+    from strix_halo_int4_gemms_b200.distributed import assign_groups
+
+    sizes = [4330] + [100] * 31 + [0] * 8 + [900] * 24
+    by_rows = assign_groups(sizes, 8)
+    by_cost = assign_groups(sizes, 8, per_group_cost=1024)
+    assert sorted(x for groups in by_cost for x in groups) == list(range(64))
+    counts_rows = [len(groups) for groups in by_rows]
+    counts_cost = [len(groups) for groups in by_cost]
+    assert max(counts_cost) - min(counts_cost) < max(counts_rows) - min(counts_rows)
+    assert max(counts_cost) <= 10
+    with pytest.raises(ValueError):
+        assign_groups(sizes, 8, per_group_cost=-1)
