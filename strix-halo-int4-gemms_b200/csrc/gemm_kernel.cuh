@@ -1305,7 +1305,9 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
-    if (lane == 0) bulk_wait_all();  // TMA stores issued by this lane have landed
+    // the staging slots must not be released while a TMA store still reads them; the writes themselves are complete
+    // at the end of the grid, and nothing in this kernel reads what they write
+    if (lane == 0) bulk_wait_read_all();
   } else if (warp >= T::kUnpackWarp0) {
     // ------------------------------------------------------------------ unpack (int4 only)
     if constexpr (T::kRegBalance) {
