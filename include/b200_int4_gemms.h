@@ -101,7 +101,12 @@ typedef struct b200_gemm_variant {
   int32_t accumulate_order; /* B200_ACCUMULATE_*: subchannel dense launches only */
   int32_t a_operand;  /* B200_A_OPERAND_* */
   int32_t tail_balance; /* B200_TAIL_* */
-  int32_t reserved[2];
+  int32_t task_align; /* grouped forward: what every task's block_start is a multiple of (the align_tile the tasks were
+                         built with), as promised by the caller; 0 = not stated.  A transposed lhs (TN / TT) puts the
+                         task's first row on the TMA x axis, which wants multiples of 16 bytes: the tensor-core path
+                         takes it only with task_align a multiple of 16, otherwise the CUDA-core kernel runs.  A task
+                         that breaks the promise is skipped and reported (code 4 of b200_int4_gemms_device_status) */
+  int32_t reserved[1];
 } b200_gemm_variant;
 
 /* Replaces amd_strix_halo_kernels_dispatch_version (dispatch.cpp:206). */
@@ -120,7 +125,9 @@ const char* b200_int4_gemms_last_error(void);
 
 /* Device-side status word of the most recent launches on a device: 0 = no kernel reported
  * a problem, 1 = a bounded wait inside a kernel ran out (the kernel gave up and returned),
- * 3 = a grouped forward launch was given a device-built task list that had overflowed its arrays.
+ * 3 = a grouped forward launch was given a device-built task list that had overflowed its arrays,
+ * 4 = a grouped forward launch with a transposed lhs met a task that does not start on a multiple of 16 rows although
+ * variant->task_align promised it (detail[0] = the task, which was skipped).
  * Reading it does not synchronise; call it after synchronising the stream.  detail[0..2]
  * (may be NULL) receive the block index and wait site.  No reference counterpart. */
 int b200_int4_gemms_device_status(int device_index, int32_t* detail);
@@ -193,7 +200,8 @@ int b200_int4_gemms_last_launch_path(void);
  *              (reference ragged.py:201-323); block_rows = the tile they were built with (<= 256;
  *              tasks of more than 128 rows run on pairs of SMs and need per-channel scales or K-groups of
  *              at least 128 on the tensor-core path).  The tensor-core path takes a row-major lhs
- *              (layouts NN and NT); TN / TT run on the CUDA-core kernel
+ *              (layouts NN and NT) and, when variant->task_align is a multiple of 16 and m is one too, a
+ *              transposed lhs (TN / TT, tasks of at most 128 rows); else TN / TT run on the CUDA-core kernel
  *   out        [m, n] bf16 or f32; rows outside every task's [actual_start, actual_end) are untouched */
 int b200_int4_gemms_launch_ragged_fwd(const b200_gemm_variant* variant, int device_index,
                                       uintptr_t stream_handle, const void* lhs, const void* rhs,

@@ -750,16 +750,20 @@ int launch_ragged_fwd_impl(
     return fail("scale_cols does not match ceil(K / subchannel)");
 
   // Tasks of more than 128 rows run on CTA pairs: rank 0 takes the first 128 rows of the block, rank 1 the rest.
-  // lhs must be row-major (a transposed lhs would put the task's first row, any multiple of align_tile, on
-  // the TMA x axis, which wants multiples of 16 bytes); rhs may be [G, Kb, N] (NN) or [G, N, Kb] (NT)
+  // A transposed lhs [Kb, M] puts the task's first row (a multiple of the align_tile the tasks were built with) on
+  // the TMA x axis, which wants multiples of 16 bytes: it is taken when the caller states that alignment in the
+  // variant (the kernel skips and reports a task that breaks it); rhs may be [G, Kb, N] or [G, N, Kb]
   TcLaunch tl{true, a_t, !b_t, false, sc_mode, EPI_NONE, v->out_dtype};
   tl.pair = block_rows > BM;
   const bool pair_ok = !tl.pair || sc_mode == SCALE_PC || v->subchannel >= BK;
-  bool tc_ok = !a_t && pair_ok && tc_has(tl) && aligned16(lhs) && aligned16(rhs) && (k_packed % 16 == 0) && (b_t || n % 16 == 0);
+  const bool lhs_ok = a_t ? (v->task_align > 0 && v->task_align % 16 == 0 && block_rows % 16 == 0 && m % 16 == 0 && !tl.pair)
+                          : (k_packed % 16 == 0);
+  bool tc_ok = lhs_ok && pair_ok && tc_has(tl) && aligned16(lhs) && aligned16(rhs) && (b_t ? k_packed % 16 == 0 : n % 16 == 0);
   if (v->path == B200_PATH_SIMT) tc_ok = false;
   if (v->path == B200_PATH_TCGEN05 && !tc_ok)
-    return fail("the tcgen05 ragged forward kernel needs layout NN or NT, 16-byte aligned operands, k_packed (and for NN n) "
-                "multiples of 16, and (for block_rows > 128) per-channel scales or K-groups of at least 128");
+    return fail("the tcgen05 ragged forward kernel needs 16-byte aligned operands and operand pitches that are multiples of 16 "
+                "bytes, for a transposed lhs (TN / TT) task starts stated as multiples of 16 rows (variant.task_align) and "
+                "tasks of at most 128 rows, and for block_rows > 128 per-channel scales or K-groups of at least 128");
 
   if (!tc_ok) {
     SimtParams sp{};
@@ -798,7 +802,11 @@ int launch_ragged_fwd_impl(
     if (tc_has(through_tmem)) tl = through_tmem;
   }
   CUtensorMap ta, tb;
-  if (int rc = make_map_2d(&ta, lhs, k_packed, m, k_packed, BK / 2, BM, tl.flavor == FLAVOR_TMEM_A ? 64 : 0, "lhs"); rc != 0) return rc;
+  if (a_t) {
+    if (int rc = make_map_2d(&ta, lhs, m, k_packed, m, NBLK, BK / 2, 0, "lhs"); rc != 0) return rc;
+  } else {
+    if (int rc = make_map_2d(&ta, lhs, k_packed, m, k_packed, BK / 2, BM, tl.flavor == FLAVOR_TMEM_A ? 64 : 0, "lhs"); rc != 0) return rc;
+  }
   if (b_t) {
     if (int rc = make_map_2d(&tb, rhs, k_packed, static_cast<uint64_t>(groups) * n, k_packed, BK / 2, NBLK, 0, "rhs"); rc != 0)
       return rc;

@@ -201,8 +201,9 @@ __device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t, int 
     const int nt = t - task * p.tiles_n;
     const int g = static_cast<int>(p.task_group_ids[task]);
     const int bs = static_cast<int>(p.task_block_starts[task]);
-    w.a_x = 0;
-    w.a_y = bs + rank_rows;
+    // a transposed lhs [K/2, M] has the task's rows on the TMA x axis
+    w.a_x = kAMn ? bs + rank_rows : 0;
+    w.a_y = kAMn ? 0 : bs + rank_rows;
     w.b_y = g * p.rows_per_group_b;
     w.n0 = nt * BN;
     w.n1 = w.n0 + NBLK;
@@ -212,6 +213,17 @@ __device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t, int 
     // task bounds come from the caller (or from the device-side builder): never trust them past the operand
     w.row_lo = max(0, static_cast<int>(p.task_actual_starts[task]));
     w.row_hi = min(p.M, static_cast<int>(p.task_actual_ends[task]));
+    if (kAMn && (bs & 15) != 0) {
+      // an x coordinate that is not a multiple of 16 bytes must never reach TMA: every role skips the task (no K
+      // blocks, no rows), and the CTA that meets it first says so in the status word
+      w.num_kb = 0;
+      w.row_hi = w.row_lo;
+      if (p.status != nullptr && threadIdx.x == 0 && p.status[0] == STATUS_OK) {
+        p.status[1] = task;
+        p.status[2] = 0;
+        p.status[0] = STATUS_TASK_ALIGNMENT;
+      }
+    }
     w.sb_off = static_cast<long long>(g) * p.lds_b * (p.subchannel ? p.scale_cols : 1);
   } else {
     const int per_g = p.tiles_m * p.tiles_n;

@@ -74,6 +74,8 @@ enum : int {
   STATUS_WAIT_TIMEOUT = 1,
   STATUS_BAD_ARGUMENT = 2,
   STATUS_TASK_OVERFLOW = 3,  // grouped forward: the device-built task list did not fit; status[1] = tasks kept
+  STATUS_TASK_ALIGNMENT = 4, // grouped forward, transposed lhs: a task starts on a row that is not a multiple of 16
+                             // (status[1] = the task); the task was skipped
 };
 
 struct AbortCtx {

@@ -102,7 +102,8 @@ class GemmVariant(ctypes.Structure):
         ("accumulate_order", ctypes.c_int32),
         ("a_operand", ctypes.c_int32),
         ("tail_balance", ctypes.c_int32),
-        ("reserved", ctypes.c_int32 * 2),
+        ("task_align", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 1),
     ]
 
 
@@ -369,6 +370,7 @@ def make_variant(
     accumulate_order: int | None = None,
     a_operand: int = A_OPERAND_AUTO,
     tail_balance: int = TAIL_AUTO,
+    task_align: int = 0,
 ) -> GemmVariant:
     """The C variant record of one launch.  ``schedule`` is the registry's launch form; ``cta_group``
     (CTA_GROUP_*) overrides the form's CTA choice when given."""
@@ -387,6 +389,7 @@ def make_variant(
     variant.accumulate_order = int(_ACCUMULATION_ORDER if accumulate_order is None else accumulate_order)
     variant.a_operand = int(a_operand)
     variant.tail_balance = int(tail_balance)
+    variant.task_align = int(task_align)   # grouped forward: what the tasks' block starts are multiples of (0: not stated)
     return variant
 
 
@@ -626,6 +629,8 @@ def launch_ragged_fwd_kernel(
     record = make_variant(
         dtype=OperandDType.INT4, layout=layout, scale=scale, epilogue=Epilogue.NONE,
         out_dtype=OUT_F32 if out.dtype is torch.float32 else OUT_BF16, path=path, a_operand=a_operand,
+        # a transposed lhs reaches the tensor cores only when every task starts on a multiple of 16 rows
+        task_align=int(getattr(group_info, "align_tile", None) or 0),
     )
     groups = int(rhs.shape[0])
     task_arrays = (

@@ -19,6 +19,7 @@ of SMs (one 256 x 256 tile per pair); ``RaggedDotConfig.pair_tasks`` says when t
 """
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass, replace
 from typing import Any
 
@@ -476,6 +477,10 @@ def ragged_dot_int4(
         if config.pair_tasks is True or rows >= PAIR_MIN_MEAN_GROUP_ROWS * groups:
             if PAIR_TASK_ROWS % config.align_tile == 0:
                 config = replace(config, block_m=PAIR_TASK_ROWS)
+    if group_info is None and layout in (GemmLayout.TN, GemmLayout.TT) and config.align_tile % 16 and config.block_m % 16 == 0:
+        # a transposed lhs reaches the tensor cores only with tasks that start on multiples of 16 rows; where the
+        # tasks start changes nothing in the result (rows outside a group are masked), so cut them that way
+        config = replace(config, align_tile=math.lcm(config.align_tile, 16))
     if group_info is None:
         _validate_group_sizes(torch, group_sizes, groups=groups, rows=rows)
         if group_sizes.device != lhs.device:

@@ -1,6 +1,8 @@
 """Grouped int4 dots on a B200 against the oracle: forward (M-ragged) and backward (K-ragged).
 Cases follow the reference's tests/test_ragged_dot.py:260-586: empty groups, odd K, groups that start
 inside an aligned block, every layout, per-channel and subchannel scales."""
+from dataclasses import replace
+
 import numpy as np
 import pytest
 import torch
@@ -75,6 +77,61 @@ def test_forward_nt_layout_on_the_tensor_core_kernel(pkg, sub):
     np.testing.assert_array_equal(as_f32(out), want)
     out, want = _fwd(pkg, [300, 40], 256, 200, layout="nt", sub=sub, seed=14, out_dtype=torch.float32)
     np.testing.assert_array_equal(out.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("layout", ["tn", "tt"])
+@pytest.mark.parametrize("sub", [0, 128])
+def test_forward_transposed_lhs_on_the_tensor_core_kernel(pkg, layout, sub):
+    """lhs stored [K/2, M]: the task's first row is a TMA x coordinate, so the tensor cores take it when the tasks
+    were built with an ``align_tile`` that is a multiple of 16; with the default of 8 the CUDA-core kernel runs
+    (and says so).  Both must equal the oracle bit for bit."""
+    import warnings
+    from strix_halo_int4_gemms_b200 import native
+
+    sizes = [100, 0, 260, 128, 7, 33]           # 528 rows: a multiple of 16, as the packed pitch of [K/2, M] needs
+    aligned = pkg.RaggedDotConfig(block_m=128, align_tile=16, pair_tasks=False)
+    out, want = _fwd(pkg, sizes, 512, 1408, layout=layout, sub=sub, config=aligned, seed=21)
+    assert native.last_launch_path() == native.LAUNCHED_TCGEN05
+    np.testing.assert_array_equal(as_f32(out), want)
+    out32, want32 = _fwd(pkg, sizes, 512, 208, layout=layout, sub=sub, config=pkg.RaggedDotConfig(block_m=64, align_tile=32, pair_tasks=False),
+                         seed=22, out_dtype=torch.float32)
+    if sub == 0:    # an fp32 result exists on the tensor cores for per-channel scales; subchannel fp32 goes to the CUDA cores
+        assert native.last_launch_path() == native.LAUNCHED_TCGEN05
+    np.testing.assert_array_equal(out32.cpu().numpy(), want32)
+    default, _ = _fwd(pkg, sizes, 512, 1408, layout=layout, sub=sub, seed=21)      # the default config is cut to suit
+    assert native.last_launch_path() == native.LAUNCHED_TCGEN05
+    assert torch.equal(default, out)
+    info8 = pkg.calculate_group_info(torch.tensor(sizes).cuda(), 128, align_tile=8)   # prebuilt tasks that start anywhere
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore", RuntimeWarning)
+        loose, _ = _fwd(pkg, sizes, 512, 1408, layout=layout, sub=sub, seed=21, group_info=info8)
+    assert native.last_launch_path() == native.LAUNCHED_SIMT
+    assert torch.equal(loose, out)
+
+
+def test_forward_transposed_lhs_with_a_broken_alignment_promise_is_reported_not_run(pkg):
+    """Tasks built with align_tile = 8 but declared as 16: the kernel skips the tasks whose first row is not a
+    multiple of 16 and reports them; nothing faults, and the context stays usable."""
+    from strix_halo_int4_gemms_b200 import native
+
+    sizes = [104, 24]                            # group 1 starts on row 104: a multiple of 8, not of 16
+    data = make_ragged_fwd_inputs(m=128, n=256, k=256, group_sizes=sizes, layout=pkg.GemmLayout.TN, scale=scale_spec(pkg, 0), seed=3)
+    dev = {name: data[name].cuda() for name in ("lhs", "rhs", "a_scale", "b_scale", "group_sizes")}
+    info = pkg.calculate_group_info(dev["group_sizes"], 128, align_tile=8)
+    lying = replace(info, align_tile=16)
+    out = torch.full((128, 256), 7.0, dtype=torch.bfloat16, device="cuda")
+    native.launch_ragged_fwd_kernel(dev["lhs"], dev["rhs"], group_info=lying, a_scale=dev["a_scale"], b_scale=dev["b_scale"], out=out,
+                                    scale=scale_spec(pkg, 0), config=pkg.RaggedDotConfig(), layout=pkg.GemmLayout.TN, rows=128, cols=256,
+                                    k_packed=128, scale_cols=1, path=native.PATH_TCGEN05)
+    torch.cuda.synchronize()
+    status, detail = native.device_status(0)
+    assert status == 4 and detail[0] == 1, (status, detail)       # task 1 (group 1, block start 104)
+    native.reset_device_status(0)
+    want = oracle.ragged_dot_fwd(data["lhs"].numpy(), data["rhs"].numpy(), sizes, bf16_bits(data["a_scale"]), bf16_bits(data["b_scale"]), layout="tn")
+    np.testing.assert_array_equal(as_f32(out[:104]), want[:104])  # the well-formed task ran
+    assert bool((out[104:] == 7.0).all())                         # the other one wrote nothing
+    again, want2 = _fwd(pkg, sizes, 256, 256, layout="tn", seed=3)
+    np.testing.assert_array_equal(as_f32(again), want2)
 
 
 def test_forward_widens_tasks_for_large_groups(pkg):
