@@ -981,8 +981,9 @@ int launch_ragged_bwd_impl(const b200_gemm_variant* v, int device_index, uintptr
   if (sc_mode == SCALE_SC && scale_cols != (k + v->subchannel - 1) / v->subchannel)
     return fail("scale_cols does not match ceil(K / subchannel)");
 
-  TcLaunch tl{true, a_t, true, true, sc_mode, EPI_NONE, OUT_F32};
-  bool tc_ok = !b_t && tc_has(tl) && aligned16(lhs) && aligned16(rhs) && ((a_t ? m : k_packed) % 16 == 0) && (n % 16 == 0);
+  TcLaunch tl{true, a_t, !b_t, true, sc_mode, EPI_NONE, OUT_F32};
+  bool tc_ok = tc_has(tl) && aligned16(lhs) && aligned16(rhs) && ((a_t ? m : k_packed) % 16 == 0) &&
+               ((b_t ? k_packed : n) % 16 == 0);
   // CTA pairs (256-row tiles) where a paired kernel exists and the rows fill them: a third less operand
   // traffic through each SM's shared memory, which this kernel shares with its fp32 output staging
   if (tc_ok && dev->max_pair_clusters > 0 && m % (2 * BM) == 0 && v->cta_group != B200_CTA_GROUP_SINGLE) {
@@ -993,7 +994,7 @@ int launch_ragged_bwd_impl(const b200_gemm_variant* v, int device_index, uintptr
   }
   if (v->path == B200_PATH_SIMT) tc_ok = false;
   if (v->path == B200_PATH_TCGEN05 && !tc_ok)
-    return fail("the tcgen05 ragged backward kernel needs rhs stored [G, K, N], 16-byte aligned operands and operand pitches that are multiples of 16 bytes");
+    return fail("the tcgen05 ragged backward kernel needs 16-byte aligned operands, operand pitches that are multiples of 16 bytes and, for a K-major rhs (NT / TT), per-channel scales");
 
   if (!tc_ok) {
     SimtParams sp{};
@@ -1032,8 +1033,13 @@ int launch_ragged_bwd_impl(const b200_gemm_variant* v, int device_index, uintptr
     if (int rc = make_map_2d(&ta, lhs, k_packed, static_cast<uint64_t>(groups) * m, k_packed, BK / 2, BM, 0, "lhs"); rc != 0)
       return rc;
   }
-  if (int rc = make_map_2d(&tb, rhs, n, k_rows, n, NBLK, BK / 2, 0, "rhs"); rc != 0)
-    return rc;
+  if (b_t) {
+    if (int rc = make_map_2d(&tb, rhs, k_packed, static_cast<uint64_t>(groups) * n, k_packed, BK / 2, NBLK, 0, "rhs"); rc != 0)
+      return rc;
+  } else {
+    if (int rc = make_map_2d(&tb, rhs, n, k_rows, n, NBLK, BK / 2, 0, "rhs"); rc != 0)
+      return rc;
+  }
   GemmParams p{};
   p.mode = MODE_RAGGED_BWD;
   p.group_starts = group_starts;
@@ -1052,7 +1058,7 @@ int launch_ragged_bwd_impl(const b200_gemm_variant* v, int device_index, uintptr
   p.lds_b = n;
   p.num_groups = groups;
   p.rows_per_group_a = a_t ? k_packed : m;
-  p.rows_per_group_b = k_packed;
+  p.rows_per_group_b = b_t ? n : k_packed;
   p.group_sizes = reinterpret_cast<const long long*>(group_sizes);
   p.a_scale = static_cast<const __nv_bfloat16*>(lhs_scale);
   p.b_scale = static_cast<const __nv_bfloat16*>(rhs_scale);

@@ -400,7 +400,6 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   constexpr bool kFastSc = T::kFastSc;
   constexpr bool kTmemA = T::kTmemA;
   constexpr bool kTail = T::kTail;
-  static_assert(kBMn || !kMaskK, "K masking is applied to an MN-major B operand");
   static_assert(!kFastSc || kScale == SCALE_SC, "the fused accumulation order belongs to the subchannel kernels");
   // accumulator buffer and barrier phase of the grp-th accumulator hand-over
   auto acc_buf = [](int grp) { return grp % T::kAccBufs; };
@@ -1464,6 +1463,22 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               expand_word(xb[jj].w, lo.w, hi.w);
               if (jb + kBBatch < kBItems) xb[jj] = load_b(j + kBBatch);  // next batch, in flight during the stores
               if constexpr (!kBMn) {
+                if constexpr (kMaskK) {
+                  // K-major B [N, K/2]: this thread's items all cover k = kb * 128 + 32 a_c .. + 31, byte j of `lo`
+                  // holding k = ... + 2 j and byte j of `hi` k = ... + 2 j + 1: keep the bytes below the group's length
+                  const int valid = w.k_valid - (kb * BK + 32 * a_c);
+                  if (valid < 32) {
+                    auto keep = [](uint4 x, int bytes) -> uint4 {
+                      auto word = [&](uint32_t v, int first) -> uint32_t {
+                        const int nb = bytes - first;
+                        return nb >= 4 ? v : (nb <= 0 ? 0u : (v & ((1u << (8 * nb)) - 1u)));
+                      };
+                      return make_uint4(word(x.x, 0), word(x.y, 4), word(x.z, 8), word(x.w, 12));
+                    };
+                    lo = keep(lo, (valid + 1) >> 1);
+                    hi = keep(hi, valid >> 1);
+                  }
+                }
                 *reinterpret_cast<uint4*>(b8 + a_dst_lo0 + j * (kARowsPerPass * 128)) = lo;
                 *reinterpret_cast<uint4*>(b8 + a_dst_hi0 + j * (kARowsPerPass * 128)) = hi;
               } else if constexpr (k2Cta) {

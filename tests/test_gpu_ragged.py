@@ -205,7 +205,7 @@ def _bwd(pkg, sizes, m, n, *, layout="tn", sub=0, seed=0, k_capacity=None, confi
     return out, want
 
 
-@pytest.mark.parametrize("layout", ["tn", "nn"])
+@pytest.mark.parametrize("layout", ["tn", "nn", "nt", "tt"])
 def test_backward_on_cta_pairs_and_on_single_ctas(pkg, layout):
     """M = 512 is two 256-row pair tiles per group; the per-channel backward kernels exist in both forms and
     RaggedBwdDotConfig.pair_tiles pins either: both must reproduce the oracle."""
@@ -226,6 +226,19 @@ def test_backward_matches_oracle(pkg, layout, sub):
     assert out.dtype is torch.float32 and tuple(out.shape) == (6, 256, 512)
     np.testing.assert_array_equal(out.cpu().numpy(), want)
     assert float(out[1].abs().max()) == 0.0  # the empty group
+
+
+@pytest.mark.parametrize("layout", ["nt", "tt"])
+def test_backward_with_a_k_major_rhs_masks_bytes_past_the_group(pkg, layout):
+    """rhs stored [G, N, K/2]: the tensor-core kernel zeroes the bytes of a 16-byte piece that lie past the group's
+    length.  Lengths on every residue of 32 around a piece's end, odd lengths, a group of one token, N with a column
+    edge; the tail of the capacity holds random data that must not leak in."""
+    from strix_halo_int4_gemms_b200 import native
+
+    sizes = [1, 2, 31, 32, 33, 63, 64, 65, 127, 128, 129, 255, 0, 256]
+    out, want = _bwd(pkg, sizes, 256, 200, layout=layout, k_capacity=256, seed=51)
+    assert native.last_launch_path() in (native.LAUNCHED_TCGEN05, native.LAUNCHED_TCGEN05_PAIR)
+    np.testing.assert_array_equal(out.cpu().numpy(), want)
 
 
 def test_backward_odd_lengths_and_column_edge(pkg):
