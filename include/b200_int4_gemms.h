@@ -222,8 +222,7 @@ int b200_int4_gemms_launch_ragged_fwd(const b200_gemm_variant* variant, int devi
  *   lhs_scale  bf16 [groups, m] or [groups, m, scale_cols]; rhs_scale [groups, n] or [groups, scale_cols, n]
  *   group_sizes int64 [groups]
  *   out        f32 [groups, m, n]
- * All four layouts run on the tensor cores with per-channel scales (a K-major rhs with its bytes past k_g zeroed
- * while it is unpacked); subchannel scales with a K-major rhs run on the CUDA-core kernel.
+ * All four layouts run on the tensor cores (a K-major rhs with its bytes past k_g zeroed while it is unpacked).
  * Split-K is not needed for determinism here: every output tile is owned by one CTA, so
  * results are bit-identical from run to run. */
 int b200_int4_gemms_launch_ragged_bwd(const b200_gemm_variant* variant, int device_index,

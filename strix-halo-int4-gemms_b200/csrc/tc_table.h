@@ -97,7 +97,26 @@ struct TcKernelInfo {
   X(false, false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false, true, FLAVOR_PLAIN)    \
   X(true, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, true, FLAVOR_PLAIN)      \
   X(true, true, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true, FLAVOR_PLAIN)        \
+  /* a transposed A ([K, M]) with fused activations and with subchannel scales for int8 */ \
+  X(true, true, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_PLAIN)      \
+  X(true, true, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_PLAIN)     \
+  X(true, true, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_PLAIN)      \
+  X(true, true, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_PLAIN)     \
+  X(true, true, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_FUSED_SC)   \
+  X(true, true, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_FUSED_SC)  \
+  X(false, true, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_PLAIN)     \
+  X(false, true, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_PLAIN)    \
+  X(false, true, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false, FLAVOR_PLAIN)      \
+  X(false, true, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_PLAIN)     \
+  X(false, true, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_PLAIN)    \
+  X(false, true, true, SCALE_SC, EPI_NONE, OUT_BF16, false, false, FLAVOR_FUSED_SC)   \
+  X(false, true, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_FUSED_SC)  \
+  X(false, true, true, SCALE_SC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_FUSED_SC) \
   /* grouped backward with a K-major rhs [G, N, K/2] (layouts NT, TT): bytes past a group's length are masked */ \
+  X(true, false, false, SCALE_SC, EPI_NONE, OUT_F32, true, false, FLAVOR_PLAIN)        \
+  X(true, true, false, SCALE_SC, EPI_NONE, OUT_F32, true, false, FLAVOR_PLAIN)         \
+  X(true, false, false, SCALE_SC, EPI_NONE, OUT_F32, true, true, FLAVOR_PLAIN)         \
+  X(true, true, false, SCALE_SC, EPI_NONE, OUT_F32, true, true, FLAVOR_PLAIN)          \
   X(true, false, false, SCALE_PC, EPI_NONE, OUT_F32, true, false, FLAVOR_PLAIN)        \
   X(true, true, false, SCALE_PC, EPI_NONE, OUT_F32, true, false, FLAVOR_PLAIN)         \
   X(true, false, false, SCALE_PC, EPI_NONE, OUT_F32, true, true, FLAVOR_PLAIN)         \

@@ -137,6 +137,18 @@ def test_layout_tt_on_the_tensor_core_kernel(pkg, dtype):
         check_dense(pkg, m=256, n=256, k=512, dtype=dtype, layout="tt", out="f32", path=TCGEN05, seed=34)
 
 
+@pytest.mark.parametrize("dtype", ["int4", "int8"])
+@pytest.mark.parametrize("epilogue", ["none", "relu2", "swiglu"])
+@pytest.mark.parametrize("sub", [0, 128, 256])
+def test_layout_tn_with_every_scale_mode_and_epilogue_on_the_tensor_core_kernel(pkg, dtype, epilogue, sub):
+    """A stored [Kb, M]: the registry's TN cells (both dtypes, per-channel and subchannel, all three epilogues) have
+    tensor-core kernels; path = TCGEN05 makes a missing one an error instead of a detour over the CUDA cores."""
+    check_dense(pkg, m=256, n=384, k=512, dtype=dtype, layout="tn", sub=sub, epilogue=epilogue, path=TCGEN05, seed=61 + sub)
+    check_dense(pkg, m=144, n=208, k=384, dtype=dtype, layout="tn", sub=sub, epilogue=epilogue, path=TCGEN05, seed=62 + sub)
+    if sub:   # and in the library's default (fused) accumulation order
+        check_dense(pkg, m=256, n=384, k=512, dtype=dtype, layout="tn", sub=sub, epilogue=epilogue, path=TCGEN05, seed=63 + sub, order="fused")
+
+
 def test_cta_pair_falls_back_when_no_paired_kernel_exists(pkg):
     check_dense(pkg, m=256, n=256, k=256, sub=32, path=TCGEN05, cta_group=PAIR)      # K-groups of 32: single-CTA kernel
     check_dense(pkg, m=256, n=256, k=256, layout="tn", path=TCGEN05, cta_group=PAIR)

@@ -236,9 +236,10 @@ def test_backward_with_a_k_major_rhs_masks_bytes_past_the_group(pkg, layout):
     from strix_halo_int4_gemms_b200 import native
 
     sizes = [1, 2, 31, 32, 33, 63, 64, 65, 127, 128, 129, 255, 0, 256]
-    out, want = _bwd(pkg, sizes, 256, 200, layout=layout, k_capacity=256, seed=51)
-    assert native.last_launch_path() in (native.LAUNCHED_TCGEN05, native.LAUNCHED_TCGEN05_PAIR)
-    np.testing.assert_array_equal(out.cpu().numpy(), want)
+    for sub in (0, 32, 128):
+        out, want = _bwd(pkg, sizes, 256, 200, layout=layout, sub=sub, k_capacity=256, seed=51 + sub)
+        assert native.last_launch_path() in (native.LAUNCHED_TCGEN05, native.LAUNCHED_TCGEN05_PAIR), sub
+        np.testing.assert_array_equal(out.cpu().numpy(), want, err_msg=f"K-groups of {sub}")
 
 
 def test_backward_odd_lengths_and_column_edge(pkg):
