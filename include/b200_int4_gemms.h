@@ -85,6 +85,14 @@ enum { B200_A_OPERAND_AUTO = 0, B200_A_OPERAND_SMEM = 1, B200_A_OPERAND_TMEM = 2
  * 4096^3 the measured gain was within noise); OFF: whole tiles only.  Without a workspace whole tiles are scheduled. */
 enum { B200_TAIL_AUTO = 0, B200_TAIL_OFF = 1, B200_TAIL_ALWAYS = 2 };
 
+/* Tile width of per-channel int4 CTA-pair launches with a B stored [K, N] and bf16 output (dense, and grouped
+ * forward).  A pair can own a 256 x 512 tile instead of 256 x 256: each CTA then unpacks its rows of A once per K
+ * block for two blocks of B (a quarter less unpack work and shared-memory traffic per output element; one
+ * accumulator fills TMEM, so the epilogue of a tile is not hidden behind the next tile).  AUTO takes wide tiles when
+ * their waves, at 0.9 of the time of two narrow tiles each, need less time than the narrow tiles' waves; OFF / ON
+ * force either (ON falls back where no wide kernel exists).  Bit-identical results. */
+enum { B200_WIDE_AUTO = 0, B200_WIDE_OFF = 1, B200_WIDE_ON = 2 };
+
 typedef struct b200_gemm_variant {
   int32_t dtype;      /* B200_DTYPE_*      */
   int32_t layout;     /* B200_LAYOUT_*     */
@@ -106,7 +114,7 @@ typedef struct b200_gemm_variant {
                          task's first row on the TMA x axis, which wants multiples of 16 bytes: the tensor-core path
                          takes it only with task_align a multiple of 16, otherwise the CUDA-core kernel runs.  A task
                          that breaks the promise is skipped and reported (code 4 of b200_int4_gemms_device_status) */
-  int32_t reserved[1];
+  int32_t wide_tiles; /* B200_WIDE_* */
 } b200_gemm_variant;
 
 /* Replaces amd_strix_halo_kernels_dispatch_version (dispatch.cpp:206). */

@@ -273,6 +273,7 @@ int check_variant(const b200_gemm_variant* v) {
     return fail("variant.accumulate_order is unknown");
   if (v->a_operand < B200_A_OPERAND_AUTO || v->a_operand > B200_A_OPERAND_TMEM) return fail("variant.a_operand is unknown");
   if (v->tail_balance < B200_TAIL_AUTO || v->tail_balance > B200_TAIL_ALWAYS) return fail("variant.tail_balance is unknown");
+  if (v->wide_tiles < B200_WIDE_AUTO || v->wide_tiles > B200_WIDE_ON) return fail("variant.wide_tiles is unknown");
   return 0;
 }
 
@@ -511,6 +512,26 @@ int plan_dense(const b200_gemm_variant* v, const DeviceState* dev, const void* a
       TcLaunch through_tmem = tl;
       through_tmem.flavor = FLAVOR_TMEM_A;
       if (tc_has(through_tmem)) tl = through_tmem;
+    }
+    // Wide tiles (256 x 512 per pair) where such a kernel exists: a wide tile takes 0.9 of the time of the two
+    // narrow tiles it replaces (measured at 4096^3 and 8192^3), so they win when their waves need less time.
+    // They come before A-through-TMEM (3650 against 3312 TOPS at 8192^3) and after the balanced tail, which AUTO
+    // only takes for launches without a full wave.
+    if (tl.pair && (tl.flavor == FLAVOR_PLAIN || tl.flavor == FLAVOR_TMEM_A) && pl.slices == 1 && pl.tail_units == 0 &&
+        pl.tile_cols == BN && v->wide_tiles != B200_WIDE_OFF && v->schedule == B200_SCHEDULE_PERSISTENT) {
+      TcLaunch wide = tl;
+      wide.flavor = FLAVOR_WIDE;
+      const int wide_cols = (n + 2 * BN - 1) / (2 * BN);
+      const long long wide_waves = (static_cast<long long>(pl.tiles_m) * wide_cols + max_units - 1) / max_units;
+      const long long narrow_waves = (static_cast<long long>(num_tiles) + max_units - 1) / max_units;
+      if (tc_has(wide) && (v->wide_tiles == B200_WIDE_ON || 18 * wide_waves < 10 * narrow_waves)) {
+        tl = wide;
+        pl.tile_cols = 2 * BN;
+        pl.tiles_n = wide_cols;
+        const int wide_tiles = pl.tiles_m * pl.tiles_n;
+        pl.grid = (wide_tiles < max_units ? wide_tiles : max_units) * cta_per_tile;
+        if (v->group_m <= 0) pl.group_m = 4;  // with TMA four K blocks ahead the raster hardly matters; 1 .. 8 measured alike
+      }
     }
     pl.kernel = tl;
   } else {
@@ -814,14 +835,30 @@ int launch_ragged_fwd_impl(
     if (int rc = make_map_2d(&tb, rhs, n, static_cast<uint64_t>(groups) * k_packed, n, NBLK, BK / 2, 0, "rhs"); rc != 0)
       return rc;
   }
+  // wide tiles (256 rows x 512 columns per pair), by the rule of the dense launches: a wide tile takes 0.9 of the
+  // time of the two it replaces (with a device-side task count, num_tasks is the capacity of the arrays)
+  int tile_cols = BN;
+  if (tl.pair && (tl.flavor == FLAVOR_PLAIN || tl.flavor == FLAVOR_TMEM_A) && v->wide_tiles != B200_WIDE_OFF && dev->max_pair_clusters > 0) {
+    TcLaunch wide = tl;
+    wide.flavor = FLAVOR_WIDE;
+    const long long units = dev->max_pair_clusters;
+    const long long narrow_waves = (static_cast<long long>(num_tasks) * ((n + BN - 1) / BN) + units - 1) / units;
+    const long long wide_waves = (static_cast<long long>(num_tasks) * ((n + 2 * BN - 1) / (2 * BN)) + units - 1) / units;
+    if (tc_has(wide) && (v->wide_tiles == B200_WIDE_ON || 18 * wide_waves < 10 * narrow_waves)) {
+      tl = wide;
+      tile_cols = 2 * BN;
+      // the lhs map of the A-through-TMEM kernel is swizzled; the wide kernel stages A like the plain one
+      if (int rc = make_map_2d(&ta, lhs, k_packed, m, k_packed, BK / 2, BM, 0, "lhs"); rc != 0) return rc;
+    }
+  }
   GemmParams p{};
   p.mode = MODE_RAGGED_FWD;
   p.M = m;
   p.N = n;
   p.K = k;
-  p.tile_cols = BN;
+  p.tile_cols = tile_cols;
   p.tiles_m = num_tasks;
-  p.tiles_n = (n + BN - 1) / BN;
+  p.tiles_n = (n + tile_cols - 1) / tile_cols;
   p.num_tiles = p.tiles_m * p.tiles_n;
   p.group_m = 1;
   p.gate_col_offset = NBLK;

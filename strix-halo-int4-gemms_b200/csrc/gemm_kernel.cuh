@@ -205,7 +205,7 @@ __device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t, int 
     w.a_x = kAMn ? bs + rank_rows : 0;
     w.a_y = kAMn ? 0 : bs + rank_rows;
     w.b_y = g * p.rows_per_group_b;
-    w.n0 = nt * BN;
+    w.n0 = nt * p.tile_cols;  // 256, or 512 for the wide kernels
     w.n1 = w.n0 + NBLK;
     w.k_len = p.K;
     w.num_kb = (p.K + BK - 1) / BK;
@@ -308,7 +308,13 @@ static __device__ __noinline__ void tail_sum_into_tmem(uint32_t acc, const int4*
 //   FLAVOR_TAIL      per-channel kernels that can run the balanced tail (GemmParams::tail_units): the code for parts of
 //                    tiles and their partial sums is compiled into these instantiations only, so that it does not
 //                    weigh on the register allocation of the plain kernels
-enum : int { FLAVOR_PLAIN = 0, FLAVOR_FUSED_SC = 1, FLAVOR_TMEM_A = 2, FLAVOR_TAIL = 3 };
+//   FLAVOR_WIDE      per-channel int4 CTA-pair kernels with tiles of 256 x 512: every CTA unpacks its 128 rows of A once
+//                    per K block for TWO 128-column blocks of B (two MMAs of N = 256 per K step), a quarter less
+//                    unpack work and shared-memory traffic per output element; the 512 TMEM columns hold one
+//                    accumulator, so a tile's epilogue (eight warps) is not hidden behind the next tile's MMAs.
+//                    Two int8 stages and four packed ones: what counts is how far ahead TMA runs (measured at
+//                    4096^3: 54.6 us with 3 + 2 stages, 52.8 with 2 + 3, 52.1 with 2 + 4)
+enum : int { FLAVOR_PLAIN = 0, FLAVOR_FUSED_SC = 1, FLAVOR_TMEM_A = 2, FLAVOR_TAIL = 3, FLAVOR_WIDE = 5 };
 
 template <bool kInt4, bool kAMn, bool kBMn, int kScale, int kEpi, int kOut, bool kMaskK, bool k2Cta = false, int kFlavor = FLAVOR_PLAIN>
 struct KernelTraits {
@@ -323,7 +329,10 @@ struct KernelTraits {
                 "A through TMEM: per-channel int4 CTA-pair kernels with a row-major A");
   static constexpr bool kTail = kFlavor == FLAVOR_TAIL;
   static_assert(!kTail || (kScale == SCALE_PC && !kMaskK), "the balanced tail belongs to the dense per-channel kernels");
-  static constexpr int kAccBufs = kTmemA ? 1 : 2;          // accumulator buffers of 256 TMEM columns
+  static constexpr bool kWide = kFlavor == FLAVOR_WIDE;
+  static_assert(!kWide || (kInt4 && !kAMn && kBMn && k2Cta && kScale == SCALE_PC && !kMaskK && kEpi != EPI_SWIGLU && kOut == OUT_BF16),
+                "wide tiles: per-channel int4 CTA-pair kernels, NN layout, bf16 output, no gate block");
+  static constexpr int kAccBufs = (kTmemA || kWide) ? 1 : 2;  // accumulator buffers (256 TMEM columns; wide: one of 512)
   static constexpr int kTmemAStage0 = 256;                 // first TMEM column of the A stages (32 columns each)
   // Eight unpack warps beside the eight epilogue warps of a subchannel kernel were tried (640 threads: 168 registers
   // for the epilogue, 56 for the unpack warps): the spills made it a third slower than four unpack warps.
@@ -335,14 +344,14 @@ struct KernelTraits {
   // Kernels with eight epilogue warps re-balance registers between roles with setmaxnreg, which works on
   // warpgroups (4 consecutive warps): warps 0..3 = TMA, MMA and two idle warps, 4..11 = epilogue, then unpack
   // (4 warps next to the subchannel epilogue, whose running sums need 200 registers; 8 warps otherwise).
-  static constexpr bool kRegBalance = (kScale == SCALE_SC) || kShortK || kTmemA;
+  static constexpr bool kRegBalance = (kScale == SCALE_SC) || kShortK || kTmemA || kWide;
   static constexpr int kUnpackWarps = kInt4 ? ((kScale == SCALE_SC && !kWideSc) ? 4 : 8) : 0;
   static constexpr int kEpiWarps = kRegBalance ? 8 : 4;
   static constexpr int kEpiWarp0 = kRegBalance ? 4 : 2;
   static constexpr int kUnpackWarp0 = kEpiWarp0 + kEpiWarps;
   static constexpr int kThreads = (kUnpackWarp0 + kUnpackWarps) * 32;
-  static constexpr int kRegsLight = (kWideSc || kTmemA) ? 24 : (kScale == SCALE_SC) ? 32 : 40;    // TMA / MMA warpgroup (subchannel: every register counts)
-  static constexpr int kRegsUnpack = kWideSc ? 56 : kTmemA ? 72 : 80;
+  static constexpr int kRegsLight = (kWideSc || kTmemA || kWide) ? 24 : (kScale == SCALE_SC) ? 32 : 40;    // TMA / MMA warpgroup (subchannel: every register counts)
+  static constexpr int kRegsUnpack = kWideSc ? 56 : (kTmemA || kWide) ? 72 : 80;
   static constexpr int kRegsEpilogue = kWideSc ? 168 : (kScale == SCALE_SC) ? 200 : 136;  // subchannel: 128 running sums + room to interleave
   // The most registers per thread the kernel can be launched with (what the compiler may use before the
   // re-balance).  setmaxnreg.dec must not name more than a warp currently has, setmaxnreg.inc not less: a
@@ -354,13 +363,14 @@ struct KernelTraits {
   static constexpr int kRegPoolNeeded = kRegBalance ? (128 * kRegsLight + 256 * kRegsEpilogue + kUnpackWarps * 32 * kRegsUnpack) : 0;
   // A CTA of a pair holds one 128-wide block of B (the MMA reads the other one from the peer), so
   // its stages are a third smaller and more of them fit.
-  static constexpr int kBBlocks = k2Cta ? 1 : 2;
+  static constexpr int kBBlocks = (k2Cta && !kWide) ? 1 : 2;
   static constexpr int kStages = kTmemA ? 7
+                                 : kWide ? 2
                                  : kShortK ? (k2Cta ? 3 : 2)
                                  : kInt4 ? (k2Cta ? 4 : 3)
                                          : (k2Cta ? 6 : 4);  // int8 UMMA stages
   static constexpr int kPkStages =
-      kTmemA ? 4 : kInt4 ? (k2Cta ? (kShortK ? 3 : 4) : 2) : 0; // packed staging stages
+      kTmemA ? 4 : kWide ? 4 : kInt4 ? (k2Cta ? (kShortK ? 3 : 4) : 2) : 0; // packed staging stages
   static constexpr int kA8Bytes = kTmemA ? 0 : BM * BK;     // 16 KB (none: A lives in TMEM)
   static constexpr int kB8Bytes = kBBlocks * NBLK * BK;     // 32 KB (pair: 16 KB)
   static constexpr int kStageBytes = kA8Bytes + kB8Bytes;
@@ -370,7 +380,7 @@ struct KernelTraits {
   static constexpr int kBarBytes = 512;
   // results leave through shared memory + TMA stores (per-channel kernels; 2 KB per epilogue warp)
   static constexpr bool kTmaStore = (kScale == SCALE_PC) ? (kOut != OUT_S32) : (kOut == OUT_BF16);
-  static constexpr int kStagingSlots = 2;
+  static constexpr int kStagingSlots = kWide ? 1 : 2;
   // fp32 output of the backward kernels: two 4 KB slots per warp, so that a chunk is staged while TMA still
   // reads the previous one
   static constexpr int kF32Slots = kShortK ? 2 : 1;
@@ -400,6 +410,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   constexpr bool kFastSc = T::kFastSc;
   constexpr bool kTmemA = T::kTmemA;
   constexpr bool kTail = T::kTail;
+  constexpr bool kWide = T::kWide;
   static_assert(!kFastSc || kScale == SCALE_SC, "the fused accumulation order belongs to the subchannel kernels");
   // accumulator buffer and barrier phase of the grp-th accumulator hand-over
   auto acc_buf = [](int grp) { return grp % T::kAccBufs; };
@@ -522,7 +533,12 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
             // a CTA of a pair brings one block of B: the leader the first, its peer the second
             const int nb0 = (k2Cta && cta_rank != 0) ? w.n1 : w.n0;
-            if constexpr (kBMn) {
+            if constexpr (kWide) {
+              // this CTA's 128 columns of each of the tile's two 256-column halves
+              tma_load_2d(dst + T::kPkABytes, &tmap_b, w.n0 + NBLK * cta_rank, w.b_y + kb * (BK / 2), pk_full_bar(s));
+              tma_load_2d(dst + T::kPkABytes + T::kPkBBytes / 2, &tmap_b, w.n0 + BN + NBLK * cta_rank,
+                          w.b_y + kb * (BK / 2), pk_full_bar(s));
+            } else if constexpr (kBMn) {
               tma_load_2d(dst + T::kPkABytes, &tmap_b, nb0, w.b_y + kb * (BK / 2), pk_full_bar(s));
               if constexpr (!k2Cta)
                 tma_load_2d(dst + T::kPkABytes + T::kPkBBytes / 2, &tmap_b, w.n1,
@@ -642,6 +658,9 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 else
                   mma(tmem_base + b * BN, make_desc(a_lo + k * kAStep), make_desc(b_lo + k * kBStep),
                       ((kb | k) != 0 ? 1u : 0u) | onto);
+                if constexpr (kWide)  // the tile's second 256 columns: the same A, this pair's second blocks of B
+                  mma(tmem_base + BN, make_desc(a_lo + k * kAStep), make_desc(b_lo + ((T::kB8Bytes / 2) >> 4) + k * kBStep),
+                      ((kb | k) != 0 ? 1u : 0u));
               }
             }
             commit(empty_bar(s));
@@ -837,8 +856,9 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // latency per tile, overlapped with the wait for the accumulator.
         if constexpr (kOut != OUT_S32) {
           const int tc = 8 * lane;
-          const int bcol = (tc < NBLK) ? (w.n0 + tc) : (w.n1 + tc - NBLK);                 // column of b_scale
-          const int ocol = (tc < NBLK || kEpi != EPI_SWIGLU) ? (w.n0 + tc) : (w.n0 + tc - NBLK);  // output column
+          // wide tiles: the strip holds the scales of this warp's own 256 columns of the 512
+          const int bcol = kWide ? (w.n0 + BN * half + tc) : (tc < NBLK) ? (w.n0 + tc) : (w.n1 + tc - NBLK);  // column of b_scale
+          const int ocol = kWide ? bcol : (tc < NBLK || kEpi != EPI_SWIGLU) ? (w.n0 + tc) : (w.n0 + tc - NBLK);  // output column
           const long long idx = w.sb_off + bcol;
           float f[8];
           if (ocol + 8 <= p.N && (idx & 7) == 0) {
@@ -928,7 +948,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const float2 sa2 = make_float2(sa_pre, sa_pre);
 #pragma unroll
             for (int i4 = 0; i4 < 8; ++i4) {
-              const float4 sb4 = reinterpret_cast<const float4*>(sb_strip)[8 * c + i4];  // broadcast read
+              const float4 sb4 = reinterpret_cast<const float4*>(sb_strip)[8 * (kWide ? (c & 7) : c) + i4];  // broadcast read
               const float2 lo = __fmul2_rn(__fmul2_rn(make_float2(static_cast<float>(static_cast<int>(r[4 * i4])),
                                                                   static_cast<float>(static_cast<int>(r[4 * i4 + 1]))), sa2),
                                            make_float2(sb4.x, sb4.y));
@@ -962,11 +982,14 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               // are clipped by the tensor map.  bf16: 64 B per row, two 2 KB slots, 64-byte swizzle
               // (chunk ^ ((row >> 1) & 3)).  fp32: 128 B per row, one 4 KB slot, 128-byte swizzle.
               if constexpr (kOut == OUT_BF16) {
-                const int slot = store_count & 1;
+                const int slot = T::kStagingSlots == 2 ? (store_count & 1) : 0;
                 ++store_count;
                 uint8_t* dst = stage_out + slot * 2048 + lane * 64;
                 const int sw = (lane >> 1) & 3;
-                if (lane == 0) bulk_wait_read_keep1();
+                if (lane == 0) {
+                  if constexpr (T::kStagingSlots == 2) bulk_wait_read_keep1();
+                  else bulk_wait_read_all();
+                }
                 __syncwarp();
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -1069,7 +1092,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         };
 
-        constexpr int kAllChunks = (kEpi == EPI_SWIGLU) ? 4 : 8;
+        constexpr int kAllChunks = (kEpi == EPI_SWIGLU) ? 4 : kWide ? 16 : 8;
         // with eight epilogue warps, the two warps of a lane quarter split the chunks between them
         constexpr int kOutChunks = kAllChunks / (T::kEpiWarps / 4);
         const int c_first = half * kOutChunks;
@@ -1413,12 +1436,13 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint8_t* pk_b = pk_a + T::kPkABytes;
           // all loads of the stage first: they do not depend on the int8 stage being free
           // B items are handled in batches of at most 4 to bound the registers holding raw data
-          constexpr int kBItems = (k2Cta ? 512 : 1024) / UT;  // one or two 128-wide blocks of B
+          constexpr bool kOneB = T::kBBlocks == 1;
+          constexpr int kBItems = (kOneB ? 512 : 1024) / UT;  // one or two 128-wide blocks of B
           constexpr int kBBatch = kBItems < 4 ? kBItems : 4;
           uint4 xa[kTmemA ? 1 : 512 / UT];
           uint4 xb[kBBatch];  // K-major B: packed tile [256 rows][64 B], same item scheme as K-major A
           auto load_b = [&](int j) -> uint4 {
-            if constexpr (kBMn && k2Cta) return *reinterpret_cast<const uint4*>(pk_b + m_src0 + j * (kMRowsPerPass * 128));
+            if constexpr (kBMn && kOneB) return *reinterpret_cast<const uint4*>(pk_b + m_src0 + j * (kMRowsPerPass * 128));
             else if constexpr (kBMn) return *reinterpret_cast<const uint4*>(pk_b + b_src0 + j * (kBRowsPerPass * 128));
             else return *reinterpret_cast<const uint4*>(pk_b + a_src0 + j * (kARowsPerPass * 64));
           };
@@ -1481,7 +1505,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
                 *reinterpret_cast<uint4*>(b8 + a_dst_lo0 + j * (kARowsPerPass * 128)) = lo;
                 *reinterpret_cast<uint4*>(b8 + a_dst_hi0 + j * (kARowsPerPass * 128)) = hi;
-              } else if constexpr (k2Cta) {
+              } else if constexpr (kOneB) {
                 // one block, same item scheme as an MN-major A: packed row m_p0 + kMRowsPerPass * j
                 if constexpr (kMaskK) {
                   const int k_lo = kb * BK + 2 * (m_p0 + kMRowsPerPass * j);

@@ -97,6 +97,9 @@ struct TcKernelInfo {
   X(false, false, false, SCALE_PC, EPI_RELU2, OUT_BF16, false, true, FLAVOR_PLAIN)    \
   X(true, false, true, SCALE_SC, EPI_RELU2, OUT_BF16, false, true, FLAVOR_PLAIN)      \
   X(true, true, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true, FLAVOR_PLAIN)        \
+  /* per-channel int4 CTA pairs on 256 x 512 tiles */ \
+  X(true, false, true, SCALE_PC, EPI_NONE, OUT_BF16, false, true, FLAVOR_WIDE)        \
+  X(true, false, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, true, FLAVOR_WIDE)       \
   /* a transposed A ([K, M]) with fused activations and with subchannel scales for int8 */ \
   X(true, true, true, SCALE_PC, EPI_RELU2, OUT_BF16, false, false, FLAVOR_PLAIN)      \
   X(true, true, true, SCALE_PC, EPI_SWIGLU, OUT_BF16, false, false, FLAVOR_PLAIN)     \

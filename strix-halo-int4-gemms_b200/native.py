@@ -34,6 +34,7 @@ LAUNCHED_NOTHING, LAUNCHED_TCGEN05, LAUNCHED_TCGEN05_PAIR, LAUNCHED_SIMT = 0, 1,
 ACCUMULATE_FUSED, ACCUMULATE_REFERENCE = 0, 1
 A_OPERAND_AUTO, A_OPERAND_SMEM, A_OPERAND_TMEM = 0, 1, 2
 TAIL_AUTO, TAIL_OFF, TAIL_ALWAYS = 0, 1, 2
+WIDE_AUTO, WIDE_OFF, WIDE_ON = 0, 1, 2
 
 # Order of roundings of subchannel dense launches made through the registry / public API: "fused" (default; the
 # last multiply and the add of each K-group share one rounding) or "reference" (every rounding of the reference's
@@ -103,7 +104,7 @@ class GemmVariant(ctypes.Structure):
         ("a_operand", ctypes.c_int32),
         ("tail_balance", ctypes.c_int32),
         ("task_align", ctypes.c_int32),
-        ("reserved", ctypes.c_int32 * 1),
+        ("wide_tiles", ctypes.c_int32),
     ]
 
 
@@ -371,6 +372,7 @@ def make_variant(
     a_operand: int = A_OPERAND_AUTO,
     tail_balance: int = TAIL_AUTO,
     task_align: int = 0,
+    wide_tiles: int = 0,
 ) -> GemmVariant:
     """The C variant record of one launch.  ``schedule`` is the registry's launch form; ``cta_group``
     (CTA_GROUP_*) overrides the form's CTA choice when given."""
@@ -389,6 +391,7 @@ def make_variant(
     variant.accumulate_order = int(_ACCUMULATION_ORDER if accumulate_order is None else accumulate_order)
     variant.a_operand = int(a_operand)
     variant.tail_balance = int(tail_balance)
+    variant.wide_tiles = int(wide_tiles)   # WIDE_AUTO / WIDE_OFF / WIDE_ON: 256 x 512 tiles on CTA pairs
     variant.task_align = int(task_align)   # grouped forward: what the tasks' block starts are multiples of (0: not stated)
     return variant
 
@@ -613,6 +616,7 @@ def launch_ragged_fwd_kernel(
     stream: Any | None = None,
     path: int = PATH_AUTO,
     a_operand: int = A_OPERAND_AUTO,
+    wide_tiles: int = WIDE_AUTO,
 ) -> Any:
     """Grouped forward launch over prebuilt row-block tasks (reference native.py:533-600)."""
     torch = _torch()
@@ -628,7 +632,7 @@ def launch_ragged_fwd_kernel(
     library = load_dispatch_library(library_path)
     record = make_variant(
         dtype=OperandDType.INT4, layout=layout, scale=scale, epilogue=Epilogue.NONE,
-        out_dtype=OUT_F32 if out.dtype is torch.float32 else OUT_BF16, path=path, a_operand=a_operand,
+        out_dtype=OUT_F32 if out.dtype is torch.float32 else OUT_BF16, path=path, a_operand=a_operand, wide_tiles=wide_tiles,
         # a transposed lhs reaches the tensor cores only when every task starts on a multiple of 16 rows
         task_align=int(getattr(group_info, "align_tile", None) or 0),
     )

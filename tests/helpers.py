@@ -75,7 +75,7 @@ def assert_close_rms(got: np.ndarray, want: np.ndarray, *, rtol=1e-2, atol_rms=1
 # GPU side: calls through the C ABI (ctypes) with arbitrary shapes
 # ----------------------------------------------------------------------------------------------
 def abi_dense(pkg, case, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue="none", out="bf16", path=0, schedule="persistent", cta_group=0,
-              order="reference", a_operand=0, tail=None):
+              order="reference", a_operand=0, tail=None, wide=None):
     """One dense launch through ``b200_int4_gemms_launch_dense``; returns the CUDA output tensor.  ``order``: the
     subchannel accumulation order, "reference" (every rounding of the reference math: what the bit-equality checks
     use) or "fused" (the library's default)."""
@@ -96,6 +96,7 @@ def abi_dense(pkg, case, *, m, n, k, dtype="int4", layout="nn", sub=0, epilogue=
         accumulate_order=native.ACCUMULATE_REFERENCE if order == "reference" else native.ACCUMULATE_FUSED,
         a_operand=a_operand,
         tail_balance=native.TAIL_OFF if tail is False else (native.TAIL_ALWAYS if tail is True else native.TAIL_AUTO),
+        wide_tiles=native.WIDE_OFF if wide is False else (native.WIDE_ON if wide is True else native.WIDE_AUTO),
     )
     stream = torch.cuda.current_stream().cuda_stream
     # tail=True / False: hand the launch the workspace the balanced tail needs and ask for it wherever it applies
