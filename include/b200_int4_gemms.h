@@ -90,7 +90,10 @@ enum { B200_TAIL_AUTO = 0, B200_TAIL_OFF = 1, B200_TAIL_ALWAYS = 2 };
  * block for two blocks of B (a quarter less unpack work and shared-memory traffic per output element; one
  * accumulator fills TMEM, so the epilogue of a tile is not hidden behind the next tile).  AUTO takes wide tiles when
  * their waves, at 0.9 of the time of two narrow tiles each, need less time than the narrow tiles' waves; OFF / ON
- * force either (ON falls back where no wide kernel exists).  Bit-identical results. */
+ * force either (ON falls back where no wide kernel exists).  Where the wide tiles leave a thin last wave (at most
+ * eight full waves before it, N a multiple of 512, tail_balance not OFF) three 512-column tiles of a row are traded
+ * for four of 384 columns (second MMA with N = 128) until the last wave holds 384-column tiles only: at 4096^3, 74
+ * tiles of 512 and 72 of 384 columns instead of 128 of 512, 52.1 -> 49.8 us.  Bit-identical results. */
 enum { B200_WIDE_AUTO = 0, B200_WIDE_OFF = 1, B200_WIDE_ON = 2 };
 
 typedef struct b200_gemm_variant {
@@ -191,7 +194,7 @@ typedef struct b200_dense_plan {
   int32_t group_m;   /* raster width in row tiles */
   int32_t split_k;   /* slices actually used */
   int32_t tail_units; /* > 0: the balanced tail is used, over this many CTAs (pairs), given a workspace */
-  int32_t reserved[1];
+  int32_t tiles_384; /* wide tiles only: tiles of 384 instead of 512 columns (mixed column cuts for a thin last wave) */
 } b200_dense_plan;
 int b200_int4_gemms_plan_dense(const b200_gemm_variant* variant, int device_index, int32_t m, int32_t n,
                                int32_t k, b200_dense_plan* plan);

@@ -386,6 +386,8 @@ struct DensePlan {
   bool integer_partials = false;
   int tail_units = 0;    // > 0: balanced tail over this many scheduling units (needs the workspace)
   int tail_split = 0, tail_waves = 0, tail_rest = 0;
+  // wide kernel, mixed column cuts (GemmParams::mix_*); mix_total_wide < 0: all tiles 512 columns wide
+  int mix_total_wide = -1, mix_rows_hi = 0, mix_wide_hi = 0, mix_wide_lo = 0, mix_tq_hi = 0, mix_tq_lo = 0;
 };
 
 // Workspace of the balanced tail: one partial-sum slot of 2 x 128 x 256 s32 per scheduling unit, then the flags.
@@ -531,6 +533,24 @@ int plan_dense(const b200_gemm_variant* v, const DeviceState* dev, const void* a
         const int wide_tiles = pl.tiles_m * pl.tiles_n;
         pl.grid = (wide_tiles < max_units ? wide_tiles : max_units) * cta_per_tile;
         if (v->group_m <= 0) pl.group_m = 4;  // with TMA four K blocks ahead the raster hardly matters; 1 .. 8 measured alike
+        // A thin last wave: trade three 512-column tiles of a row for four of 384 columns (a 384-column tile takes
+        // 0.9 of the time of a whole one) until the last wave holds 384-column tiles only.  Only where one wave is a
+        // visible share of the run and N is whole 512-column tiles.
+        const int rest_w = wide_tiles % max_units, full_w = wide_tiles / max_units;
+        if (v->tail_balance != B200_TAIL_OFF && rest_w > 0 && full_w >= 1 && full_w <= 8 && n % (2 * BN) == 0) {
+          const int swaps = (rest_w + 2) / 3;                       // each swap removes three wide tiles, adds four narrower
+          const int spill = 3 * swaps - rest_w;                     // 384-column tiles that land in the last full wave
+          const int per_row_max = wide_cols / 3;
+          if (4 * swaps - spill <= max_units && swaps <= pl.tiles_m * per_row_max) {
+            const int lo = swaps / pl.tiles_m, hi_rows = swaps % pl.tiles_m;   // swaps per row tile: lo, or lo + 1 for the first hi_rows
+            pl.mix_rows_hi = hi_rows;
+            pl.mix_wide_hi = wide_cols - 3 * (lo + 1);
+            pl.mix_wide_lo = wide_cols - 3 * lo;
+            pl.mix_tq_hi = 4 * (lo + 1);
+            pl.mix_tq_lo = 4 * lo;
+            pl.mix_total_wide = wide_tiles - 3 * swaps;
+          }
+        }
       }
     }
     pl.kernel = tl;
@@ -586,6 +606,7 @@ extern "C" int b200_int4_gemms_plan_dense(const b200_gemm_variant* v, int device
   out->group_m = pl.tensor_core ? pl.group_m : 0;
   out->split_k = pl.slices;
   out->tail_units = pl.tail_units;
+  if (pl.mix_total_wide >= 0) out->tiles_384 = pl.mix_rows_hi * pl.mix_tq_hi + (pl.tiles_m - pl.mix_rows_hi) * pl.mix_tq_lo;
   return 0;
 }
 
@@ -690,6 +711,15 @@ extern "C" int b200_int4_gemms_launch_dense(const b200_gemm_variant* v, int devi
   p.k_slices = pl.slices;
   p.k_per_slice = pl.k_per_slice;
   p.num_tiles = p.tiles_m * p.tiles_n * pl.slices;
+  p.mix_total_wide = pl.mix_total_wide;
+  if (pl.mix_total_wide >= 0) {
+    p.mix_rows_hi = pl.mix_rows_hi;
+    p.mix_wide_hi = pl.mix_wide_hi;
+    p.mix_wide_lo = pl.mix_wide_lo;
+    p.mix_tq_hi = pl.mix_tq_hi;
+    p.mix_tq_lo = pl.mix_tq_lo;
+    p.num_tiles = pl.mix_total_wide + pl.mix_rows_hi * pl.mix_tq_hi + (p.tiles_m - pl.mix_rows_hi) * pl.mix_tq_lo;
+  }
   p.group_m = pl.group_m;
   p.gate_col_offset = swiglu ? n : NBLK;
   p.ldc = n;

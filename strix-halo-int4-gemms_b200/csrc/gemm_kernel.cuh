@@ -77,6 +77,11 @@ struct GemmParams {
   int* tail_partials;    // [units][2 ranks][128][256] s32
   int* tail_flags;       // [units][2 ranks][2]: epilogue warps that have written their part, and readers that have seen
                          // it; zero before the first launch on a workspace, and again at the end of every launch
+  // wide kernels, dense: mixed column cuts.  The first mix_rows_hi row tiles hold mix_wide_hi tiles of 512 columns
+  // followed by mix_tq_hi tiles of 384, the other row tiles mix_wide_lo and mix_tq_lo; the tile list has all the
+  // 512-column tiles first (mix_total_wide of them) and then the 384-column ones, so that the last wave of the
+  // round-robin schedule holds tiles of three quarters of the width only.  mix_total_wide < 0: one width (tile_cols)
+  int mix_total_wide, mix_rows_hi, mix_wide_hi, mix_wide_lo, mix_tq_hi, mix_tq_lo;
   // ragged
   int num_groups;
   int rows_per_group_a;  // rows of the stacked A map per group (bwd)
@@ -109,6 +114,7 @@ struct TileWork {
   int k_first;       // first valid k (1 when a flat group starts on the odd token of a byte, else 0)
   int part;          // balanced tail: PART_WHOLE, PART_OWNER (part 0 + the other parts' partial sums), PART_PRODUCER
   int part_slot;     // partial-sum slot written (producer: its own unit)
+  int tq;            // wide kernels: 1 = the tile is 384 columns wide (its second MMA has N = 128: 64 columns per CTA)
   int out_row0;      // output row of tile row 0
   int row_lo, row_hi;// valid output rows [lo, hi)
   long long out_off; // element offset added to out (bwd: g*M*N)
@@ -122,7 +128,7 @@ enum : int { PART_WHOLE = 0, PART_OWNER = 1, PART_PRODUCER = 2 };
 // `rank` is the CTA's rank in its pair (always 0 for single-CTA kernels); `unit` the scheduling unit (cluster or CTA)
 // index, used by the balanced-tail schedule, in which `t` counts the unit's own segments.  A pair works on 256 rows of
 // output: rank r owns rows [128 r, 128 r + 128) of them, and p.tiles_m counts 256-row tiles.
-template <bool kAMn, bool k2Cta, bool kTail = false>
+template <bool kAMn, bool k2Cta, bool kTail = false, bool kWide = false>
 __device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t, int rank, int unit) {
   constexpr int RM = k2Cta ? 2 * BM : BM;  // output rows per scheduled tile
   const int rank_rows = k2Cta ? rank * BM : 0;
@@ -132,6 +138,7 @@ __device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t, int 
   w.kb0 = 0;
   w.part = PART_WHOLE;
   w.part_slot = 0;
+  w.tq = 0;
   w.out_off = 0;
   w.out_row_base = 0;
   w.sa_off = 0;
@@ -168,12 +175,32 @@ __device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t, int 
     const int first_m = grp * p.group_m;
     const int rows_here = min(p.tiles_m - first_m, p.group_m);
     const int local = t - grp * per_group;
-    const int mt = first_m + local % rows_here;
+    int mt = first_m + local % rows_here;
     const int nt = local / rows_here;
+    int n0 = nt * p.tile_cols;
+    if (kWide && p.mix_total_wide >= 0) {
+      // mixed column cuts: row by row, the 512-column tiles of every row first, then the 384-column ones
+      const bool tq = t >= p.mix_total_wide;
+      const int u = tq ? t - p.mix_total_wide : t;
+      const int per_hi = tq ? p.mix_tq_hi : p.mix_wide_hi, per_lo = tq ? p.mix_tq_lo : p.mix_wide_lo;
+      const int hi_span = p.mix_rows_hi * per_hi;
+      int idx;
+      if (u < hi_span) {
+        mt = u / per_hi;
+        idx = u - mt * per_hi;
+      } else {
+        const int r = (u - hi_span) / per_lo;
+        mt = p.mix_rows_hi + r;
+        idx = (u - hi_span) - r * per_lo;
+      }
+      const int wide_before = tq ? (mt < p.mix_rows_hi ? p.mix_wide_hi : p.mix_wide_lo) : 0;
+      n0 = wide_before * (2 * BN) + idx * (tq ? 3 * NBLK : 2 * BN);
+      w.tq = tq ? 1 : 0;
+    }
     w.a_x = kAMn ? mt * RM + rank_rows : 0;
     w.a_y = kAMn ? 0 : mt * RM + rank_rows;
     w.b_y = 0;
-    w.n0 = nt * p.tile_cols;
+    w.n0 = n0;
     w.n1 = w.n0 + p.gate_col_offset;
     w.k_len = p.K;
     if (p.k_slices > 1) {
@@ -517,7 +544,9 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int it = 0;
       bool ok = true;
       for (int t = tile0; t < num_tiles && ok; t += tile_step) {
-        const TileWork w = decode_tile<kAMn, k2Cta, kTail>(p, t, cta_rank, unit);
+        const TileWork w = decode_tile<kAMn, k2Cta, kTail, kWide>(p, t, cta_rank, unit);
+        // wide tiles: this CTA's share of the tile's second 256 (or, for a 384-column tile, 128) columns
+        const int wide_b1_x = w.n0 + BN + (w.tq ? NBLK / 2 : NBLK) * cta_rank;
         for (int kbl = 0; kbl < w.num_kb; ++kbl, ++it) {
           const int kb = kbl + w.kb0;  // K block of the whole reduction (a split-K slice starts past 0)
           if constexpr (kInt4) {
@@ -536,8 +565,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if constexpr (kWide) {
               // this CTA's 128 columns of each of the tile's two 256-column halves
               tma_load_2d(dst + T::kPkABytes, &tmap_b, w.n0 + NBLK * cta_rank, w.b_y + kb * (BK / 2), pk_full_bar(s));
-              tma_load_2d(dst + T::kPkABytes + T::kPkBBytes / 2, &tmap_b, w.n0 + BN + NBLK * cta_rank,
-                          w.b_y + kb * (BK / 2), pk_full_bar(s));
+              tma_load_2d(dst + T::kPkABytes + T::kPkBBytes / 2, &tmap_b, wide_b1_x, w.b_y + kb * (BK / 2), pk_full_bar(s));
             } else if constexpr (kBMn) {
               tma_load_2d(dst + T::kPkABytes, &tmap_b, nb0, w.b_y + kb * (BK / 2), pk_full_bar(s));
               if constexpr (!k2Cta)
@@ -602,7 +630,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int it = 0;
       bool ok = true;
       for (int t = tile0; t < num_tiles && ok; t += tile_step) {
-        const TileWork w = decode_tile<kAMn, k2Cta, kTail>(p, t, cta_rank, unit);
+        const TileWork w = decode_tile<kAMn, k2Cta, kTail, kWide>(p, t, cta_rank, unit);
         for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
@@ -627,8 +655,10 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int grp = 0;  // accumulator hand-over counter (one per K-group)
     bool ok = true;
     for (int t = tile0; t < num_tiles && ok; t += tile_step) {
-      const TileWork w = decode_tile<kAMn, k2Cta, kTail>(p, t, cta_rank, unit);
+      const TileWork w = decode_tile<kAMn, k2Cta, kTail, kWide>(p, t, cta_rank, unit);
       const int total_mma = (w.k_len + 31) / 32;  // K=32 steps that hold real data
+      // 384-column tiles: the second MMA covers 128 columns, the first 64 of each CTA's second block of B
+      const uint32_t idesc_second = (kWide && w.tq) ? umma_idesc_i8(k2Cta ? 2 * BM : BM, NBLK, kAMn, kBMn) : idesc;
       if constexpr (kScale == SCALE_PC) {
         if (w.num_kb == 0) continue;
         const int b = acc_buf(grp);
@@ -659,8 +689,8 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   mma(tmem_base + b * BN, make_desc(a_lo + k * kAStep), make_desc(b_lo + k * kBStep),
                       ((kb | k) != 0 ? 1u : 0u) | onto);
                 if constexpr (kWide)  // the tile's second 256 columns: the same A, this pair's second blocks of B
-                  mma(tmem_base + BN, make_desc(a_lo + k * kAStep), make_desc(b_lo + ((T::kB8Bytes / 2) >> 4) + k * kBStep),
-                      ((kb | k) != 0 ? 1u : 0u));
+                  umma_i8_pair(tmem_base + BN, make_desc(a_lo + k * kAStep), make_desc(b_lo + ((T::kB8Bytes / 2) >> 4) + k * kBStep),
+                               idesc_second, ((kb | k) != 0 ? 1u : 0u));
               }
             }
             commit(empty_bar(s));
@@ -840,7 +870,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     //   subchannel, 8 warps : plain -> [128*half, +128); SwiGLU -> up [64*half,+64) with gate 128+[64*half,+64)
     constexpr int kOwnCols = (kScale == SCALE_SC) ? 128 : 256;
     for (int t = tile0; t < num_tiles && ok; t += tile_step) {
-      const TileWork w = decode_tile<kAMn, k2Cta, kTail>(p, t, cta_rank, unit);
+      const TileWork w = decode_tile<kAMn, k2Cta, kTail, kWide>(p, t, cta_rank, unit);
       const int row = w.out_row0 + row_in_tile;
       const bool row_ok = (row >= w.row_lo) && (row < w.row_hi);
       const long long sa_row = w.sa_off + static_cast<long long>(row) * (kScale == SCALE_SC ? p.scale_cols : 1);
@@ -1096,13 +1126,14 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // with eight epilogue warps, the two warps of a lane quarter split the chunks between them
         constexpr int kOutChunks = kAllChunks / (T::kEpiWarps / 4);
         const int c_first = half * kOutChunks;
+        const int c_end = c_first + ((kWide && w.tq && half == 1) ? kOutChunks / 2 : kOutChunks);  // 384 columns: chunks 8 .. 11
         // two register sets: the TMEM read of the next chunk is in flight while this one is processed
         uint32_t ra[32], rb[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) { ra[i] = 0u; rb[i] = 0u; }
         if (!zero_tile && kOutChunks > 0) tmem_ld_32x32b_x32(acc_addr + 32 * c_first, ra);
 #pragma unroll 1
-        for (int c = c_first; c < c_first + kOutChunks; c += 2) {
+        for (int c = c_first; c < c_end; c += 2) {
           if (!zero_tile) {
             tmem_ld_wait();
             tmem_ld_fence(ra);
@@ -1112,7 +1143,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (!zero_tile) {
             tmem_ld_wait();
             tmem_ld_fence(rb);
-            if (c + 2 < c_first + kOutChunks) {
+            if (c + 2 < c_end) {
               tmem_ld_32x32b_x32(acc_addr + 32 * (c + 2), ra);
             } else if constexpr (kEpi != EPI_SWIGLU) {
               // the warp's last chunk is in registers: hand the accumulator back before processing it (the SwiGLU
@@ -1363,7 +1394,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         int it = 0;
         bool ok = true;
         for (int t = tile0; t < num_tiles && ok; t += tile_step) {
-          const TileWork w = decode_tile<kAMn, k2Cta, kTail>(p, t, cta_rank, unit);
+          const TileWork w = decode_tile<kAMn, k2Cta, kTail, kWide>(p, t, cta_rank, unit);
           for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
             const int ps = it % PS;
             const uint32_t pph = (it / PS) & 1;
@@ -1425,7 +1456,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int it = 0;
       bool ok = true;
       for (int t = tile0; t < num_tiles && ok; t += tile_step) {
-        const TileWork w = decode_tile<kAMn, k2Cta, kTail>(p, t, cta_rank, unit);
+        const TileWork w = decode_tile<kAMn, k2Cta, kTail, kWide>(p, t, cta_rank, unit);
         for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
           const int ps = it % PS;
           const uint32_t pph = (it / PS) & 1;

@@ -119,7 +119,7 @@ class DensePlan(ctypes.Structure):
         ("group_m", ctypes.c_int32),
         ("split_k", ctypes.c_int32),
         ("tail_units", ctypes.c_int32),
-        ("reserved", ctypes.c_int32 * 1),
+        ("tiles_384", ctypes.c_int32),
     ]
 
     def as_tuple(self) -> tuple[int, int, int, int, int, int]:

@@ -22,7 +22,12 @@ def _plan(pkg, *, m, n, k, dtype="int4", epilogue="none", wide=None, sub=0, layo
 
 
 def test_plan_takes_wide_tiles_when_their_waves_need_less_time(pkg):
-    assert _plan(pkg, m=4096, n=4096, k=4096).tile_cols == 512            # 128 wide tiles in 2 waves against 256 in 4
+    plan = _plan(pkg, m=4096, n=4096, k=4096)                            # 128 wide tiles in 2 waves against 256 in 4 ...
+    assert plan.tile_cols == 512 and plan.tiles_384 == 72 and plan.grid == 148   # ... recut as 74 of 512 and 72 of 384 columns
+    assert _plan(pkg, m=8192, n=8192, k=8192).tiles_384 == 0              # 6.9 waves: the last one is full enough
+    assert _plan(pkg, m=3840, n=4096, k=4096).tiles_384 == 64             # 120 tiles: 46 past the wave, 16 swaps, two of them early
+    assert _plan(pkg, m=2560, n=4096, k=4096).tile_cols == 256            # 160 narrow tiles in 3 waves beat 80 wide ones in 2
+    assert _plan(pkg, m=2560, n=4096, k=4096, wide=True).tiles_384 == 8   # forced: 80 tiles, two swaps in the first two row tiles
     assert _plan(pkg, m=8192, n=8192, k=8192).tile_cols == 512            # also where A through TMEM used to be chosen
     assert _plan(pkg, m=4096, n=4096, k=4096, wide=False).tile_cols == 256
     assert _plan(pkg, m=1024, n=2048, k=4096).tile_cols == 256            # 32 tiles: one wave either way
@@ -38,7 +43,10 @@ def test_plan_takes_wide_tiles_when_their_waves_need_less_time(pkg):
     (2048 + 128, 2560, 384),    # five wide column tiles, a half-empty last row of tiles
     (768, 512 + 48, 256),       # the second wide tile holds 48 columns
     (256, 256 + 16, 1024),      # a wide tile with little more than its first half
-    (4096, 4096, 640),          # two waves of wide tiles on the whole GPU
+    (4096, 4096, 640),          # two waves on the whole GPU: 74 tiles of 512 columns, then 72 of 384
+    (3840, 4096, 512),          # 72 + 64: two 384-column tiles end the first wave
+    (2560, 4096, 384),          # 74 + 8: only the first two row tiles are recut
+    (2560 - 128, 4096, 256),    # the same with a half-empty last row of tiles
 ])
 @pytest.mark.parametrize("epilogue", ["none", "relu2"])
 def test_wide_tiles_equal_narrow_tiles_and_the_cuda_core_kernel(pkg, m, n, k, epilogue):
