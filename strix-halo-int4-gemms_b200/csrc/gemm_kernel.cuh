@@ -285,6 +285,8 @@ __device__ __forceinline__ TileWork decode_tile(const GemmParams& p, int t, int 
     w.sa_off = static_cast<long long>(g) * p.M * (p.subchannel ? p.scale_cols : 1);
     w.sb_off = static_cast<long long>(g) * p.lds_b * (p.subchannel ? p.scale_cols : 1);
   }
+  // wide kernels: a last column tile that holds between 257 and 384 columns runs as a 384-column tile as well
+  if (kWide && p.N - w.n0 <= 3 * NBLK && p.N - w.n0 > 2 * NBLK) w.tq = 1;
   return w;
 }
 
