@@ -395,11 +395,13 @@ struct KernelTraits {
   static constexpr int kBBlocks = (k2Cta && !kWide) ? 1 : 2;
   static constexpr int kStages = kTmemA ? 7
                                  : kWide ? 2
-                                 : kShortK ? (k2Cta ? 3 : 2)
+                                 : kShortK ? 2
                                  : kInt4 ? (k2Cta ? 4 : 3)
                                          : (k2Cta ? 6 : 4);  // int8 UMMA stages
   static constexpr int kPkStages =
-      kTmemA ? 4 : kWide ? 4 : kInt4 ? (k2Cta ? (kShortK ? 3 : 4) : 2) : 0; // packed staging stages
+      kTmemA ? 4 : kWide ? 4 : kInt4 ? (k2Cta ? (kShortK ? 5 : 4) : 2) : 0; // packed staging stages (backward pairs: a group's reduction is
+                                                                  // short, so what pays is TMA running five K blocks ahead across tiles:
+                                                                  // 200.5 us with 3 + 3 stages, 190.1 with 2 + 4, 186.2 with 2 + 5)
   static constexpr int kA8Bytes = kTmemA ? 0 : BM * BK;     // 16 KB (none: A lives in TMEM)
   static constexpr int kB8Bytes = kBBlocks * NBLK * BK;     // 32 KB (pair: 16 KB)
   static constexpr int kStageBytes = kA8Bytes + kB8Bytes;
